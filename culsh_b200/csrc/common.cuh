@@ -1,0 +1,234 @@
+// Shared host/device helpers: error plumbing, the per-handle context, stream-ordered
+// buffers and the key layout description.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <curand.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/culsh_b200.h"
+
+namespace culsh_b200 {
+
+// ---------------------------------------------------------------------------------------
+// Errors: host code throws Error, the C ABI catches it and returns the status code.
+// ---------------------------------------------------------------------------------------
+struct Error : public std::runtime_error {
+    int status;
+    Error(int s, const std::string& m) : std::runtime_error(m), status(s) {}
+};
+
+[[noreturn]] inline void fail(int status, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    throw Error(status, buf);
+}
+
+#define CU_CHECK(call)                                                                      \
+    do {                                                                                    \
+        cudaError_t e__ = (call);                                                           \
+        if (e__ != cudaSuccess)                                                             \
+            ::culsh_b200::fail(e__ == cudaErrorMemoryAllocation ? CULSH_ERR_ALLOC           \
+                                                                : CULSH_ERR_CUDA,           \
+                               "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__),     \
+                               __FILE__, __LINE__);                                         \
+    } while (0)
+
+#define CURAND_CHECK(call)                                                                  \
+    do {                                                                                    \
+        curandStatus_t s__ = (call);                                                        \
+        if (s__ != CURAND_STATUS_SUCCESS)                                                   \
+            ::culsh_b200::fail(CULSH_ERR_CUDA, "%s failed: curand status %d (%s:%d)", #call, \
+                               (int)s__, __FILE__, __LINE__);                               \
+    } while (0)
+
+#define KERNEL_CHECK() CU_CHECK(cudaGetLastError())
+
+inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// ---------------------------------------------------------------------------------------
+// Key layout.  A signature of one (row, table) is held as NW 32-bit words, word 0 most
+// significant, so that comparing the words as unsigned integers in order equals the
+// unsigned byte-lexicographic order of upstream's raw signature memory
+// (core/fit.cuh:265-282, core/query.cuh:44-48):
+//   RPLSH   : k sign bits, hash 0 as the most significant bit, right-aligned.
+//   PSLSH   : for each hash its low `elem_bytes` bytes in little-endian order (the
+//             remaining bytes of the int32 are sign extension, so they never decide a
+//             comparison once every stored value fits the narrow width).
+//   MinHash : bswap32 of each uint32 hash (elem_bytes = 4).
+// key_bytes counts the significant bytes (the radix passes); unused leading bytes are 0.
+// ---------------------------------------------------------------------------------------
+struct KeySpec {
+    int family = 0;
+    int n_hashes = 0;
+    int elem_bytes = 0;  // RPLSH: 0 (bit-packed)
+    int key_bytes = 0;
+    int key_words = 0;   // NW, one of 1, 2, 4, 8, 16
+    int sig_nbytes = 0;  // upstream's raw width
+};
+
+inline int round_key_words(int bytes) {
+    int w = (bytes + 3) / 4;
+    if (w <= 1) return 1;
+    if (w <= 2) return 2;
+    if (w <= 4) return 4;
+    if (w <= 8) return 8;
+    if (w <= 16) return 16;
+    return -1;
+}
+
+inline KeySpec make_key_spec(int family, int k, int elem_bytes) {
+    KeySpec s;
+    s.family = family;
+    s.n_hashes = k;
+    if (family == CULSH_RPLSH) {
+        s.elem_bytes = 0;
+        s.key_bytes = (k + 7) / 8;
+        s.sig_nbytes = k;
+    } else {
+        s.elem_bytes = (family == CULSH_MINHASH) ? 4 : elem_bytes;
+        s.key_bytes = k * s.elem_bytes;
+        s.sig_nbytes = k * 4;
+    }
+    s.key_words = round_key_words(s.key_bytes);
+    return s;
+}
+
+// ---------------------------------------------------------------------------------------
+// Context behind a handle: device, stream, a pinned scratch block for small D2H reads,
+// staging buffers for host inputs, cached hash parameters.
+// ---------------------------------------------------------------------------------------
+struct ParamKey {
+    int family, H, d, window, is_double;
+    uint64_t seed;
+    bool operator<(const ParamKey& o) const {
+        return std::memcmp(this, &o, sizeof(ParamKey)) < 0;
+    }
+};
+
+struct Ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev[8] = {};
+    cudaEvent_t copy_done[2] = {};
+    cudaEvent_t chunk_free[2] = {};
+    uint64_t* pinned = nullptr;       // 64 x u64 words of pinned host memory
+    int* d_error = nullptr;           // device-side self-check word
+    bool profiling = false;
+    int projection_path = 0;
+    culsh_stats stats{};
+    int sm_count = 148;
+    size_t smem_optin = 0;
+
+    ~Ctx() {
+        cudaSetDevice(device);
+        if (stream) cudaStreamSynchronize(stream);
+        for (auto& e : ev) if (e) cudaEventDestroy(e);
+        for (auto& e : copy_done) if (e) cudaEventDestroy(e);
+        for (auto& e : chunk_free) if (e) cudaEventDestroy(e);
+        if (pinned) cudaFreeHost(pinned);
+        if (d_error) cudaFree(d_error);
+        if (copy_stream) cudaStreamDestroy(copy_stream);
+        if (stream) cudaStreamDestroy(stream);
+    }
+};
+using CtxPtr = std::shared_ptr<Ctx>;
+
+// Stream-ordered device buffer (cudaMallocAsync on the context's stream; the pool keeps
+// freed blocks, so steady-state calls do not reach the driver allocator).
+template <typename T>
+struct DevBuf {
+    T* p = nullptr;
+    size_t n = 0;
+    CtxPtr ctx;
+    DevBuf() = default;
+    DevBuf(const CtxPtr& c, size_t count) { alloc(c, count); }
+    DevBuf(const DevBuf&) = delete;
+    DevBuf& operator=(const DevBuf&) = delete;
+    DevBuf(DevBuf&& o) noexcept : p(o.p), n(o.n), ctx(std::move(o.ctx)) { o.p = nullptr; o.n = 0; }
+    DevBuf& operator=(DevBuf&& o) noexcept {
+        if (this != &o) {
+            release();
+            p = o.p; n = o.n; ctx = std::move(o.ctx);
+            o.p = nullptr; o.n = 0;
+        }
+        return *this;
+    }
+    ~DevBuf() { release(); }
+    void alloc(const CtxPtr& c, size_t count) {
+        release();
+        ctx = c;
+        n = count;
+        if (count == 0) return;
+        void* q = nullptr;
+        cudaError_t e = cudaMallocAsync(&q, count * sizeof(T), c->stream);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            fail(CULSH_ERR_ALLOC, "device allocation of %zu bytes failed: %s", count * sizeof(T),
+                 cudaGetErrorString(e));
+        }
+        p = static_cast<T*>(q);
+    }
+    void release() {
+        if (p && ctx) {
+            int cur = -1;
+            cudaGetDevice(&cur);
+            if (cur != ctx->device) cudaSetDevice(ctx->device);
+            cudaFreeAsync(p, ctx->stream);
+            if (cur != ctx->device && cur >= 0) cudaSetDevice(cur);
+        }
+        p = nullptr;
+        n = 0;
+    }
+    size_t bytes() const { return n * sizeof(T); }
+};
+
+inline bool is_device_pointer(const void* p) {
+    if (!p) return false;
+    cudaPointerAttributes a{};
+    cudaError_t e = cudaPointerGetAttributes(&a, p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// Copy device -> (host | device) destination and wait.
+inline void copy_out(const CtxPtr& c, void* dst, const void* src_dev, size_t bytes) {
+    if (bytes == 0) return;
+    if (!dst) fail(CULSH_ERR_INVALID, "destination pointer is null");
+    CU_CHECK(cudaMemcpyAsync(dst, src_dev, bytes, cudaMemcpyDefault, c->stream));
+    CU_CHECK(cudaStreamSynchronize(c->stream));
+}
+
+// Read up to 64 u64 words from device memory through the pinned scratch block.
+inline void read_words(const CtxPtr& c, const void* src_dev, size_t bytes, void* host_out) {
+    if (bytes > 64 * sizeof(uint64_t)) fail(CULSH_ERR_INTERNAL, "read_words: too large");
+    CU_CHECK(cudaMemcpyAsync(c->pinned, src_dev, bytes, cudaMemcpyDeviceToHost, c->stream));
+    CU_CHECK(cudaStreamSynchronize(c->stream));
+    std::memcpy(host_out, c->pinned, bytes);
+}
+
+// Device-side self-check word: kernels OR a code into it instead of trapping.
+enum DeviceErrorBits : int {
+    DEV_ERR_LOOKBACK_TIMEOUT = 1,  // a bounded wait on another tile's status ran out
+    DEV_ERR_NARROW_OVERFLOW = 2,   // a p-stable hash value does not fit the narrow key width
+    DEV_ERR_MBAR_TIMEOUT = 4,      // a bounded mbarrier wait ran out (tensor-core projection)
+    DEV_ERR_RANGE = 8              // an index outside its array was skipped
+};
+
+}  // namespace culsh_b200

@@ -1,0 +1,1152 @@
+// Host orchestration and the C ABI of the engine (see include/culsh_b200.h).
+#include "common.cuh"
+#include "index_build.cuh"
+#include "minhash.cuh"
+#include "project_simt.cuh"
+#include "project_tc.cuh"
+#include "query.cuh"
+#include "radix_sort.cuh"
+
+#include <algorithm>
+#include <mutex>
+
+using namespace culsh_b200;
+
+// -----------------------------------------------------------------------------------------
+// Objects behind the opaque pointers
+// -----------------------------------------------------------------------------------------
+struct culsh_handle {
+    CtxPtr ctx;
+};
+
+struct culsh_index {
+    CtxPtr ctx;
+    KeySpec ks;
+    int family = 0, n = 0, d = 0, L = 0, k = 0, window = 0, is_double = 0;
+    uint64_t seed = 0;
+    int n_buckets = 0;
+    DevBuf<int32_t> cand;            // [n*L]   row ids grouped by (table, bucket)
+    DevBuf<uint32_t> bucket_keys;    // [B][NW] packed signatures, sorted inside a table
+    DevBuf<int32_t> bucket_offsets;  // [B+1]
+    DevBuf<int32_t> table_offsets;   // [L+1]
+    DevBuf<uint8_t> p0;              // projection (float/double [H][d]) | hash A (uint32 [H])
+    DevBuf<uint8_t> p1;              // bias (float/double [H])          | hash B (uint32 [H])
+    DevBuf<uint8_t> p_split;         // tensor-core path: hi/lo split of the projection
+};
+
+struct culsh_candidates {
+    CtxPtr ctx;
+    int n_queries = 0;
+    uint64_t total = 0;
+    DevBuf<int32_t> indices;
+    DevBuf<uint64_t> counts;
+    DevBuf<uint64_t> offsets;
+    bool empty() const { return !indices.p && !counts.p && !offsets.p; }
+};
+
+namespace {
+
+thread_local std::string g_last_error;
+
+template <typename F>
+int guarded(F&& f) {
+    try {
+        f();
+        return CULSH_OK;
+    } catch (const Error& e) {
+        g_last_error = e.what();
+        return e.status;
+    } catch (const std::bad_alloc&) {
+        g_last_error = "host allocation failed";
+        return CULSH_ERR_ALLOC;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+        return CULSH_ERR_INTERNAL;
+    }
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        CU_CHECK(cudaGetDevice(&prev));
+        if (prev != dev) CU_CHECK(cudaSetDevice(dev));
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+struct StageTimer {
+    const CtxPtr& c;
+    int next = 0;
+    explicit StageTimer(const CtxPtr& ctx) : c(ctx) {}
+    void mark() {
+        if (c->profiling && next < 8) cudaEventRecord(c->ev[next++], c->stream);
+    }
+    float between(int a, int b) const {
+        float ms = 0.f;
+        if (c->profiling && b < next) cudaEventElapsedTime(&ms, c->ev[a], c->ev[b]);
+        return ms;
+    }
+};
+
+void reset_error_word(const CtxPtr& c) {
+    CU_CHECK(cudaMemsetAsync(c->d_error, 0, sizeof(int), c->stream));
+}
+
+int read_error_word(const CtxPtr& c) {
+    int e = 0;
+    read_words(c, c->d_error, sizeof(int), &e);
+    return e;
+}
+
+void check_error_word(int e) {
+    if (e & DEV_ERR_LOOKBACK_TIMEOUT)
+        fail(CULSH_ERR_INTERNAL, "radix sort: a bounded wait on a preceding tile ran out");
+    if (e & DEV_ERR_MBAR_TIMEOUT)
+        fail(CULSH_ERR_INTERNAL, "projection: a bounded wait on a copy/MMA barrier ran out");
+    if (e & DEV_ERR_RANGE) fail(CULSH_ERR_INTERNAL, "a kernel skipped an out-of-range index");
+}
+
+// -----------------------------------------------------------------------------------------
+// Hash parameters.  Same cuRAND calls in the same order as upstream so that a seed means
+// the same hash functions: XORWOW (CURAND_RNG_PSEUDO_DEFAULT), default ordering,
+//   RPLSH   : GenerateNormal[Double](H*d)                      rplsh/hash.cuh:59-78
+//   PSLSH   : GenerateNormal[Double](H*d), GenerateUniform[Double](H), P /= int w
+//                                                               pslsh/hash.cuh:60-89
+//   MinHash : Generate(A,H), Generate(B,H), A%(p-1)+1, B%p      minhash/hash.cuh:26-54
+// -----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void scale_by_int_kernel(T* p, size_t n, int w) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = p[i] / w;  // T / int, as upstream's thrust placeholder expression
+}
+
+__global__ void minhash_normalize_kernel(uint32_t* A, uint32_t* B, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        A[i] = (A[i] % (MINHASH_PRIME - 1u)) + 1u;
+        B[i] = B[i] % MINHASH_PRIME;
+    }
+}
+
+struct CurandGen {
+    curandGenerator_t g = nullptr;
+    CurandGen(cudaStream_t s, uint64_t seed) {
+        CURAND_CHECK(curandCreateGenerator(&g, CURAND_RNG_PSEUDO_DEFAULT));
+        curandStatus_t st = curandSetStream(g, s);
+        if (st == CURAND_STATUS_SUCCESS) st = curandSetPseudoRandomGeneratorSeed(g, seed);
+        if (st != CURAND_STATUS_SUCCESS) {
+            curandDestroyGenerator(g);
+            fail(CULSH_ERR_CUDA, "cuRAND generator setup failed: status %d", (int)st);
+        }
+    }
+    ~CurandGen() {
+        if (g) curandDestroyGenerator(g);
+    }
+};
+
+void generate_params(culsh_index& ix) {
+    const CtxPtr& c = ix.ctx;
+    const int H = ix.L * ix.k;
+    CurandGen gen(c->stream, ix.seed);
+    if (ix.family == CULSH_MINHASH) {
+        ix.p0.alloc(c, sizeof(uint32_t) * H);
+        ix.p1.alloc(c, sizeof(uint32_t) * H);
+        CURAND_CHECK(curandGenerate(gen.g, reinterpret_cast<uint32_t*>(ix.p0.p), H));
+        CURAND_CHECK(curandGenerate(gen.g, reinterpret_cast<uint32_t*>(ix.p1.p), H));
+        minhash_normalize_kernel<<<(unsigned)ceil_div(H, 256), 256, 0, c->stream>>>(
+            reinterpret_cast<uint32_t*>(ix.p0.p), reinterpret_cast<uint32_t*>(ix.p1.p), H);
+        KERNEL_CHECK();
+        return;
+    }
+    const size_t pn = (size_t)H * ix.d;
+    if (pn % 2 != 0)
+        fail(CULSH_ERR_INVALID,
+             "n_hash_tables*n_hashes*n_features = %zu must be even (cuRAND normal generation)", pn);
+    const size_t esz = ix.is_double ? 8 : 4;
+    ix.p0.alloc(c, esz * pn);
+    if (ix.is_double)
+        CURAND_CHECK(curandGenerateNormalDouble(gen.g, reinterpret_cast<double*>(ix.p0.p), pn, 0.0, 1.0));
+    else
+        CURAND_CHECK(curandGenerateNormal(gen.g, reinterpret_cast<float*>(ix.p0.p), pn, 0.0f, 1.0f));
+    if (ix.family == CULSH_PSLSH) {
+        ix.p1.alloc(c, esz * H);
+        if (ix.is_double) {
+            CURAND_CHECK(curandGenerateUniformDouble(gen.g, reinterpret_cast<double*>(ix.p1.p), H));
+            scale_by_int_kernel<double><<<(unsigned)ceil_div(pn, 256), 256, 0, c->stream>>>(
+                reinterpret_cast<double*>(ix.p0.p), pn, ix.window);
+        } else {
+            CURAND_CHECK(curandGenerateUniform(gen.g, reinterpret_cast<float*>(ix.p1.p), H));
+            scale_by_int_kernel<float><<<(unsigned)ceil_div(pn, 256), 256, 0, c->stream>>>(
+                reinterpret_cast<float*>(ix.p0.p), pn, ix.window);
+        }
+        KERNEL_CHECK();
+    }
+    // the generator is destroyed at scope exit; its work is ordered on the stream
+    CU_CHECK(cudaStreamSynchronize(c->stream));
+}
+
+// -----------------------------------------------------------------------------------------
+// Hash stage drivers
+// -----------------------------------------------------------------------------------------
+// Hash dense rows (host or device memory) into keys[L][n_total][NW] at row_offset.
+template <typename T>
+void hash_dense(const culsh_index& ix, const KeySpec& ks, const T* X, int n, uint32_t* keys,
+                uint8_t* ovf_rows, int n_total, int row_offset) {
+    const CtxPtr& c = ix.ctx;
+    if (n == 0) return;
+    const T* P = reinterpret_cast<const T*>(ix.p0.p);
+    const T* bias = reinterpret_cast<const T*>(ix.p1.p);
+    auto launch = [&](cudaStream_t s, const T* Xd, int rows, int off) {
+        bool tc = false;
+        if (std::is_same<T, float>::value && c->projection_path != 1)
+            tc = launch_project_tc(c, s, ix.family, reinterpret_cast<const float*>(Xd),
+                                   reinterpret_cast<const float*>(P), ix.p_split.p,
+                                   reinterpret_cast<const float*>(bias), rows, ix.d, ix.L, ix.k, ks,
+                                   keys, ovf_rows, off, n_total);
+        if (!tc) {
+            if (c->projection_path == 2)
+                fail(CULSH_ERR_UNSUPPORTED, "tensor-core projection path is not available for this shape");
+            launch_project_simt<T>(c, s, ix.family, Xd, P, bias, rows, ix.d, ix.L, ix.k, ks, keys,
+                                   ovf_rows, off, n_total);
+        }
+        c->stats.hash_path = tc ? 1 : 0;
+    };
+    if (is_device_pointer(X)) {
+        launch(c->stream, X, n, row_offset);
+        return;
+    }
+    // Host input: stream it through two device staging buffers so the copy of chunk i+1
+    // overlaps the hashing of chunk i.
+    const size_t row_bytes = sizeof(T) * (size_t)ix.d;
+    size_t chunk_rows = std::max<size_t>(1024, (size_t)(32u << 20) / row_bytes);
+    chunk_rows = std::min<size_t>(chunk_rows, (size_t)n);
+    chunk_rows = (chunk_rows + 127) / 128 * 128;
+    DevBuf<uint8_t> stage[2];
+    stage[0].alloc(c, chunk_rows * row_bytes);
+    stage[1].alloc(c, chunk_rows * row_bytes);
+    // the staging buffers were allocated on the main stream: order the copy stream after it
+    CU_CHECK(cudaEventRecord(c->chunk_free[0], c->stream));
+    CU_CHECK(cudaEventRecord(c->chunk_free[1], c->stream));
+    int slot = 0;
+    for (size_t r0 = 0; r0 < (size_t)n; r0 += chunk_rows, slot ^= 1) {
+        const int rows = (int)std::min(chunk_rows, (size_t)n - r0);
+        CU_CHECK(cudaStreamWaitEvent(c->copy_stream, c->chunk_free[slot], 0));
+        CU_CHECK(cudaMemcpyAsync(stage[slot].p, reinterpret_cast<const uint8_t*>(X) + r0 * row_bytes,
+                                 rows * row_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+        CU_CHECK(cudaEventRecord(c->copy_done[slot], c->copy_stream));
+        CU_CHECK(cudaStreamWaitEvent(c->stream, c->copy_done[slot], 0));
+        launch(c->stream, reinterpret_cast<const T*>(stage[slot].p), rows, row_offset + (int)r0);
+        CU_CHECK(cudaEventRecord(c->chunk_free[slot], c->stream));
+    }
+}
+
+// CSR rows (host or device) -> keys.  indptr is rebased on the host side of a chunk, so
+// host inputs are copied whole (indices + indptr) before hashing.
+void hash_csr(const culsh_index& ix, const KeySpec& ks, const int32_t* indices, const int32_t* indptr,
+              int n, uint32_t* keys, int n_total, int row_offset) {
+    const CtxPtr& c = ix.ctx;
+    if (n == 0) return;
+    DevBuf<int32_t> d_indptr, d_indices;
+    const int32_t* ip = indptr;
+    const int32_t* ii = indices;
+    if (!is_device_pointer(indptr)) {
+        d_indptr.alloc(c, (size_t)n + 1);
+        CU_CHECK(cudaMemcpyAsync(d_indptr.p, indptr, sizeof(int32_t) * ((size_t)n + 1),
+                                 cudaMemcpyHostToDevice, c->stream));
+        ip = d_indptr.p;
+    }
+    if (!is_device_pointer(indices)) {
+        int32_t nnz = 0;
+        if (is_device_pointer(indptr)) read_words(c, indptr + n, sizeof(int32_t), &nnz);
+        else nnz = indptr[n];
+        if (nnz < 0) fail(CULSH_ERR_INVALID, "indptr[n] is negative");
+        if (nnz > 0 && !indices) fail(CULSH_ERR_INVALID, "indices is null");
+        d_indices.alloc(c, (size_t)nnz);
+        if (nnz)
+            CU_CHECK(cudaMemcpyAsync(d_indices.p, indices, sizeof(int32_t) * (size_t)nnz,
+                                     cudaMemcpyHostToDevice, c->stream));
+        ii = d_indices.p;
+    }
+    launch_minhash(c, c->stream, ii, ip, reinterpret_cast<const uint32_t*>(ix.p0.p),
+                   reinterpret_cast<const uint32_t*>(ix.p1.p), n, ix.L, ix.k, ks, keys, n_total,
+                   row_offset);
+    // staging buffers are released in stream order after the kernel
+}
+
+// -----------------------------------------------------------------------------------------
+// Index build from hashed keys
+// -----------------------------------------------------------------------------------------
+struct SortBuffers {
+    DevBuf<uint32_t> keys[2];
+    DevBuf<uint32_t> vals[2];
+    DevBuf<uint32_t> ghist, status, counter;
+    void alloc(const CtxPtr& c, size_t items, const KeySpec& ks, int n, int L) {
+        keys[0].alloc(c, items * ks.key_words);
+        keys[1].alloc(c, items * ks.key_words);
+        vals[0].alloc(c, items);
+        vals[1].alloc(c, items);
+        ghist.alloc(c, (size_t)L * ks.key_bytes * 256);
+        status.alloc(c, radix_sort_status_words(n, L, ks.key_words));
+        counter.alloc(c, 1);
+    }
+};
+
+// Sort + bucket construction.  On return ix holds cand/bucket arrays; if want_i2b the
+// (row, table) -> bucket map is filled.  Returns the device error word read at the one
+// host synchronisation of the build.
+int build_index(culsh_index& ix, SortBuffers& sb, DevBuf<int32_t>* item_to_bucket, StageTimer& tm) {
+    const CtxPtr& c = ix.ctx;
+    const int n = ix.n, L = ix.L, NW = ix.ks.key_words;
+    uint32_t* kp[2] = {sb.keys[0].p, sb.keys[1].p};
+    uint32_t* vp[2] = {sb.vals[0].p, sb.vals[1].p};
+    int cur = radix_sort_tables(c, NW, kp, vp, n, L, ix.ks.key_bytes, sb.ghist.p, sb.status.p,
+                                sb.counter.p);
+    tm.mark();
+    const int tpt = (int)ceil_div(n, IB_TILE);
+    const size_t n_tiles = (size_t)tpt * L;
+    DevBuf<uint32_t> tile_heads(c, n_tiles), tile_base(c, n_tiles + 1),
+        scratch(c, scan_scratch_elems(n_tiles));
+    CULSH_DISPATCH_NW(NW, launch_bucket_count<NW>(c->stream, kp[cur], n, L, tile_heads.p));
+    exclusive_scan<uint32_t, uint32_t>(c->stream, tile_heads.p, n_tiles, tile_base.p, scratch.p);
+    // the one host round trip of the build: bucket total + self-check word
+    uint32_t B = 0;
+    int err = 0;
+    CU_CHECK(cudaMemcpyAsync(c->pinned, tile_base.p + n_tiles, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
+    CU_CHECK(cudaMemcpyAsync(c->pinned + 1, c->d_error, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    CU_CHECK(cudaStreamSynchronize(c->stream));
+    std::memcpy(&B, c->pinned, sizeof(uint32_t));
+    std::memcpy(&err, c->pinned + 1, sizeof(int));
+    if (err) return err;
+    ix.n_buckets = (int)B;
+    ix.bucket_keys.alloc(c, (size_t)B * NW);
+    ix.bucket_offsets.alloc(c, (size_t)B + 1);
+    ix.table_offsets.alloc(c, (size_t)L + 1);
+    if (item_to_bucket) item_to_bucket->alloc(c, (size_t)n * L);
+    CULSH_DISPATCH_NW(NW, launch_bucket_write<NW>(c->stream, kp[cur], vp[cur], n, L, tile_base.p,
+                                                  ix.bucket_keys.p, ix.bucket_offsets.p,
+                                                  ix.table_offsets.p,
+                                                  item_to_bucket ? item_to_bucket->p : nullptr));
+    // the sorted row ids are the candidate array: adopt the buffer
+    static_assert(sizeof(int32_t) == sizeof(uint32_t), "");
+    DevBuf<uint32_t>& v = sb.vals[cur];
+    ix.cand.p = reinterpret_cast<int32_t*>(v.p);
+    ix.cand.n = v.n;
+    ix.cand.ctx = v.ctx;
+    v.p = nullptr;
+    v.n = 0;
+    tm.mark();
+    c->stats.n_items = (uint64_t)n * L;
+    c->stats.n_buckets = B;
+    c->stats.sort_passes = ix.ks.key_bytes;
+    c->stats.key_words = NW;
+    c->stats.elem_bytes = ix.ks.elem_bytes;
+    return 0;
+}
+
+void validate_shape(int n, int d, int L, int k) {
+    if (n <= 0) fail(CULSH_ERR_INVALID, "n_samples must be positive");
+    if (d <= 0) fail(CULSH_ERR_INVALID, "n_features must be positive");
+    if (L <= 0) fail(CULSH_ERR_INVALID, "n_hash_tables must be positive");
+    if (k <= 0) fail(CULSH_ERR_INVALID, "n_hashes must be positive");
+    if ((uint64_t)n * (uint64_t)L >= (1ull << 31))
+        fail(CULSH_ERR_UNSUPPORTED, "n_samples * n_hash_tables must be below 2^31");
+    if (n >= (1 << 30)) fail(CULSH_ERR_UNSUPPORTED, "n_samples must be below 2^30");
+}
+
+// Hash + sort + build.  `hash_fn(ks, keys)` fills the key array for a given key layout.
+template <typename HashFn>
+void fit_common(culsh_index& ix, HashFn&& hash_fn, DevBuf<int32_t>* item_to_bucket) {
+    const CtxPtr& c = ix.ctx;
+    c->stats = culsh_stats{};
+    int eb = ix.family == CULSH_PSLSH ? 1 : (ix.family == CULSH_MINHASH ? 4 : 0);
+    const size_t items = (size_t)ix.n * ix.L;
+    while (true) {
+        ix.ks = make_key_spec(ix.family, ix.k, eb);
+        if (ix.ks.key_words < 0)
+            fail(CULSH_ERR_UNSUPPORTED, "signature of %d hashes x %d bytes exceeds the 64-byte key limit",
+                 ix.k, std::max(1, eb));
+        StageTimer tm(c);
+        SortBuffers sb;
+        sb.alloc(c, items, ix.ks, ix.n, ix.L);
+        reset_error_word(c);
+        tm.mark();
+        hash_fn(ix.ks, sb.keys[0].p);
+        tm.mark();
+        int err = build_index(ix, sb, item_to_bucket, tm);
+        if (err & DEV_ERR_NARROW_OVERFLOW) {  // p-stable values do not fit: widen and redo
+            if (eb >= 4) fail(CULSH_ERR_INTERNAL, "overflow reported at full width");
+            eb *= 2;
+            continue;
+        }
+        check_error_word(err);
+        c->stats.hash_ms = tm.between(0, 1);
+        c->stats.sort_ms = tm.between(1, 2);
+        c->stats.build_ms = tm.between(2, 3);
+        c->stats.total_ms = tm.between(0, 3);
+        break;
+    }
+}
+
+// -----------------------------------------------------------------------------------------
+// Query from matched bucket ids (matched[q*L + t])
+// -----------------------------------------------------------------------------------------
+int bitmap_window_bits(const CtxPtr& c, int n_rows) {
+    size_t fixed = 3 * BM_MAX_L * sizeof(int) + 1024;
+    size_t max_bits = ((c->smem_optin > fixed ? c->smem_optin - fixed : 0) * 8) / 1024 * 1024;
+    size_t want = ((size_t)n_rows + 1023) / 1024 * 1024;
+    size_t cap = std::min<size_t>(max_bits, (size_t)1 << 20);
+    return (int)std::min(want, cap);
+}
+
+void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, culsh_candidates& out,
+                        StageTimer& tm) {
+    const CtxPtr& c = ix.ctx;
+    cudaStream_t s = c->stream;
+    const int L = ix.L;
+    out.ctx = c;
+    out.n_queries = n_q;
+    out.counts.alloc(c, (size_t)n_q);
+    out.offsets.alloc(c, (size_t)n_q + 1);
+    DevBuf<uint64_t> raw_cnt(c, n_q), raw_off(c, (size_t)n_q + 1), scratch(c, scan_scratch_elems(n_q));
+    DevBuf<uint32_t> big_list(c, n_q), n_big(c, 1);
+    CU_CHECK(cudaMemsetAsync(n_big.p, 0, sizeof(uint32_t), s));
+    raw_count_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(matched, ix.bucket_offsets.p, n_q, L,
+                                                                 raw_cnt.p, big_list.p, n_big.p);
+    KERNEL_CHECK();
+    exclusive_scan<uint64_t, uint64_t>(s, raw_cnt.p, n_q, raw_off.p, scratch.p);
+    uint64_t raw_total = 0;
+    uint32_t nb = 0;
+    CU_CHECK(cudaMemcpyAsync(c->pinned, raw_off.p + n_q, sizeof(uint64_t), cudaMemcpyDeviceToHost, s));
+    CU_CHECK(cudaMemcpyAsync(c->pinned + 1, n_big.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    CU_CHECK(cudaStreamSynchronize(s));
+    std::memcpy(&raw_total, c->pinned, sizeof(uint64_t));
+    std::memcpy(&nb, c->pinned + 1, sizeof(uint32_t));
+    c->stats.raw_candidates += raw_total;
+    if (raw_total == 0) {
+        CU_CHECK(cudaMemsetAsync(out.counts.p, 0, out.counts.bytes(), s));
+        CU_CHECK(cudaMemsetAsync(out.offsets.p, 0, out.offsets.bytes(), s));
+        out.total = 0;
+        CU_CHECK(cudaStreamSynchronize(s));
+        return;
+    }
+    DevBuf<int32_t> tmp(c, raw_total);
+    {
+        size_t blocks = std::min<size_t>(ceil_div(n_q, SM_WARPS), (size_t)c->sm_count * 16);
+        dedupe_small_kernel<<<(unsigned)blocks, SM_THREADS, 0, s>>>(
+            matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, raw_off.p, n_q, L, tmp.p, out.counts.p);
+        KERNEL_CHECK();
+    }
+    if (nb) {
+        int wbits = bitmap_window_bits(c, ix.n);
+        size_t smem = (size_t)wbits / 8 + 3 * BM_MAX_L * sizeof(int);
+        CU_CHECK(cudaFuncSetAttribute(dedupe_bitmap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dedupe_bitmap_kernel<<<nb, BM_THREADS, smem, s>>>(big_list.p, matched, ix.bucket_offsets.p,
+                                                          ix.cand.p, raw_off.p, L, ix.n, wbits, tmp.p,
+                                                          out.counts.p);
+        KERNEL_CHECK();
+    }
+    exclusive_scan<uint64_t, uint64_t>(s, out.counts.p, n_q, out.offsets.p, scratch.p);
+    uint64_t total = 0;
+    read_words(c, out.offsets.p + n_q, sizeof(uint64_t), &total);
+    out.total = total;
+    c->stats.unique_candidates += total;
+    if (total) {
+        out.indices.alloc(c, total);
+        size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
+        compact_small_kernel<<<(unsigned)blocks, 256, 0, s>>>(tmp.p, raw_cnt.p, raw_off.p, out.counts.p,
+                                                             out.offsets.p, n_q, out.indices.p);
+        KERNEL_CHECK();
+        if (nb) {
+            compact_big_kernel<<<nb, 256, 0, s>>>(big_list.p, tmp.p, raw_off.p, out.counts.p,
+                                                  out.offsets.p, out.indices.p);
+            KERNEL_CHECK();
+        }
+    }
+    tm.mark();
+    CU_CHECK(cudaStreamSynchronize(s));
+}
+
+// Hash a batch of queries, look the buckets up, gather + dedupe.
+template <typename HashFn>
+void query_batch(const culsh_index& ix, int n_q, HashFn&& hash_fn, culsh_candidates& out) {
+    const CtxPtr& c = ix.ctx;
+    const int NW = ix.ks.key_words;
+    StageTimer tm(c);
+    const size_t pairs = (size_t)n_q * ix.L;
+    DevBuf<uint32_t> qkeys(c, pairs * NW);
+    DevBuf<uint8_t> ovf;
+    if (ix.family == CULSH_PSLSH && ix.ks.elem_bytes < 4) ovf.alloc(c, pairs);
+    DevBuf<int32_t> matched(c, pairs);
+    tm.mark();
+    hash_fn(ix.ks, qkeys.p, ovf.p);
+    tm.mark();
+    CULSH_DISPATCH_NW(NW, (lookup_kernel<NW><<<(unsigned)ceil_div(pairs, 256), 256, 0, c->stream>>>(
+                              qkeys.p, ovf.p, n_q, ix.L, ix.bucket_keys.p, ix.table_offsets.p, matched.p)));
+    KERNEL_CHECK();
+    tm.mark();
+    query_from_matched(ix, matched.p, n_q, out, tm);
+    c->stats.hash_ms += tm.between(0, 1);
+    c->stats.lookup_ms += tm.between(1, 2);
+    c->stats.gather_ms += tm.between(2, 3);
+    c->stats.total_ms += tm.between(0, 3);
+}
+
+// Concatenate batch results (linear, once): replaces the per-batch Candidates::merge of
+// core/candidates.cuh:139-197.
+void concat_candidates(const CtxPtr& c, std::vector<std::unique_ptr<culsh_candidates>>& parts,
+                       culsh_candidates& out) {
+    int nq = 0;
+    uint64_t total = 0;
+    for (auto& p : parts) { nq += p->n_queries; total += p->total; }
+    out.ctx = c;
+    out.n_queries = nq;
+    out.total = total;
+    out.counts.alloc(c, nq);
+    out.offsets.alloc(c, (size_t)nq + 1);
+    if (total) out.indices.alloc(c, total);
+    int q0 = 0;
+    uint64_t base = 0;
+    for (auto& p : parts) {
+        if (p->n_queries == 0) continue;
+        CU_CHECK(cudaMemcpyAsync(out.counts.p + q0, p->counts.p, sizeof(uint64_t) * p->n_queries,
+                                 cudaMemcpyDeviceToDevice, c->stream));
+        size_t m = (size_t)p->n_queries + 1;
+        shift_offsets_kernel<<<(unsigned)ceil_div(m, 256), 256, 0, c->stream>>>(p->offsets.p, m, base,
+                                                                              out.offsets.p + q0);
+        KERNEL_CHECK();
+        if (p->total)
+            CU_CHECK(cudaMemcpyAsync(out.indices.p + base, p->indices.p, sizeof(int32_t) * p->total,
+                                     cudaMemcpyDeviceToDevice, c->stream));
+        q0 += p->n_queries;
+        base += p->total;
+    }
+    CU_CHECK(cudaStreamSynchronize(c->stream));
+}
+
+void empty_result(const CtxPtr& c, culsh_candidates& out) {
+    out.ctx = c;
+    out.n_queries = 0;
+    out.total = 0;
+    out.counts.alloc(c, 1);  // non-null so the object is not "empty" in upstream's sense
+    out.offsets.alloc(c, 1);
+    CU_CHECK(cudaMemsetAsync(out.offsets.p, 0, sizeof(uint64_t), c->stream));
+    CU_CHECK(cudaStreamSynchronize(c->stream));
+}
+
+// -----------------------------------------------------------------------------------------
+// Family front ends
+// -----------------------------------------------------------------------------------------
+void prepare_tc_split(culsh_index& ix) {
+    if (ix.family == CULSH_MINHASH || ix.is_double) return;
+    prepare_project_tc(ix.ctx, reinterpret_cast<const float*>(ix.p0.p), ix.L * ix.k, ix.d, ix.p_split);
+}
+
+template <typename T>
+std::unique_ptr<culsh_index> new_dense_index(culsh_handle* h, int family, int n, int d, int L, int k,
+                                             int window, uint64_t seed) {
+    validate_shape(n, d, L, k);
+    if (family == CULSH_PSLSH && window <= 0) fail(CULSH_ERR_INVALID, "window_size must be positive");
+    auto ix = std::make_unique<culsh_index>();
+    ix->ctx = h->ctx;
+    ix->family = family;
+    ix->n = n; ix->d = d; ix->L = L; ix->k = k;
+    ix->window = family == CULSH_PSLSH ? window : 0;
+    ix->is_double = std::is_same<T, double>::value ? 1 : 0;
+    ix->seed = seed;
+    generate_params(*ix);
+    prepare_tc_split(*ix);
+    return ix;
+}
+
+template <typename T>
+void fit_dense(culsh_handle* h, int family, const T* X, int n, int d, int L, int k, int window,
+               uint64_t seed, culsh_index** out) {
+    if (!h || !out) fail(CULSH_ERR_INVALID, "null handle or output pointer");
+    if (!X) fail(CULSH_ERR_INVALID, "X is null");
+    DeviceGuard g(h->ctx->device);
+    auto ix = new_dense_index<T>(h, family, n, d, L, k, window, seed);
+    fit_common(*ix, [&](const KeySpec& ks, uint32_t* keys) {
+        hash_dense<T>(*ix, ks, X, n, keys, nullptr, n, 0);
+    }, nullptr);
+    CU_CHECK(cudaStreamSynchronize(h->ctx->stream));
+    *out = ix.release();
+}
+
+template <typename T>
+void fit_query_dense(culsh_handle* h, int family, const T* X, int n, int d, int L, int k, int window,
+                     uint64_t seed, culsh_candidates** out) {
+    if (!h || !out) fail(CULSH_ERR_INVALID, "null handle or output pointer");
+    if (!X) fail(CULSH_ERR_INVALID, "X is null");
+    DeviceGuard g(h->ctx->device);
+    auto ix = new_dense_index<T>(h, family, n, d, L, k, window, seed);
+    DevBuf<int32_t> i2b;
+    fit_common(*ix, [&](const KeySpec& ks, uint32_t* keys) {
+        hash_dense<T>(*ix, ks, X, n, keys, nullptr, n, 0);
+    }, &i2b);
+    auto res = std::make_unique<culsh_candidates>();
+    StageTimer tm(h->ctx);
+    tm.mark();
+    query_from_matched(*ix, i2b.p, n, *res, tm);
+    h->ctx->stats.gather_ms = tm.between(0, 1);
+    *out = res.release();
+}
+
+template <typename T>
+void query_dense(culsh_handle* h, int family, const T* Q, int n_q, const culsh_index* ix,
+                 int batch_size, culsh_candidates** out) {
+    if (!h || !out || !ix) fail(CULSH_ERR_INVALID, "null handle, index or output pointer");
+    if (ix->family != family) fail(CULSH_ERR_INVALID, "index belongs to another LSH family");
+    if (ix->ctx->device != h->ctx->device) fail(CULSH_ERR_INVALID, "index lives on another device");
+    const bool want_double = std::is_same<T, double>::value;
+    if (ix->is_double && !want_double)
+        fail(CULSH_ERR_INVALID, "Index was fitted with float64, but query is float32");
+    if (!ix->is_double && want_double)
+        fail(CULSH_ERR_INVALID, "Index was fitted with float32, but query is float64");
+    if (n_q < 0) fail(CULSH_ERR_INVALID, "n_queries must not be negative");
+    DeviceGuard g(h->ctx->device);
+    const CtxPtr& c = ix->ctx;
+    c->stats = culsh_stats{};
+    auto res = std::make_unique<culsh_candidates>();
+    if (n_q == 0) {
+        empty_result(c, *res);
+        *out = res.release();
+        return;
+    }
+    if (!Q) fail(CULSH_ERR_INVALID, "Q is null");
+    if ((uint64_t)n_q * ix->L >= (1ull << 31) && (batch_size <= 0 || batch_size >= n_q))
+        fail(CULSH_ERR_UNSUPPORTED, "n_queries * n_hash_tables must be below 2^31 per batch");
+    reset_error_word(c);
+    auto run = [&](const T* Qb, int nb, culsh_candidates& dst) {
+        query_batch(*ix, nb, [&](const KeySpec& ks, uint32_t* keys, uint8_t* ovf) {
+            hash_dense<T>(*ix, ks, Qb, nb, keys, ovf, nb, 0);
+        }, dst);
+    };
+    if (batch_size <= 0 || batch_size >= n_q) {  // rplsh.cu:190-192
+        run(Q, n_q, *res);
+    } else {
+        std::vector<std::unique_ptr<culsh_candidates>> parts;
+        for (int s0 = 0; s0 < n_q; s0 += batch_size) {
+            int nb = std::min(batch_size, n_q - s0);
+            parts.emplace_back(new culsh_candidates());
+            run(Q + (size_t)s0 * ix->d, nb, *parts.back());
+        }
+        concat_candidates(c, parts, *res);
+    }
+    check_error_word(read_error_word(c));
+    *out = res.release();
+}
+
+std::unique_ptr<culsh_index> new_minhash_index(culsh_handle* h, int n, int d, int L, int k, uint64_t seed) {
+    validate_shape(n, std::max(d, 1), L, k);
+    auto ix = std::make_unique<culsh_index>();
+    ix->ctx = h->ctx;
+    ix->family = CULSH_MINHASH;
+    ix->n = n; ix->d = d; ix->L = L; ix->k = k;
+    ix->seed = seed;
+    generate_params(*ix);
+    return ix;
+}
+
+size_t copy_bytes_or_zero(size_t n, size_t esz) { return n * esz; }
+
+}  // namespace
+
+// =========================================================================================
+// C ABI
+// =========================================================================================
+extern "C" {
+
+const char* culsh_last_error(void) { return g_last_error.c_str(); }
+
+int culsh_create(int device, culsh_handle** out) {
+    return guarded([&] {
+        if (!out) fail(CULSH_ERR_INVALID, "out is null");
+        int count = 0;
+        CU_CHECK(cudaGetDeviceCount(&count));
+        if (device < 0 || device >= count) fail(CULSH_ERR_INVALID, "no CUDA device %d (have %d)", device, count);
+        DeviceGuard g(device);
+        auto c = std::make_shared<Ctx>();
+        c->device = device;
+        CU_CHECK(cudaStreamCreate(&c->stream));  // blocking stream, as upstream (cuda_utils.cuh:38)
+        CU_CHECK(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+        for (auto& e : c->ev) CU_CHECK(cudaEventCreate(&e));
+        for (auto& e : c->copy_done) CU_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        for (auto& e : c->chunk_free) CU_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        CU_CHECK(cudaMallocHost(&c->pinned, 64 * sizeof(uint64_t)));
+        CU_CHECK(cudaMalloc(&c->d_error, sizeof(int)));
+        CU_CHECK(cudaMemset(c->d_error, 0, sizeof(int)));
+        cudaDeviceProp prop{};
+        CU_CHECK(cudaGetDeviceProperties(&prop, device));
+        c->sm_count = prop.multiProcessorCount;
+        c->smem_optin = prop.sharedMemPerBlockOptin;
+        // keep freed blocks in the stream-ordered pool instead of returning them to the driver
+        cudaMemPool_t pool;
+        CU_CHECK(cudaDeviceGetDefaultMemPool(&pool, device));
+        uint64_t thresh = UINT64_MAX;
+        CU_CHECK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thresh));
+        auto h = new culsh_handle();
+        h->ctx = c;
+        *out = h;
+    });
+}
+
+int culsh_destroy(culsh_handle* h) {
+    return guarded([&] { delete h; });
+}
+
+int culsh_get_stats(const culsh_handle* h, culsh_stats* out) {
+    return guarded([&] {
+        if (!h || !out) fail(CULSH_ERR_INVALID, "null argument");
+        *out = h->ctx->stats;
+    });
+}
+
+int culsh_set_profiling(culsh_handle* h, int enabled) {
+    return guarded([&] {
+        if (!h) fail(CULSH_ERR_INVALID, "null handle");
+        h->ctx->profiling = enabled != 0;
+    });
+}
+
+int culsh_set_projection_path(culsh_handle* h, int path) {
+    return guarded([&] {
+        if (!h) fail(CULSH_ERR_INVALID, "null handle");
+        if (path < 0 || path > 2) fail(CULSH_ERR_INVALID, "path must be 0, 1 or 2");
+        h->ctx->projection_path = path;
+    });
+}
+
+// ---- RPLSH ------------------------------------------------------------------------------
+int culsh_rplsh_fit_f32(culsh_handle* h, const float* X, int n, int d, int L, int k, uint64_t seed,
+                        culsh_index** out) {
+    return guarded([&] { fit_dense<float>(h, CULSH_RPLSH, X, n, d, L, k, 0, seed, out); });
+}
+int culsh_rplsh_fit_f64(culsh_handle* h, const double* X, int n, int d, int L, int k, uint64_t seed,
+                        culsh_index** out) {
+    return guarded([&] { fit_dense<double>(h, CULSH_RPLSH, X, n, d, L, k, 0, seed, out); });
+}
+int culsh_rplsh_query_f32(culsh_handle* h, const float* Q, int n_q, const culsh_index* ix, int batch,
+                          culsh_candidates** out) {
+    return guarded([&] { query_dense<float>(h, CULSH_RPLSH, Q, n_q, ix, batch, out); });
+}
+int culsh_rplsh_query_f64(culsh_handle* h, const double* Q, int n_q, const culsh_index* ix, int batch,
+                          culsh_candidates** out) {
+    return guarded([&] { query_dense<double>(h, CULSH_RPLSH, Q, n_q, ix, batch, out); });
+}
+int culsh_rplsh_fit_query_f32(culsh_handle* h, const float* X, int n, int d, int L, int k,
+                              uint64_t seed, culsh_candidates** out) {
+    return guarded([&] { fit_query_dense<float>(h, CULSH_RPLSH, X, n, d, L, k, 0, seed, out); });
+}
+int culsh_rplsh_fit_query_f64(culsh_handle* h, const double* X, int n, int d, int L, int k,
+                              uint64_t seed, culsh_candidates** out) {
+    return guarded([&] { fit_query_dense<double>(h, CULSH_RPLSH, X, n, d, L, k, 0, seed, out); });
+}
+
+// ---- PSLSH ------------------------------------------------------------------------------
+int culsh_pslsh_fit_f32(culsh_handle* h, const float* X, int n, int d, int L, int k, int w,
+                        uint64_t seed, culsh_index** out) {
+    return guarded([&] { fit_dense<float>(h, CULSH_PSLSH, X, n, d, L, k, w, seed, out); });
+}
+int culsh_pslsh_fit_f64(culsh_handle* h, const double* X, int n, int d, int L, int k, int w,
+                        uint64_t seed, culsh_index** out) {
+    return guarded([&] { fit_dense<double>(h, CULSH_PSLSH, X, n, d, L, k, w, seed, out); });
+}
+int culsh_pslsh_query_f32(culsh_handle* h, const float* Q, int n_q, const culsh_index* ix, int batch,
+                          culsh_candidates** out) {
+    return guarded([&] { query_dense<float>(h, CULSH_PSLSH, Q, n_q, ix, batch, out); });
+}
+int culsh_pslsh_query_f64(culsh_handle* h, const double* Q, int n_q, const culsh_index* ix, int batch,
+                          culsh_candidates** out) {
+    return guarded([&] { query_dense<double>(h, CULSH_PSLSH, Q, n_q, ix, batch, out); });
+}
+int culsh_pslsh_fit_query_f32(culsh_handle* h, const float* X, int n, int d, int L, int k, int w,
+                              uint64_t seed, culsh_candidates** out) {
+    return guarded([&] { fit_query_dense<float>(h, CULSH_PSLSH, X, n, d, L, k, w, seed, out); });
+}
+int culsh_pslsh_fit_query_f64(culsh_handle* h, const double* X, int n, int d, int L, int k, int w,
+                              uint64_t seed, culsh_candidates** out) {
+    return guarded([&] { fit_query_dense<double>(h, CULSH_PSLSH, X, n, d, L, k, w, seed, out); });
+}
+
+// ---- MinHash ----------------------------------------------------------------------------
+int culsh_minhash_fit(culsh_handle* h, const int32_t* indices, const int32_t* indptr, int n, int d,
+                      int L, int k, uint64_t seed, culsh_index** out) {
+    return guarded([&] {
+        if (!h || !out) fail(CULSH_ERR_INVALID, "null handle or output pointer");
+        if (!indptr) fail(CULSH_ERR_INVALID, "indptr is null");
+        DeviceGuard g(h->ctx->device);
+        auto ix = new_minhash_index(h, n, d, L, k, seed);
+        fit_common(*ix, [&](const KeySpec& ks, uint32_t* keys) {
+            hash_csr(*ix, ks, indices, indptr, n, keys, n, 0);
+        }, nullptr);
+        CU_CHECK(cudaStreamSynchronize(h->ctx->stream));
+        *out = ix.release();
+    });
+}
+
+int culsh_minhash_query(culsh_handle* h, const int32_t* indices, const int32_t* indptr, int n_q,
+                        const culsh_index* ix, culsh_candidates** out) {
+    return guarded([&] {
+        if (!h || !out || !ix) fail(CULSH_ERR_INVALID, "null handle, index or output pointer");
+        if (ix->family != CULSH_MINHASH) fail(CULSH_ERR_INVALID, "index belongs to another LSH family");
+        if (n_q < 0) fail(CULSH_ERR_INVALID, "n_queries must not be negative");
+        DeviceGuard g(h->ctx->device);
+        const CtxPtr& c = ix->ctx;
+        c->stats = culsh_stats{};
+        auto res = std::make_unique<culsh_candidates>();
+        if (n_q == 0) {
+            empty_result(c, *res);
+            *out = res.release();
+            return;
+        }
+        if (!indptr) fail(CULSH_ERR_INVALID, "indptr is null");
+        if ((uint64_t)n_q * ix->L >= (1ull << 31))
+            fail(CULSH_ERR_UNSUPPORTED, "n_queries * n_hash_tables must be below 2^31");
+        reset_error_word(c);
+        query_batch(*ix, n_q, [&](const KeySpec& ks, uint32_t* keys, uint8_t*) {
+            hash_csr(*ix, ks, indices, indptr, n_q, keys, n_q, 0);
+        }, *res);
+        check_error_word(read_error_word(c));
+        *out = res.release();
+    });
+}
+
+int culsh_minhash_fit_query(culsh_handle* h, const int32_t* indices, const int32_t* indptr, int n,
+                            int d, int L, int k, uint64_t seed, culsh_candidates** out) {
+    return guarded([&] {
+        if (!h || !out) fail(CULSH_ERR_INVALID, "null handle or output pointer");
+        if (!indptr) fail(CULSH_ERR_INVALID, "indptr is null");
+        DeviceGuard g(h->ctx->device);
+        auto ix = new_minhash_index(h, n, d, L, k, seed);
+        DevBuf<int32_t> i2b;
+        fit_common(*ix, [&](const KeySpec& ks, uint32_t* keys) {
+            hash_csr(*ix, ks, indices, indptr, n, keys, n, 0);
+        }, &i2b);
+        auto res = std::make_unique<culsh_candidates>();
+        StageTimer tm(h->ctx);
+        tm.mark();
+        query_from_matched(*ix, i2b.p, n, *res, tm);
+        h->ctx->stats.gather_ms = tm.between(0, 1);
+        *out = res.release();
+    });
+}
+
+// ---- signatures only --------------------------------------------------------------------
+static void unpack_and_copy(const CtxPtr& c, const uint32_t* keys, size_t count, const KeySpec& ks,
+                            void* dst) {
+    DevBuf<uint8_t> raw(c, count * ks.sig_nbytes);
+    unpack_keys_kernel<<<(unsigned)ceil_div(count, 256), 256, 0, c->stream>>>(
+        keys, count, ks.family, ks.n_hashes, ks.key_words, ks.elem_bytes, raw.p);
+    KERNEL_CHECK();
+    copy_out(c, dst, raw.p, raw.bytes());
+}
+
+int culsh_index_hash_dense(culsh_handle* h, const culsh_index* ix, const void* X, int n_rows,
+                           void* sig_out) {
+    return guarded([&] {
+        if (!h || !ix || !X || !sig_out) fail(CULSH_ERR_INVALID, "null argument");
+        if (ix->family == CULSH_MINHASH) fail(CULSH_ERR_INVALID, "use culsh_index_hash_csr for MinHash");
+        if (n_rows <= 0) fail(CULSH_ERR_INVALID, "n_rows must be positive");
+        DeviceGuard g(h->ctx->device);
+        const CtxPtr& c = ix->ctx;
+        KeySpec ks = make_key_spec(ix->family, ix->k, 4);  // full-width elements: nothing saturates
+        if (ks.key_words < 0) fail(CULSH_ERR_UNSUPPORTED, "signature wider than 64 bytes");
+        size_t items = (size_t)n_rows * ix->L;
+        DevBuf<uint32_t> keys(c, items * ks.key_words);
+        if (ix->is_double)
+            hash_dense<double>(*ix, ks, static_cast<const double*>(X), n_rows, keys.p, nullptr, n_rows, 0);
+        else
+            hash_dense<float>(*ix, ks, static_cast<const float*>(X), n_rows, keys.p, nullptr, n_rows, 0);
+        unpack_and_copy(c, keys.p, items, ks, sig_out);
+    });
+}
+
+int culsh_index_hash_csr(culsh_handle* h, const culsh_index* ix, const int32_t* indices,
+                         const int32_t* indptr, int n_rows, void* sig_out) {
+    return guarded([&] {
+        if (!h || !ix || !indptr || !sig_out) fail(CULSH_ERR_INVALID, "null argument");
+        if (ix->family != CULSH_MINHASH) fail(CULSH_ERR_INVALID, "index is not a MinHash index");
+        if (n_rows <= 0) fail(CULSH_ERR_INVALID, "n_rows must be positive");
+        DeviceGuard g(h->ctx->device);
+        const CtxPtr& c = ix->ctx;
+        size_t items = (size_t)n_rows * ix->L;
+        DevBuf<uint32_t> keys(c, items * ix->ks.key_words);
+        hash_csr(*ix, ix->ks, indices, indptr, n_rows, keys.p, n_rows, 0);
+        unpack_and_copy(c, keys.p, items, ix->ks, sig_out);
+    });
+}
+
+// ---- Index getters / loaders ------------------------------------------------------------
+int culsh_index_get_meta(const culsh_index* ix, culsh_index_meta* m) {
+    return guarded([&] {
+        if (!ix || !m) fail(CULSH_ERR_INVALID, "null argument");
+        std::memset(m, 0, sizeof(*m));
+        m->family = ix->family;
+        m->n_total_candidates = (int32_t)((size_t)ix->n * ix->L);
+        m->n_total_buckets = ix->n_buckets;
+        m->n_hash_tables = ix->L;
+        m->n_hashes = ix->k;
+        m->sig_nbytes = ix->ks.sig_nbytes;
+        m->n_features = ix->d;
+        m->is_double = ix->is_double;
+        m->window_size = ix->window;
+        m->n_samples = ix->n;
+        m->key_words = ix->ks.key_words;
+        m->elem_bytes = ix->ks.elem_bytes;
+        m->seed = ix->seed;
+        // core/index.cuh:148-165 plus the family parameters (rplsh/index.cuh, pslsh/index.cuh,
+        // minhash/index.cuh size_bytes), in upstream's layout
+        uint64_t sz = ((uint64_t)ix->n_buckets + 1) * 4 + ((uint64_t)ix->L + 1) * 4 +
+                      (uint64_t)ix->n_buckets * ix->ks.sig_nbytes + (uint64_t)ix->n * ix->L * 4;
+        sz += ix->p0.bytes() + ix->p1.bytes();
+        m->size_bytes = sz;
+    });
+}
+
+int culsh_index_get_candidate_indices(const culsh_index* ix, int32_t* dst) {
+    return guarded([&] {
+        if (!ix) fail(CULSH_ERR_INVALID, "null index");
+        DeviceGuard g(ix->ctx->device);
+        copy_out(ix->ctx, dst, ix->cand.p, ix->cand.bytes());
+    });
+}
+int culsh_index_get_bucket_signatures(const culsh_index* ix, uint8_t* dst) {
+    return guarded([&] {
+        if (!ix) fail(CULSH_ERR_INVALID, "null index");
+        DeviceGuard g(ix->ctx->device);
+        if (ix->n_buckets) unpack_and_copy(ix->ctx, ix->bucket_keys.p, (size_t)ix->n_buckets, ix->ks, dst);
+    });
+}
+int culsh_index_get_bucket_candidate_offsets(const culsh_index* ix, int32_t* dst) {
+    return guarded([&] {
+        if (!ix) fail(CULSH_ERR_INVALID, "null index");
+        DeviceGuard g(ix->ctx->device);
+        copy_out(ix->ctx, dst, ix->bucket_offsets.p, ix->bucket_offsets.bytes());
+    });
+}
+int culsh_index_get_table_bucket_offsets(const culsh_index* ix, int32_t* dst) {
+    return guarded([&] {
+        if (!ix) fail(CULSH_ERR_INVALID, "null index");
+        DeviceGuard g(ix->ctx->device);
+        copy_out(ix->ctx, dst, ix->table_offsets.p, ix->table_offsets.bytes());
+    });
+}
+int culsh_index_get_projection(const culsh_index* ix, void* dst) {
+    return guarded([&] {
+        if (!ix) fail(CULSH_ERR_INVALID, "null index");
+        if (ix->family == CULSH_MINHASH) fail(CULSH_ERR_INVALID, "MinHash index has no projection");
+        DeviceGuard g(ix->ctx->device);
+        copy_out(ix->ctx, dst, ix->p0.p, ix->p0.bytes());
+    });
+}
+int culsh_index_get_bias(const culsh_index* ix, void* dst) {
+    return guarded([&] {
+        if (!ix) fail(CULSH_ERR_INVALID, "null index");
+        if (ix->family != CULSH_PSLSH) fail(CULSH_ERR_INVALID, "only a p-stable index has a bias");
+        DeviceGuard g(ix->ctx->device);
+        copy_out(ix->ctx, dst, ix->p1.p, ix->p1.bytes());
+    });
+}
+int culsh_index_get_hash_a(const culsh_index* ix, uint32_t* dst) {
+    return guarded([&] {
+        if (!ix) fail(CULSH_ERR_INVALID, "null index");
+        if (ix->family != CULSH_MINHASH) fail(CULSH_ERR_INVALID, "not a MinHash index");
+        DeviceGuard g(ix->ctx->device);
+        copy_out(ix->ctx, dst, ix->p0.p, ix->p0.bytes());
+    });
+}
+int culsh_index_get_hash_b(const culsh_index* ix, uint32_t* dst) {
+    return guarded([&] {
+        if (!ix) fail(CULSH_ERR_INVALID, "null index");
+        if (ix->family != CULSH_MINHASH) fail(CULSH_ERR_INVALID, "not a MinHash index");
+        DeviceGuard g(ix->ctx->device);
+        copy_out(ix->ctx, dst, ix->p1.p, ix->p1.bytes());
+    });
+}
+
+int culsh_index_load(culsh_handle* h, int family, int is_double, const int32_t* candidate_indices,
+                     const uint8_t* bucket_signatures, const int32_t* bucket_candidate_offsets,
+                     const int32_t* table_bucket_offsets, const void* param0, const void* param1,
+                     int n_total_candidates, int n_total_buckets, int L, int k, int sig_nbytes,
+                     int n_features, int window_size, uint64_t seed, culsh_index** out) {
+    return guarded([&] {
+        if (!h || !out) fail(CULSH_ERR_INVALID, "null handle or output pointer");
+        if (family < CULSH_RPLSH || family > CULSH_MINHASH) fail(CULSH_ERR_INVALID, "unknown family");
+        if (L <= 0 || k <= 0 || n_total_candidates <= 0 || n_total_buckets <= 0)
+            fail(CULSH_ERR_INVALID, "index dimensions must be positive");
+        if (n_total_candidates % L != 0)
+            fail(CULSH_ERR_INVALID, "n_total_candidates is not a multiple of n_hash_tables");
+        const int expect_sig = family == CULSH_RPLSH ? k : 4 * k;
+        if (sig_nbytes != expect_sig)
+            fail(CULSH_ERR_INVALID, "sig_nbytes=%d does not match n_hashes=%d for this family", sig_nbytes, k);
+        if (!candidate_indices || !bucket_signatures || !bucket_candidate_offsets ||
+            !table_bucket_offsets || !param0)
+            fail(CULSH_ERR_INVALID, "null array");
+        if (family != CULSH_RPLSH && !param1) fail(CULSH_ERR_INVALID, "second parameter array is null");
+        if (family != CULSH_MINHASH && n_features <= 0) fail(CULSH_ERR_INVALID, "n_features must be positive");
+        DeviceGuard g(h->ctx->device);
+        const CtxPtr& c = h->ctx;
+        cudaStream_t s = c->stream;
+        auto ix = std::make_unique<culsh_index>();
+        ix->ctx = c;
+        ix->family = family;
+        ix->L = L; ix->k = k; ix->d = n_features;
+        ix->n = n_total_candidates / L;
+        ix->window = family == CULSH_PSLSH ? window_size : 0;
+        ix->is_double = family == CULSH_MINHASH ? 0 : (is_double ? 1 : 0);
+        ix->seed = seed;
+        ix->n_buckets = n_total_buckets;
+        const size_t B = (size_t)n_total_buckets;
+        ix->cand.alloc(c, (size_t)n_total_candidates);
+        ix->bucket_offsets.alloc(c, B + 1);
+        ix->table_offsets.alloc(c, (size_t)L + 1);
+        CU_CHECK(cudaMemcpyAsync(ix->cand.p, candidate_indices, ix->cand.bytes(), cudaMemcpyDefault, s));
+        CU_CHECK(cudaMemcpyAsync(ix->bucket_offsets.p, bucket_candidate_offsets, ix->bucket_offsets.bytes(), cudaMemcpyDefault, s));
+        CU_CHECK(cudaMemcpyAsync(ix->table_offsets.p, table_bucket_offsets, ix->table_offsets.bytes(), cudaMemcpyDefault, s));
+        const int H = L * k;
+        if (family == CULSH_MINHASH) {
+            ix->p0.alloc(c, sizeof(uint32_t) * H);
+            ix->p1.alloc(c, sizeof(uint32_t) * H);
+        } else {
+            const size_t esz = ix->is_double ? 8 : 4;
+            ix->p0.alloc(c, esz * H * n_features);
+            if (family == CULSH_PSLSH) ix->p1.alloc(c, esz * H);
+        }
+        CU_CHECK(cudaMemcpyAsync(ix->p0.p, param0, ix->p0.bytes(), cudaMemcpyDefault, s));
+        if (ix->p1.n) CU_CHECK(cudaMemcpyAsync(ix->p1.p, param1, ix->p1.bytes(), cudaMemcpyDefault, s));
+        // raw signatures -> packed keys (p-stable: narrowest element width that holds them)
+        DevBuf<uint8_t> raw(c, B * sig_nbytes);
+        CU_CHECK(cudaMemcpyAsync(raw.p, bucket_signatures, raw.bytes(), cudaMemcpyDefault, s));
+        int eb = family == CULSH_MINHASH ? 4 : 0;
+        if (family == CULSH_PSLSH) {
+            DevBuf<int> width(c, 1);
+            int one = 1;
+            CU_CHECK(cudaMemcpyAsync(width.p, &one, sizeof(int), cudaMemcpyHostToDevice, s));
+            size_t cnt = B * k;
+            pslsh_width_kernel<<<(unsigned)ceil_div(cnt, 256), 256, 0, s>>>(
+                reinterpret_cast<const int32_t*>(raw.p), cnt, width.p);
+            KERNEL_CHECK();
+            read_words(c, width.p, sizeof(int), &eb);
+            while (eb < 4 && round_key_words(k * eb) < 0) eb *= 2;
+        }
+        ix->ks = make_key_spec(family, k, eb);
+        if (ix->ks.key_words < 0) fail(CULSH_ERR_UNSUPPORTED, "signature wider than the 64-byte key limit");
+        ix->bucket_keys.alloc(c, B * ix->ks.key_words);
+        pack_keys_kernel<<<(unsigned)ceil_div(B, 256), 256, 0, s>>>(raw.p, B, family, k, ix->ks.key_words,
+                                                                   ix->ks.elem_bytes, ix->bucket_keys.p);
+        KERNEL_CHECK();
+        prepare_tc_split(*ix);
+        CU_CHECK(cudaStreamSynchronize(s));
+        *out = ix.release();
+    });
+}
+
+void culsh_index_free(culsh_index* ix) {
+    if (!ix) return;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(ix->ctx->device);
+    delete ix;
+    if (prev >= 0) cudaSetDevice(prev);
+}
+
+// ---- Candidates -------------------------------------------------------------------------
+int culsh_candidates_get_meta(const culsh_candidates* c, int32_t* n_queries, uint64_t* total,
+                              int32_t* is_empty) {
+    return guarded([&] {
+        if (!c) fail(CULSH_ERR_INVALID, "null candidates");
+        if (n_queries) *n_queries = c->n_queries;
+        if (total) *total = c->total;
+        if (is_empty) *is_empty = c->empty() ? 1 : 0;
+    });
+}
+int culsh_candidates_get_indices(const culsh_candidates* c, int32_t* dst) {
+    return guarded([&] {
+        if (!c) fail(CULSH_ERR_INVALID, "null candidates");
+        DeviceGuard g(c->ctx->device);
+        copy_out(c->ctx, dst, c->indices.p, sizeof(int32_t) * c->total);
+    });
+}
+int culsh_candidates_get_counts(const culsh_candidates* c, uint64_t* dst) {
+    return guarded([&] {
+        if (!c) fail(CULSH_ERR_INVALID, "null candidates");
+        DeviceGuard g(c->ctx->device);
+        copy_out(c->ctx, dst, c->counts.p, sizeof(uint64_t) * (size_t)c->n_queries);
+    });
+}
+int culsh_candidates_get_offsets(const culsh_candidates* c, uint64_t* dst) {
+    return guarded([&] {
+        if (!c) fail(CULSH_ERR_INVALID, "null candidates");
+        DeviceGuard g(c->ctx->device);
+        copy_out(c->ctx, dst, c->offsets.p, sizeof(uint64_t) * ((size_t)c->n_queries + 1));
+    });
+}
+int culsh_candidates_device_ptrs(const culsh_candidates* c, const int32_t** indices,
+                                 const uint64_t** counts, const uint64_t** offsets) {
+    return guarded([&] {
+        if (!c) fail(CULSH_ERR_INVALID, "null candidates");
+        if (indices) *indices = c->indices.p;
+        if (counts) *counts = c->counts.p;
+        if (offsets) *offsets = c->offsets.p;
+    });
+}
+void culsh_candidates_free(culsh_candidates* c) {
+    if (!c) return;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (c->ctx) cudaSetDevice(c->ctx->device);
+    delete c;
+    if (prev >= 0) cudaSetDevice(prev);
+}
+
+// ---- shard merge ------------------------------------------------------------------------
+int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
+                                 const int32_t* const* shard_indices,
+                                 const uint64_t* const* shard_offsets, const int64_t* row_base,
+                                 culsh_candidates** out) {
+    return guarded([&] {
+        if (!h || !out || !shard_indices || !shard_offsets || !row_base)
+            fail(CULSH_ERR_INVALID, "null argument");
+        if (n_shards <= 0 || n_q < 0) fail(CULSH_ERR_INVALID, "bad shard or query count");
+        DeviceGuard g(h->ctx->device);
+        const CtxPtr& c = h->ctx;
+        cudaStream_t s = c->stream;
+        auto res = std::make_unique<culsh_candidates>();
+        if (n_q == 0) {
+            empty_result(c, *res);
+            *out = res.release();
+            return;
+        }
+        DevBuf<const int32_t*> d_idx(c, n_shards);
+        DevBuf<const uint64_t*> d_off(c, n_shards);
+        DevBuf<int64_t> d_base(c, n_shards);
+        CU_CHECK(cudaMemcpyAsync(d_idx.p, shard_indices, sizeof(void*) * n_shards, cudaMemcpyHostToDevice, s));
+        CU_CHECK(cudaMemcpyAsync(d_off.p, shard_offsets, sizeof(void*) * n_shards, cudaMemcpyHostToDevice, s));
+        CU_CHECK(cudaMemcpyAsync(d_base.p, row_base, sizeof(int64_t) * n_shards, cudaMemcpyHostToDevice, s));
+        res->ctx = c;
+        res->n_queries = n_q;
+        res->counts.alloc(c, n_q);
+        res->offsets.alloc(c, (size_t)n_q + 1);
+        DevBuf<uint64_t> scratch(c, scan_scratch_elems(n_q));
+        shard_counts_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(d_off.p, n_shards, n_q, res->counts.p);
+        KERNEL_CHECK();
+        exclusive_scan<uint64_t, uint64_t>(s, res->counts.p, n_q, res->offsets.p, scratch.p);
+        uint64_t total = 0;
+        read_words(c, res->offsets.p + n_q, sizeof(uint64_t), &total);
+        res->total = total;
+        if (total) {
+            res->indices.alloc(c, total);
+            size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
+            shard_interleave_kernel<<<(unsigned)blocks, 256, 0, s>>>(d_idx.p, d_off.p, d_base.p, n_shards,
+                                                                    n_q, res->offsets.p, res->indices.p);
+            KERNEL_CHECK();
+        }
+        CU_CHECK(cudaStreamSynchronize(s));
+        *out = res.release();
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,337 @@
+// Query side: bucket lookup, candidate gather and per-query cross-table dedupe, written
+// into the CSR result.  Replaces find_matching_buckets_kernel (core/query.cuh:31-101) and
+// query_from_matched_buckets (core/query.cuh:290-478): upstream materialises the raw
+// candidates, runs a 32-bit segmented radix sort over them, flags/reduces/scans and
+// compacts (about 15 passes over `raw` ints); here each query's bucket lists are merged
+// on chip - a shared-memory bitmap over row ids for large candidate sets, a warp-level
+// sort for small ones - and each list is read once and its unique ids written once.
+#pragma once
+
+#include "common.cuh"
+#include "radix_sort.cuh"
+
+namespace culsh_b200 {
+
+// ---------------------------------------------------------------------------------------
+// Lookup: one thread per (table, query); binary search over the table's sorted bucket keys.
+// matched[q*L + t] = bucket id or -1 (same layout as upstream's matched_bucket_indices).
+// ---------------------------------------------------------------------------------------
+template <int NW>
+__device__ __forceinline__ int compare_keys(const uint32_t* __restrict__ a,
+                                            const uint32_t* __restrict__ b) {
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+        if (a[w] != b[w]) return a[w] < b[w] ? -1 : 1;
+    }
+    return 0;
+}
+
+template <int NW>
+__global__ void __launch_bounds__(256)
+lookup_kernel(const uint32_t* __restrict__ qkeys, const uint8_t* __restrict__ q_ovf, int n_q, int L,
+              const uint32_t* __restrict__ bucket_keys, const int32_t* __restrict__ table_offsets,
+              int32_t* __restrict__ matched) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_q * L) return;
+    const int t = (int)(idx / n_q);
+    const int q = (int)(idx - (size_t)t * n_q);
+    uint32_t key[NW];
+    load_key<NW>(qkeys + idx * NW, key);
+    int lo = table_offsets[t], hi = table_offsets[t + 1] - 1;
+    int found = -1;
+    if (q_ovf && q_ovf[idx]) hi = lo - 1;  // value outside the index's narrow range: no bucket
+    while (lo <= hi) {
+        int mid = lo + ((hi - lo) >> 1);
+        int c = compare_keys<NW>(key, bucket_keys + (size_t)mid * NW);
+        if (c == 0) { found = mid; break; }
+        if (c < 0) hi = mid - 1; else lo = mid + 1;
+    }
+    matched[(size_t)q * L + t] = found;
+}
+
+// ---------------------------------------------------------------------------------------
+// Raw (pre-dedupe) candidate count per query; queries above the small-path limit are
+// appended to big_list.
+// ---------------------------------------------------------------------------------------
+constexpr int SMALL_MAX = 512;  // largest raw count handled by the warp path
+
+__global__ void __launch_bounds__(256)
+raw_count_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
+                 int n_q, int L, uint64_t* __restrict__ raw_cnt, uint32_t* __restrict__ big_list,
+                 uint32_t* __restrict__ n_big) {
+    int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= n_q) return;
+    uint64_t c = 0;
+    for (int t = 0; t < L; ++t) {
+        int b = matched[(size_t)q * L + t];
+        if (b >= 0) c += (uint64_t)(bucket_offsets[b + 1] - bucket_offsets[b]);
+    }
+    raw_cnt[q] = c;
+    if (c > SMALL_MAX) big_list[atomicAdd(n_big, 1u)] = (uint32_t)q;
+}
+
+// ---------------------------------------------------------------------------------------
+// Small path: one warp per query, raw <= SMALL_MAX.  Bitonic sort in the warp's slice of
+// shared memory, adjacent-unique, ballot compaction.  Output goes to tmp[raw_off[q] ...].
+// ---------------------------------------------------------------------------------------
+constexpr int SM_THREADS = 256;
+constexpr int SM_WARPS = SM_THREADS / 32;
+
+__global__ void __launch_bounds__(SM_THREADS)
+dedupe_small_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
+                    const int32_t* __restrict__ cand, const uint64_t* __restrict__ raw_cnt,
+                    const uint64_t* __restrict__ raw_off, int n_q, int L, int32_t* __restrict__ tmp,
+                    uint64_t* __restrict__ uniq_cnt) {
+    __shared__ int32_t s_buf[SM_WARPS][SMALL_MAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int32_t* buf = s_buf[warp];
+    for (int q = blockIdx.x * SM_WARPS + warp; q < n_q; q += gridDim.x * SM_WARPS) {
+        const uint64_t r64 = raw_cnt[q];
+        if (r64 > SMALL_MAX) continue;  // the block path owns it
+        const int r = (int)r64;
+        if (r == 0) {
+            if (lane == 0) uniq_cnt[q] = 0;
+            continue;
+        }
+        int m = 32;
+        while (m < r) m <<= 1;
+        // gather the bucket lists one after another
+        int fill = 0;
+        for (int t = 0; t < L; ++t) {
+            int b = matched[(size_t)q * L + t];
+            if (b < 0) continue;
+            int s = bucket_offsets[b], e = bucket_offsets[b + 1];
+            for (int i = s + lane; i < e; i += 32) buf[fill + (i - s)] = cand[i];
+            fill += e - s;
+        }
+        for (int i = r + lane; i < m; i += 32) buf[i] = 0x7FFFFFFF;
+        __syncwarp();
+        for (int ksz = 2; ksz <= m; ksz <<= 1) {
+            for (int j = ksz >> 1; j > 0; j >>= 1) {
+                for (int i = lane; i < m; i += 32) {
+                    int ixj = i ^ j;
+                    if (ixj > i) {
+                        int32_t a = buf[i], b = buf[ixj];
+                        bool up = (i & ksz) == 0;
+                        if ((a > b) == up) { buf[i] = b; buf[ixj] = a; }
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        // unique + compact
+        int32_t* out = tmp + raw_off[q];
+        int written = 0;
+        for (int i0 = 0; i0 < r; i0 += 32) {
+            int i = i0 + lane;
+            bool keep = false;
+            int32_t v = 0;
+            if (i < r) {
+                v = buf[i];
+                keep = i == 0 || buf[i - 1] != v;
+            }
+            uint32_t mask = __ballot_sync(0xFFFFFFFFu, keep);
+            if (keep) out[written + __popc(mask & ((1u << lane) - 1))] = v;
+            written += __popc(mask);
+        }
+        if (lane == 0) uniq_cnt[q] = (uint64_t)written;
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Block path: one CTA per query of big_list.  Row ids are marked in a shared-memory bitmap
+// covering a window of `window_bits` ids; windows are visited in increasing order, and as
+// every bucket list is ascending each window's slice of a list is found by binary search.
+// A pop-count scan of the bitmap then emits the window's ids sorted and unique.
+// ---------------------------------------------------------------------------------------
+constexpr int BM_THREADS = 512;
+constexpr int BM_WARPS = BM_THREADS / 32;
+constexpr int BM_MAX_L = 1024;  // lists kept in shared memory
+
+__device__ __forceinline__ int lower_bound_i32(const int32_t* __restrict__ a, int lo, int hi, int32_t v) {
+    while (lo < hi) {
+        int mid = lo + ((hi - lo) >> 1);
+        if (a[mid] < v) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+__global__ void __launch_bounds__(BM_THREADS)
+dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __restrict__ matched,
+                     const int32_t* __restrict__ bucket_offsets, const int32_t* __restrict__ cand,
+                     const uint64_t* __restrict__ raw_off, int L, int n_rows, int window_bits,
+                     int32_t* __restrict__ tmp, uint64_t* __restrict__ uniq_cnt) {
+    extern __shared__ __align__(16) uint32_t s_dyn[];
+    uint32_t* bitmap = s_dyn;                                // [window_bits / 32]
+    int* s_lo = reinterpret_cast<int*>(bitmap + window_bits / 32);  // [Lc] cursor (global position)
+    int* s_hi = s_lo + BM_MAX_L;                              // [Lc] end of list
+    int* s_we = s_hi + BM_MAX_L;                              // [Lc] end of the window's slice
+    __shared__ uint32_t s_wtot[BM_WARPS];
+    __shared__ int s_any;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int q = (int)big_list[blockIdx.x];
+    const int words = window_bits / 32;
+    int32_t* out = tmp + raw_off[q];
+    uint32_t written = 0;  // uniform across the block
+
+    // L may exceed BM_MAX_L: process tables in groups; groups after the first need the
+    // bitmap of the same window, so the group loop sits inside the window loop.
+    for (int win_lo = 0; win_lo < n_rows; win_lo += window_bits) {
+        const int win_hi = min(n_rows, win_lo + window_bits);
+        bool cleared = false;
+        for (int g0 = 0; g0 < L; g0 += BM_MAX_L) {
+            const int Lg = min(BM_MAX_L, L - g0);
+            if (tid == 0) s_any = 0;
+            __syncthreads();
+            for (int t = tid; t < Lg; t += BM_THREADS) {
+                int b = matched[(size_t)q * L + g0 + t];
+                int lo = 0, hi = 0, we = 0;
+                if (b >= 0) {
+                    int s = bucket_offsets[b], e = bucket_offsets[b + 1];
+                    if (n_rows <= window_bits) { lo = s; we = e; }
+                    else {
+                        lo = lower_bound_i32(cand, s, e, win_lo);
+                        we = lower_bound_i32(cand, lo, e, win_hi);
+                    }
+                    hi = e;
+                    if (we > lo) s_any = 1;
+                }
+                s_lo[t] = lo; s_hi[t] = hi; s_we[t] = we;
+            }
+            __syncthreads();
+            const int any = s_any;
+            __syncthreads();  // s_any is rewritten at the top of the next group
+            if (!any) continue;  // uniform
+            if (!cleared) {
+                for (int w = tid; w < words; w += BM_THREADS) bitmap[w] = 0;
+                cleared = true;
+                __syncthreads();
+            }
+            // mark: warps take lists round-robin, lanes stride a list
+            for (int t = warp; t < Lg; t += BM_WARPS) {
+                const int lo = s_lo[t], we = s_we[t];
+                for (int i = lo + lane; i < we; i += 32) {
+                    uint32_t id = (uint32_t)(cand[i] - win_lo);
+                    atomicOr(&bitmap[id >> 5], 1u << (id & 31));
+                }
+            }
+            __syncthreads();
+        }
+        if (!cleared) continue;  // uniform: nothing in this window
+        // ---- pop-count scan: warp w owns words [w*per_warp, (w+1)*per_warp) ----
+        const int per_warp = (words + BM_WARPS - 1) / BM_WARPS;
+        const int w_begin = warp * per_warp, w_end = min(words, w_begin + per_warp);
+        uint32_t wsum = 0;
+        for (int w = w_begin + lane; w < w_end; w += 32) wsum += __popc(bitmap[w]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xFFFFFFFFu, wsum, o);
+        if (lane == 0) s_wtot[warp] = wsum;
+        __syncthreads();
+        uint32_t wbase = 0, wtotal = 0;
+        for (int i = 0; i < BM_WARPS; ++i) {
+            uint32_t x = s_wtot[i];
+            if (i < warp) wbase += x;
+            wtotal += x;
+        }
+        uint32_t pos = written + wbase;
+        for (int w0 = w_begin; w0 < w_end; w0 += 32) {
+            const int w = w0 + lane;
+            uint32_t bits = w < w_end ? bitmap[w] : 0u;
+            uint32_t c = __popc(bits);
+            uint32_t inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+                if (lane >= o) inc += x;
+            }
+            uint32_t o_pos = pos + inc - c;
+            const int32_t id0 = win_lo + w * 32;
+            while (bits) {
+                int b = __ffs(bits) - 1;
+                bits &= bits - 1;
+                out[o_pos++] = id0 + b;
+            }
+            pos += __shfl_sync(0xFFFFFFFFu, inc, 31);
+        }
+        written += wtotal;
+        __syncthreads();
+    }
+    if (tid == 0) uniq_cnt[q] = (uint64_t)written;
+}
+
+// ---------------------------------------------------------------------------------------
+// Compaction of the per-query segments from their raw offsets to their final offsets.
+// ---------------------------------------------------------------------------------------
+// Queries of big_list: a whole block copies the segment.
+__global__ void __launch_bounds__(256)
+compact_big_kernel(const uint32_t* __restrict__ big_list, const int32_t* __restrict__ tmp,
+                   const uint64_t* __restrict__ raw_off, const uint64_t* __restrict__ uniq_cnt,
+                   const uint64_t* __restrict__ offsets, int32_t* __restrict__ out) {
+    const int q = (int)big_list[blockIdx.x];
+    const uint64_t c = uniq_cnt[q];
+    const int32_t* src = tmp + raw_off[q];
+    int32_t* dst = out + offsets[q];
+    for (uint64_t i = threadIdx.x; i < c; i += blockDim.x) dst[i] = src[i];
+}
+
+// Small queries only (big ones are copied by compact_big_kernel).
+__global__ void __launch_bounds__(256)
+compact_small_kernel(const int32_t* __restrict__ tmp, const uint64_t* __restrict__ raw_cnt,
+                     const uint64_t* __restrict__ raw_off, const uint64_t* __restrict__ uniq_cnt,
+                     const uint64_t* __restrict__ offsets, int n_q, int32_t* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t n_warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t q = warp; q < (size_t)n_q; q += n_warps) {
+        if (raw_cnt[q] > SMALL_MAX) continue;
+        const uint64_t c = uniq_cnt[q];
+        const int32_t* src = tmp + raw_off[q];
+        int32_t* dst = out + offsets[q];
+        for (uint64_t i = lane; i < c; i += 32) dst[i] = src[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Batch / shard merging helpers.
+// ---------------------------------------------------------------------------------------
+// offsets_out[q0 + i] = offsets_in[i] + shift, i in [0, n]
+__global__ void shift_offsets_kernel(const uint64_t* __restrict__ in, size_t n, uint64_t shift,
+                                     uint64_t* __restrict__ out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = in[i] + shift;
+}
+
+// counts[q] = sum over shards of (off_r[q+1] - off_r[q])
+__global__ void shard_counts_kernel(const uint64_t* const* __restrict__ shard_offsets, int n_shards,
+                                    int n_q, uint64_t* __restrict__ counts) {
+    int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= n_q) return;
+    uint64_t c = 0;
+    for (int r = 0; r < n_shards; ++r) c += shard_offsets[r][q + 1] - shard_offsets[r][q];
+    counts[q] = c;
+}
+
+// one warp per query: copy each shard's list (shifted to global ids) in shard order
+__global__ void __launch_bounds__(256)
+shard_interleave_kernel(const int32_t* const* __restrict__ shard_indices,
+                        const uint64_t* const* __restrict__ shard_offsets,
+                        const int64_t* __restrict__ row_base, int n_shards, int n_q,
+                        const uint64_t* __restrict__ offsets, int32_t* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t n_warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t q = warp; q < (size_t)n_q; q += n_warps) {
+        uint64_t o = offsets[q];
+        for (int r = 0; r < n_shards; ++r) {
+            const uint64_t s = shard_offsets[r][q], e = shard_offsets[r][q + 1];
+            const int32_t* src = shard_indices[r] + s;
+            const int32_t base = (int32_t)row_base[r];
+            for (uint64_t i = lane; i < e - s; i += 32) out[o + i] = src[i] + base;
+            o += e - s;
+        }
+    }
+}
+
+}  // namespace culsh_b200

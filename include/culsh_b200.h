@@ -1,0 +1,197 @@
+/*
+ * culsh_b200 - C ABI of the B200-native LSH engine (hash -> bucket index -> lookup ->
+ * gather/dedupe -> CSR) that stands in for cuLSH's pybind11 module `culsh._culsh_core`.
+ *
+ * Upstream has no C ABI: its Python layer binds C++ classes with pybind11
+ * (python/csrc/bindings.cu:481-588).  Each entry point below names the upstream
+ * class method / C++ function it replaces (paths relative to the upstream project root).
+ *
+ * Conventions
+ *  - Every function returns 0 on success, a negative culsh_status otherwise; the text of
+ *    the last failure is available from culsh_last_error() (thread-local).  Nothing calls
+ *    exit() and no CUDA error is ignored (upstream: core/utils.cuh:10-52).
+ *  - Array arguments are plain pointers.  An input or output pointer may live on the
+ *    device of the handle OR in host memory (pageable or pinned); the library finds out
+ *    with cudaPointerGetAttributes and stages host data itself.  Upstream only takes
+ *    device pointers (python/csrc/common/array_utils.cuh:17-28) and leaves the
+ *    host->device copy to CuPy in the Python layer (python/culsh/utils.py:34-53).
+ *  - Dense inputs are C-contiguous row-major [n][d]; CSR inputs are int32 indices/indptr.
+ *  - Every call is synchronous: it returns after its work on the handle's stream has
+ *    finished (upstream: synchronize() after each method, bindings.cu:41,51,68,...).
+ *  - Objects are not thread-safe; use one handle per host thread.
+ */
+#ifndef CULSH_B200_H
+#define CULSH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum culsh_status {
+    CULSH_OK = 0,
+    CULSH_ERR_INVALID = -1,    /* bad argument (shape, dtype mismatch, null pointer)        */
+    CULSH_ERR_CUDA = -2,       /* a CUDA runtime / cuRAND call failed                       */
+    CULSH_ERR_ALLOC = -3,      /* device or host allocation failed                          */
+    CULSH_ERR_INTERNAL = -4,   /* a kernel reported a failed self-check (e.g. a bounded wait
+                                  ran out); the context stays usable                        */
+    CULSH_ERR_UNSUPPORTED = -5 /* limits: n*L >= 2^31, n_hashes too wide for one CTA, ...   */
+} culsh_status;
+
+typedef enum culsh_family {
+    CULSH_RPLSH = 0,  /* random projection, cosine; signature element uint8 0/1 */
+    CULSH_PSLSH = 1,  /* p-stable, Euclidean; signature element int32            */
+    CULSH_MINHASH = 2 /* MinHash, Jaccard; signature element uint32              */
+} culsh_family;
+
+/* Opaque objects. */
+typedef struct culsh_handle culsh_handle;         /* replaces CUDAResourceManager, python/csrc/common/cuda_utils.cuh:30-61 */
+typedef struct culsh_index culsh_index;           /* replaces rplsh::Index / pslsh::Index / minhash::Index (+ core::Index, core/index.cuh:12-195) */
+typedef struct culsh_candidates culsh_candidates; /* replaces core::Candidates, core/candidates.cuh:14-137 */
+
+/* Mirror of the read-only properties bound in bindings.cu:381-404 (+ is_double, window). */
+typedef struct culsh_index_meta {
+    int32_t family;             /* culsh_family */
+    int32_t n_total_candidates; /* n_samples * n_hash_tables */
+    int32_t n_total_buckets;
+    int32_t n_hash_tables;
+    int32_t n_hashes;
+    int32_t sig_nbytes;         /* upstream's raw signature width: k*1 (RPLSH) or k*4 */
+    int32_t n_features;
+    int32_t is_double;          /* dense families: parameters stored as float64 */
+    int32_t window_size;        /* PSLSH only, else 0 */
+    int32_t n_samples;
+    int32_t key_words;          /* internal packed key width in 32-bit words */
+    int32_t elem_bytes;         /* internal bytes kept per signature element */
+    uint64_t seed;
+    uint64_t size_bytes;        /* core/index.cuh:148-165 + family parameters, upstream layout */
+} culsh_index_meta;
+
+/* Per-stage figures of the last fit / query on a handle (device time from CUDA events). */
+typedef struct culsh_stats {
+    float hash_ms, sort_ms, build_ms, lookup_ms, gather_ms, total_ms;
+    uint64_t n_items, n_buckets, raw_candidates, unique_candidates;
+    int32_t sort_passes, key_words, elem_bytes, hash_path; /* hash_path: 0 SIMT, 1 tcgen05 */
+} culsh_stats;
+
+/* ---- handle -------------------------------------------------------------------------- */
+/* CUDAResourceManager(): one stream per object (python/csrc/common/cuda_utils.cuh:36-39). */
+int culsh_create(int device, culsh_handle** out);
+int culsh_destroy(culsh_handle* h);
+const char* culsh_last_error(void);
+int culsh_get_stats(const culsh_handle* h, culsh_stats* out);
+/* 1 = time stages with CUDA events (adds a few event records per call). Default 0. */
+int culsh_set_profiling(culsh_handle* h, int enabled);
+/* Force the projection path: 0 auto, 1 SIMT fp32/fp64 kernel, 2 tcgen05 3xTF32 kernel. */
+int culsh_set_projection_path(culsh_handle* h, int path);
+
+/* ---- RPLSH: RPLSHCore, bindings.cu:25-116; rplsh/rplsh.cu:18-226 ---------------------- */
+/* RPLSHCore.fit_float / fit_double  -> rplsh::fit (rplsh.cu:18-84). */
+int culsh_rplsh_fit_f32(culsh_handle* h, const float* X, int n_samples, int n_features,
+                        int n_hash_tables, int n_hashes, uint64_t seed, culsh_index** out);
+int culsh_rplsh_fit_f64(culsh_handle* h, const double* X, int n_samples, int n_features,
+                        int n_hash_tables, int n_hashes, uint64_t seed, culsh_index** out);
+/* RPLSHCore.query_float / query_double -> rplsh::query / query_batched (rplsh.cu:86-128,
+ * 188-226).  batch_size <= 0 means "not given".  A dtype that differs from the index's is
+ * CULSH_ERR_INVALID (bindings.cu:58-60,75-77). */
+int culsh_rplsh_query_f32(culsh_handle* h, const float* Q, int n_queries, const culsh_index* index,
+                          int batch_size, culsh_candidates** out);
+int culsh_rplsh_query_f64(culsh_handle* h, const double* Q, int n_queries, const culsh_index* index,
+                          int batch_size, culsh_candidates** out);
+/* RPLSHCore.fit_query_float / fit_query_double -> rplsh::fit_query (rplsh.cu:130-186). */
+int culsh_rplsh_fit_query_f32(culsh_handle* h, const float* X, int n_samples, int n_features,
+                              int n_hash_tables, int n_hashes, uint64_t seed, culsh_candidates** out);
+int culsh_rplsh_fit_query_f64(culsh_handle* h, const double* X, int n_samples, int n_features,
+                              int n_hash_tables, int n_hashes, uint64_t seed, culsh_candidates** out);
+
+/* ---- PSLSH: PSLSHCore, bindings.cu:171-265; pslsh/pslsh.cu:18-242 --------------------- */
+int culsh_pslsh_fit_f32(culsh_handle* h, const float* X, int n_samples, int n_features,
+                        int n_hash_tables, int n_hashes, int window_size, uint64_t seed,
+                        culsh_index** out);
+int culsh_pslsh_fit_f64(culsh_handle* h, const double* X, int n_samples, int n_features,
+                        int n_hash_tables, int n_hashes, int window_size, uint64_t seed,
+                        culsh_index** out);
+int culsh_pslsh_query_f32(culsh_handle* h, const float* Q, int n_queries, const culsh_index* index,
+                          int batch_size, culsh_candidates** out);
+int culsh_pslsh_query_f64(culsh_handle* h, const double* Q, int n_queries, const culsh_index* index,
+                          int batch_size, culsh_candidates** out);
+int culsh_pslsh_fit_query_f32(culsh_handle* h, const float* X, int n_samples, int n_features,
+                              int n_hash_tables, int n_hashes, int window_size, uint64_t seed,
+                              culsh_candidates** out);
+int culsh_pslsh_fit_query_f64(culsh_handle* h, const double* X, int n_samples, int n_features,
+                              int n_hash_tables, int n_hashes, int window_size, uint64_t seed,
+                              culsh_candidates** out);
+
+/* ---- MinHash: MinHashCore, bindings.cu:119-168; minhash/minhash.cu:19-102 ------------- */
+/* indices: int32 [nnz] column ids, indptr: int32 [n+1]; nnz = indptr[n]. */
+int culsh_minhash_fit(culsh_handle* h, const int32_t* indices, const int32_t* indptr, int n_samples,
+                      int n_features, int n_hash_tables, int n_hashes, uint64_t seed,
+                      culsh_index** out);
+int culsh_minhash_query(culsh_handle* h, const int32_t* indices, const int32_t* indptr,
+                        int n_queries, const culsh_index* index, culsh_candidates** out);
+int culsh_minhash_fit_query(culsh_handle* h, const int32_t* indices, const int32_t* indptr,
+                            int n_samples, int n_features, int n_hash_tables, int n_hashes,
+                            uint64_t seed, culsh_candidates** out);
+
+/* ---- signatures only (diagnostic; upstream keeps X_sig internal: rplsh/hash.cuh:93-129,
+ *      pslsh/hash.cuh:105-142, minhash/hash.cuh:142-155).  `sig_out` receives upstream's
+ *      table-major raw layout [L][n][k] of uint8 / int32 / uint32, host or device. -------- */
+int culsh_index_hash_dense(culsh_handle* h, const culsh_index* index, const void* X, int n_rows,
+                           void* sig_out);
+int culsh_index_hash_csr(culsh_handle* h, const culsh_index* index, const int32_t* indices,
+                         const int32_t* indptr, int n_rows, void* sig_out);
+
+/* ---- Index: getters bindings.cu:341-404, loaders bindings.cu:407-476 ------------------ */
+int culsh_index_get_meta(const culsh_index* index, culsh_index_meta* out);
+/* Each getter copies into dst (host or device): sizes are n_total_candidates, B*sig_nbytes,
+ * B+1 and L+1 elements.  Arrays are produced in upstream's canonical layout. */
+int culsh_index_get_candidate_indices(const culsh_index* index, int32_t* dst);
+int culsh_index_get_bucket_signatures(const culsh_index* index, uint8_t* dst);
+int culsh_index_get_bucket_candidate_offsets(const culsh_index* index, int32_t* dst);
+int culsh_index_get_table_bucket_offsets(const culsh_index* index, int32_t* dst);
+/* get_projection_matrix (H*d), get_bias (H): element type follows is_double.
+ * get_hash_a / get_hash_b (H uint32). */
+int culsh_index_get_projection(const culsh_index* index, void* dst);
+int culsh_index_get_bias(const culsh_index* index, void* dst);
+int culsh_index_get_hash_a(const culsh_index* index, uint32_t* dst);
+int culsh_index_get_hash_b(const culsh_index* index, uint32_t* dst);
+/* RPLSHIndex.load_float/load_double, PSLSHIndex.load_*, MinHashIndex.load: rebuild an
+ * index from arrays in upstream's layout (as written by Model.save, e.g.
+ * python/culsh/rp_lsh.py:259-274).  param0 = projection | hash_a, param1 = bias | hash_b
+ * (NULL for RPLSH). */
+int culsh_index_load(culsh_handle* h, int family, int is_double, const int32_t* candidate_indices,
+                     const uint8_t* bucket_signatures, const int32_t* bucket_candidate_offsets,
+                     const int32_t* table_bucket_offsets, const void* param0, const void* param1,
+                     int n_total_candidates, int n_total_buckets, int n_hash_tables, int n_hashes,
+                     int sig_nbytes, int n_features, int window_size, uint64_t seed,
+                     culsh_index** out);
+void culsh_index_free(culsh_index* index);
+
+/* ---- Candidates: getters bindings.cu:268-338 ------------------------------------------ */
+int culsh_candidates_get_meta(const culsh_candidates* c, int32_t* n_queries,
+                              uint64_t* n_total_candidates, int32_t* is_empty);
+/* dst holds n_total_candidates int32 / n_queries uint64 / n_queries+1 uint64; host or device. */
+int culsh_candidates_get_indices(const culsh_candidates* c, int32_t* dst);
+int culsh_candidates_get_counts(const culsh_candidates* c, uint64_t* dst);
+int culsh_candidates_get_offsets(const culsh_candidates* c, uint64_t* dst);
+/* Device pointers of the result (borrowed; valid until culsh_candidates_free). */
+int culsh_candidates_device_ptrs(const culsh_candidates* c, const int32_t** indices,
+                                 const uint64_t** counts, const uint64_t** offsets);
+void culsh_candidates_free(culsh_candidates* c);
+
+/* ---- row-sharded indexes (no upstream counterpart: upstream is single-GPU) ------------- */
+/* Interleave R per-shard CSR results that were produced for the same queries into one CSR
+ * with global row ids: shard r's ids are shifted by row_base[r]; per query the shard lists
+ * are concatenated in shard order.  All shard arrays are device pointers on the handle's
+ * device (gathered there by the caller, e.g. with NCCL). */
+int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_queries,
+                                 const int32_t* const* shard_indices,
+                                 const uint64_t* const* shard_offsets, const int64_t* row_base,
+                                 culsh_candidates** out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CULSH_B200_H */

@@ -1,0 +1,428 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on the same seeded inputs.
+
+Bars: integer stages (MinHash signatures, every index array, candidate CSR) bit-exact;
+dense signatures bit-exact except elements whose pre-quantisation value lies within 1e-5
+(relative) of the sign / floor boundary - those are counted and must stay rare.
+"""
+import os
+
+import numpy as np
+import pytest
+import scipy.sparse as sp
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+REL_BAND = 1e-5  # tolerance stated by the target: relative distance to the quantisation boundary
+
+
+@pytest.fixture(scope="module")
+def eng():
+    import culsh_b200
+    from culsh_b200 import _culsh_core
+    return culsh_b200, _culsh_core
+
+
+def _sig_matrix(sig_lnk):
+    """[L][n][k] -> [n][L*k] (oracle layout)."""
+    L, n, k = sig_lnk.shape
+    return np.ascontiguousarray(sig_lnk.transpose(1, 0, 2)).reshape(n, L * k)
+
+
+def _assert_index_equals_oracle(index, sig_nH, L, k):
+    want = oracle.fit_index(sig_nH, L, k)
+    assert index.n_total_buckets == want.n_total_buckets
+    assert np.array_equal(index.get_table_bucket_offsets(), want.table_bucket_offsets)
+    assert np.array_equal(index.get_bucket_candidate_offsets(), want.bucket_candidate_offsets)
+    assert np.array_equal(index.get_bucket_signatures(), want.bucket_signatures)
+    assert np.array_equal(index.get_candidate_indices(), want.candidate_indices)
+    return want
+
+
+def _assert_candidates_equal(cand, want):
+    indices, offsets, counts = want
+    assert cand.n_queries == len(counts)
+    assert np.array_equal(cand.get_offsets(), offsets)
+    assert np.array_equal(cand.get_counts(), counts)
+    assert np.array_equal(cand.get_indices(), indices)
+    assert cand.n_total_candidates == len(indices)
+
+
+# ------------------------------------------------------------------------------------------
+# RPLSH
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("n,d,L,k", [(3000, 32, 8, 12), (1000, 100, 32, 16), (777, 33, 3, 20),
+                                     (5000, 16, 4, 2), (257, 7, 2, 40)])
+def test_rplsh_fit_query_parity(eng, dtype, n, d, L, k):
+    culsh, core_mod = eng
+    rng = np.random.RandomState(n + d)
+    X = rng.randn(n, d).astype(dtype)
+    Q = np.concatenate([X[:40] + 0.01 * rng.randn(40, d), rng.randn(25, d)]).astype(dtype)
+    model = culsh.RPLSH(L, k, seed=7).fit(X)
+    ix = model.index
+    P = ix.get_projection_matrix().reshape(L * k, d)
+    assert P.dtype == dtype
+
+    core = core_mod.RPLSHCore(L, k, 7)
+    sig = _sig_matrix(core.hash(X, ix))
+    near = oracle.rplsh_near_boundary(X, P, REL_BAND)
+    want_sig = oracle.rplsh_signatures(X, P)
+    assert np.array_equal(sig[~near], want_sig[~near])
+    assert near.mean() < 1e-3
+
+    _assert_index_equals_oracle(ix, sig, L, k)
+    qsig = _sig_matrix(core.hash(Q, ix))
+    qnear = oracle.rplsh_near_boundary(Q, P, REL_BAND)
+    assert np.array_equal(qsig[~qnear], oracle.rplsh_signatures(Q, P)[~qnear])
+    oidx = oracle.fit_index(sig, L, k)
+    _assert_candidates_equal(model.query(Q), oracle.query_index(oidx, qsig))
+
+
+def test_rplsh_fit_query_self_join_and_batches(eng):
+    culsh, _ = eng
+    rng = np.random.RandomState(0)
+    X = rng.randn(2000, 24).astype(np.float32)
+    lsh = culsh.RPLSH(6, 10, seed=3)
+    a = lsh.fit_query(X)
+    model = lsh.fit(X)
+    b = model.query(X)
+    for f in ("get_indices", "get_offsets", "get_counts"):
+        assert np.array_equal(getattr(a, f)(), getattr(b, f)())
+    off = a.get_offsets().astype(np.int64)
+    ind = a.get_indices()
+    for q in range(0, 2000, 97):  # every row is its own candidate
+        seg = ind[off[q]:off[q + 1]]
+        assert q in seg and np.all(np.diff(seg) > 0)
+    for bs in (10, 333, 1999, 2000, 5000):
+        c = model.query(X, batch_size=bs)
+        for f in ("get_indices", "get_offsets", "get_counts"):
+            assert np.array_equal(getattr(c, f)(), getattr(b, f)())
+    c = lsh.fit_query(X, batch_size=500)
+    assert np.array_equal(c.get_indices(), b.get_indices())
+
+
+def test_rplsh_zero_rows_take_the_sign_bit_rule(eng):
+    """x.p == +0.0 hashes to 1 (sign bit clear), as upstream's kernel; upstream's Python oracle
+    (x > 0) would give 0."""
+    culsh, core_mod = eng
+    X = np.zeros((64, 8), dtype=np.float32)
+    X[1::2] = np.random.RandomState(1).randn(32, 8)
+    model = culsh.RPLSH(2, 8, seed=1).fit(X)
+    sig = core_mod.RPLSHCore(2, 8, 1).hash(X, model.index)
+    assert np.all(sig[:, 0::2, :] == 1)
+    cand = model.query(X[:2])
+    off = cand.get_offsets()
+    assert np.array_equal(cand.get_indices()[: int(off[1])], np.arange(0, 64, 2))
+
+
+# ------------------------------------------------------------------------------------------
+# PSLSH
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("n,d,L,k,w,scale", [(3000, 32, 8, 4, 4, 1.0), (1000, 100, 16, 8, 8, 1.0),
+                                             (999, 18, 5, 3, 1, 30.0), (600, 10, 2, 2, 1, 5000.0),
+                                             (500, 12, 4, 16, 4, 1.0)])
+def test_pslsh_fit_query_parity(eng, dtype, n, d, L, k, w, scale):
+    """scale 30 pushes hash values beyond int8, 5000 beyond int16 (key widening paths)."""
+    culsh, core_mod = eng
+    rng = np.random.RandomState(n + d + k)
+    X = (scale * rng.randn(n, d)).astype(dtype)
+    Q = np.concatenate([X[:30] + 0.01 * rng.randn(30, d), scale * rng.randn(20, d),
+                        1e6 * rng.randn(5, d)]).astype(dtype)  # the last rows fall outside every bucket
+    model = culsh.PStableLSH(L, k, window_size=w, seed=11).fit(X)
+    ix = model.index
+    P = ix.get_projection_matrix().reshape(L * k, d)
+    b = ix.get_bias()
+    assert np.all(b > 0) and np.all(b <= 1)
+
+    core = core_mod.PSLSHCore(L, k, w, 11)
+    sig = _sig_matrix(core.hash(X, ix))
+    near = oracle.pslsh_near_boundary(X, P, b, REL_BAND)
+    want = oracle.pslsh_signatures(X, P, b)
+    assert np.array_equal(sig[~near], want[~near])
+    if scale == 1.0:  # the band is relative to sum|x.p|: at large magnitudes it spans whole buckets
+        assert near.mean() < 2e-3
+    lo, hi = int(sig.min()), int(sig.max())
+    expect_eb = 1 if (lo >= -128 and hi <= 127) else (2 if (lo >= -32768 and hi <= 32767) else 4)
+    assert ix.elem_bytes == expect_eb  # narrowest element width that holds every indexed value
+
+    _assert_index_equals_oracle(ix, sig, L, k)
+    qsig = _sig_matrix(core.hash(Q, ix))
+    _assert_candidates_equal(model.query(Q), oracle.query_index(oracle.fit_index(sig, L, k), qsig))
+
+
+def test_pslsh_consistency_and_auto_window(eng):
+    culsh, _ = eng
+    rng = np.random.RandomState(5)
+    X = rng.randn(1500, 20).astype(np.float32)
+    lsh = culsh.PStableLSH(8, 4, window_size=4, seed=2)
+    a = lsh.fit_query(X)
+    model = lsh.fit(X)
+    b = model.query(X)
+    for f in ("get_indices", "get_offsets", "get_counts"):
+        assert np.array_equal(getattr(a, f)(), getattr(b, f)())
+    for bs in (10, 50, 100):
+        c = model.query(X[:300], batch_size=bs)
+        d = model.query(X[:300])
+        assert np.array_equal(c.get_indices(), d.get_indices())
+        assert np.array_equal(c.get_offsets(), d.get_offsets())
+    Xn = X / np.linalg.norm(X, axis=1, keepdims=True) * 100.0
+    m = culsh.PStableLSH(4, 4, window_size="auto", seed=1).fit(Xn.astype(np.float32))
+    assert m.window_size == 100 or m.window_size == 99  # python/tests/test_pslsh.py:243-255
+
+
+# ------------------------------------------------------------------------------------------
+# MinHash
+# ------------------------------------------------------------------------------------------
+def _random_csr(rng, n, d, density):
+    X = sp.random(n, d, density=density, format="csr", dtype=np.float32, random_state=rng)
+    X.data[:] = 1.0
+    X.sort_indices()
+    return X
+
+
+@pytest.mark.parametrize("n,d,L,k,density", [(1000, 100, 8, 4, 0.1), (1000, 100, 32, 8, 0.5),
+                                             (500, 5000, 64, 16, 0.01), (300, 50, 3, 3, 0.2),
+                                             (400, 1 << 20, 4, 2, 1e-5)])
+def test_minhash_fit_query_parity(eng, n, d, L, k, density):
+    culsh, core_mod = eng
+    rng = np.random.RandomState(L * k)
+    X = _random_csr(rng, n, d, density)
+    Q = sp.vstack([X[:30], _random_csr(rng, 20, d, density)]).tocsr()
+    Q.sort_indices()
+    model = culsh.MinHashLSH(L, k, seed=9).fit(X)
+    ix = model.index
+    A, B = ix.get_hash_a(), ix.get_hash_b()
+    assert np.all(A >= 1) and np.all(A < oracle.MINHASH_PRIME) and np.all(B < oracle.MINHASH_PRIME)
+
+    core = core_mod.MinHashCore(L, k, 9)
+    sig = _sig_matrix(core.hash(X.indices, X.indptr, n, ix))
+    want = oracle.minhash_signatures(X.indices, X.indptr, A, B)
+    assert np.array_equal(sig, want)  # integer stage: bit exact
+    empty = np.flatnonzero(np.diff(X.indptr) == 0)
+    if len(empty):
+        assert np.all(sig[empty] == 0xFFFFFFFF)
+
+    oidx = _assert_index_equals_oracle(ix, want, L, k)
+    qsig = oracle.minhash_signatures(Q.indices, Q.indptr, A, B)
+    _assert_candidates_equal(model.query(Q), oracle.query_index(oidx, qsig))
+    a = culsh.MinHashLSH(L, k, seed=9).fit_query(X)
+    b = model.query(X)
+    assert np.array_equal(a.get_indices(), b.get_indices())
+    assert np.array_equal(a.get_offsets(), b.get_offsets())
+
+
+# ------------------------------------------------------------------------------------------
+# Gather / dedupe paths and edge cases
+# ------------------------------------------------------------------------------------------
+def test_large_buckets_use_the_bitmap_path(eng):
+    """k = 2 sign bits -> four buckets per table of ~n/4 rows: raw candidate counts far above
+    the warp path's limit; heavy cross-table duplication."""
+    culsh, core_mod = eng
+    rng = np.random.RandomState(42)
+    n, d, L, k = 40000, 12, 6, 2
+    X = rng.randn(n, d).astype(np.float32)
+    model = culsh.RPLSH(L, k, seed=5).fit(X)
+    core = core_mod.RPLSHCore(L, k, 5)
+    sig = _sig_matrix(core.hash(X, model.index))
+    Q = X[:16]
+    _assert_candidates_equal(model.query(Q), oracle.query_index(oracle.fit_index(sig, L, k), sig[:16]))
+
+
+def test_bitmap_windows_beyond_one_window(eng):
+    """More rows than one shared-memory bitmap window covers (2^20 ids)."""
+    culsh, core_mod = eng
+    rng = np.random.RandomState(8)
+    n, d, L, k = (1 << 20) + 300000, 8, 3, 3
+    X = rng.randn(n, d).astype(np.float32)
+    model = culsh.RPLSH(L, k, seed=6).fit(X)
+    core = core_mod.RPLSHCore(L, k, 6)
+    sig = _sig_matrix(core.hash(X, model.index))
+    oidx = oracle.fit_index(sig, L, k)
+    assert np.array_equal(model.index.get_candidate_indices(), oidx.candidate_indices)
+    sel = [0, 5, n - 1, n // 2]
+    _assert_candidates_equal(model.query(X[sel]), oracle.query_index(oidx, sig[sel]))
+
+
+def test_no_match_and_zero_queries(eng):
+    culsh, _ = eng
+    rng = np.random.RandomState(3)
+    X = rng.randn(200, 16).astype(np.float32)
+    model = culsh.PStableLSH(4, 8, window_size=1, seed=4).fit(X)
+    far = (1000.0 + rng.randn(7, 16)).astype(np.float32)
+    c = model.query(far)
+    assert c.n_queries == 7 and c.n_total_candidates == 0
+    assert np.array_equal(c.get_counts(), np.zeros(7, np.uint64))
+    assert np.array_equal(c.get_offsets(), np.zeros(8, np.uint64))
+    assert c.get_indices().shape == (0,)
+    mixed = np.concatenate([far[:2], X[:3], far[2:4]])
+    m = model.query(mixed)
+    counts = m.get_counts()
+    assert np.all(counts[[0, 1, 5, 6]] == 0) and np.all(counts[2:5] >= 1)
+    z = model.query(np.zeros((0, 16), dtype=np.float32))
+    assert z.n_queries == 0 and z.n_total_candidates == 0
+
+
+def test_all_rows_identical_and_all_distinct(eng):
+    culsh, _ = eng
+    X = np.tile(np.arange(1, 9, dtype=np.float32), (300, 1))
+    model = culsh.RPLSH(3, 5, seed=1).fit(X)
+    assert model.index.n_total_buckets == 3
+    c = model.query(X[:2])
+    assert np.array_equal(c.get_indices(), np.concatenate([np.arange(300), np.arange(300)]))
+    rng = np.random.RandomState(2)
+    Y = rng.randn(64, 30).astype(np.float32)
+    m2 = culsh.RPLSH(2, 60, seed=1).fit(Y)  # 60 bits: all rows distinct, two-word keys
+    assert m2.index.n_total_buckets == 128 and m2.index.key_words == 2
+    c2 = m2.query(Y)
+    assert np.array_equal(c2.get_indices(), np.arange(64))
+
+
+def test_errors_are_python_exceptions(eng):
+    culsh, core_mod = eng
+    X = np.random.RandomState(0).randn(50, 8)
+    m32 = culsh.RPLSH(2, 4, seed=1).fit(X.astype(np.float32))
+    with pytest.raises(RuntimeError, match="float32"):
+        m32._core.query_double(X, 50, m32.index)
+    with pytest.raises(ValueError):
+        m32.query(np.zeros((3, 9), dtype=np.float32))
+    with pytest.raises(TypeError):
+        culsh.RPLSH(2, 4, seed=1).fit(X.astype(np.float16))
+    with pytest.raises(ValueError):
+        culsh.RPLSH(0, 4)
+    with pytest.raises(RuntimeError, match="even"):
+        culsh.RPLSH(1, 1, seed=1).fit(np.zeros((4, 3), dtype=np.float32))
+    with pytest.raises(ValueError):
+        Xs = sp.random(10, 10, density=0.5, format="csr")
+        Xs.indices = Xs.indices.astype(np.int64)
+        Xs.indptr = Xs.indptr.astype(np.int64)
+        culsh.MinHashLSH(2, 2, seed=1).fit(Xs)
+
+
+def test_device_inputs_match_host_inputs(eng):
+    import torch
+    culsh, _ = eng
+    rng = np.random.RandomState(12)
+    X = rng.randn(3000, 48).astype(np.float32)
+    Q = rng.randn(100, 48).astype(np.float32)
+    mh = culsh.RPLSH(8, 8, seed=21).fit(X)
+    md = culsh.RPLSH(8, 8, seed=21).fit(torch.from_numpy(X).cuda())
+    assert np.array_equal(mh.index.get_candidate_indices(), md.index.get_candidate_indices())
+    a = mh.query(Q)
+    b = md.query(torch.from_numpy(Q).cuda())
+    assert np.array_equal(a.get_indices(), b.get_indices())
+    t = b.get_indices(as_torch=True)
+    assert t.is_cuda and np.array_equal(t.cpu().numpy(), a.get_indices())
+    # host input larger than one staging chunk (32 MiB): chunked copy/hash pipeline
+    Xb = rng.randn(300000, 64).astype(np.float32)
+    i1 = culsh.RPLSH(2, 16, seed=3).fit(Xb).index
+    i2 = culsh.RPLSH(2, 16, seed=3).fit(torch.from_numpy(Xb).cuda()).index
+    assert np.array_equal(i1.get_candidate_indices(), i2.get_candidate_indices())
+    assert np.array_equal(i1.get_bucket_signatures(), i2.get_bucket_signatures())
+
+
+# ------------------------------------------------------------------------------------------
+# save / load and the upstream-oracle fixtures
+# ------------------------------------------------------------------------------------------
+def test_save_load_round_trip(eng, tmp_path):
+    culsh, _ = eng
+    rng = np.random.RandomState(1)
+    X = rng.randn(800, 20).astype(np.float32)
+    Q = X[:50]
+    for make, cls in ((lambda: culsh.RPLSH(6, 9, seed=5), culsh.RPLSHModel),
+                      (lambda: culsh.PStableLSH(6, 4, window_size=3, seed=5), culsh.PStableLSHModel)):
+        m = make().fit(X)
+        path = str(tmp_path / "m.npz")
+        m.save(path)
+        m2 = cls.load(path)
+        for attr in ("n_hash_tables", "n_hashes", "n_features"):
+            assert getattr(m, attr) == getattr(m2, attr)
+        for g in ("get_candidate_indices", "get_bucket_signatures", "get_bucket_candidate_offsets",
+                  "get_table_bucket_offsets", "get_projection_matrix"):
+            assert np.array_equal(getattr(m.index, g)(), getattr(m2.index, g)())
+        assert m.index.seed == m2.index.seed and m.index.sig_nbytes == m2.index.sig_nbytes
+        assert np.array_equal(m.query(Q).get_indices(), m2.query(Q).get_indices())
+    Xs = _random_csr(rng, 400, 200, 0.05)
+    m = culsh.MinHashLSH(8, 3, seed=5).fit(Xs)
+    path = str(tmp_path / "mh.npz")
+    m.save(path)
+    m2 = culsh.MinHashLSHModel.load(path)
+    assert np.array_equal(m.index.get_hash_a(), m2.index.get_hash_a())
+    assert np.array_equal(m.index.get_bucket_signatures(), m2.index.get_bucket_signatures())
+    assert np.array_equal(m.query(Xs).get_indices(), m2.query(Xs).get_indices())
+
+
+def _load_fixture_index(core_mod, g, family):
+    L, k = int(g["L"]), int(g["k"])
+    oidx = oracle.fit_index(g["sig_X"], L, k)
+    common = dict(candidate_indices=oidx.candidate_indices, bucket_signatures=oidx.bucket_signatures,
+                  bucket_candidate_offsets=oidx.bucket_candidate_offsets,
+                  table_bucket_offsets=oidx.table_bucket_offsets,
+                  n_total_candidates=len(oidx.candidate_indices), n_total_buckets=oidx.n_total_buckets,
+                  n_hash_tables=L, n_hashes=k, sig_nbytes=oidx.sig_nbytes, seed=0)
+    if family == "rplsh":
+        return core_mod.RPLSHIndex.load_float(projection=g["P"], n_features=g["X"].shape[1], **common)
+    if family == "pslsh":
+        w = int(g["window"])
+        return core_mod.PSLSHIndex.load_float(projection=(g["P"] / w).astype(np.float32),
+                                              bias=(g["b"] / w).astype(np.float32),
+                                              n_features=g["X"].shape[1], window_size=w, **common)
+    return core_mod.MinHashIndex.load(hash_a=g["A"], hash_b=g["B"], n_features=int(g["n_features"]), **common)
+
+
+def test_upstream_python_oracle_fixtures(eng, golden_dir):
+    """Indexes built from the fixtures written by upstream's ref_lsh.py, queried by the CUDA
+    path: candidate lists equal upstream's (dense families: for queries whose signatures have
+    no element inside the rounding band)."""
+    culsh, core_mod = eng
+    g = np.load(os.path.join(golden_dir, "ref_lsh_minhash.npz"))
+    ix = _load_fixture_index(core_mod, g, "minhash")
+    core = core_mod.MinHashCore(int(g["L"]), int(g["k"]), 0)
+    nq = len(g["Q_indptr"]) - 1
+    sig = _sig_matrix(core.hash(g["Q_indices"], g["Q_indptr"], nq, ix))
+    assert np.array_equal(sig, g["sig_Q"])
+    c = core.query(g["Q_indices"], g["Q_indptr"], nq, ix)
+    assert np.array_equal(c.get_offsets(), g["cand_offsets"])
+    assert np.array_equal(c.get_indices(), g["cand_indices"])
+
+    for fam, Core in (("rplsh", core_mod.RPLSHCore), ("pslsh", core_mod.PSLSHCore)):
+        g = np.load(os.path.join(golden_dir, f"ref_lsh_{fam}.npz"))
+        L, k = int(g["L"]), int(g["k"])
+        ix = _load_fixture_index(core_mod, g, fam)
+        core = Core(L, k, 0) if fam == "rplsh" else Core(L, k, int(g["window"]), 0)
+        Q = g["Q"]
+        sig = _sig_matrix(core.hash(Q, ix)).astype(np.int64)
+        same = np.all(sig == g["sig_Q"].astype(np.int64), axis=1)
+        assert same.mean() > 0.9
+        c = core.query_float(Q, len(Q), ix)
+        off, ind = c.get_offsets().astype(np.int64), c.get_indices()
+        roff, rind = g["cand_offsets"].astype(np.int64), g["cand_indices"]
+        for q in np.flatnonzero(same):
+            assert np.array_equal(ind[off[q]:off[q + 1]], rind[roff[q]:roff[q + 1]])
+
+
+def test_shard_merge_equals_unsharded(eng):
+    import torch
+    culsh, core_mod = eng
+    rng = np.random.RandomState(77)
+    n, d, L, k = 6000, 16, 6, 6
+    X = rng.randn(n, d).astype(np.float32)
+    Q = X[rng.randint(0, n, 200)] + 0.01 * rng.randn(200, d).astype(np.float32)
+    whole = culsh.RPLSH(L, k, seed=13).fit(X).query(Q)
+    for shards in (2, 3, 8):
+        per = -(-n // shards)
+        keep, ip, op, bases = [], [], [], []
+        for r in range(shards):
+            lo, hi = r * per, min(n, (r + 1) * per)
+            c = culsh.RPLSH(L, k, seed=13).fit(X[lo:hi]).query(Q)
+            keep.append(c)
+            a, _, o = c.device_pointers()
+            ip.append(a)
+            op.append(o)
+            bases.append(lo)
+        merged = core_mod.merge_shard_candidates(ip, op, bases, len(Q))
+        assert np.array_equal(merged.get_indices(), whole.get_indices())
+        assert np.array_equal(merged.get_offsets(), whole.get_offsets())
+        assert np.array_equal(merged.get_counts(), whole.get_counts())
