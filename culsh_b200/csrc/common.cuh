@@ -54,7 +54,16 @@ struct Error : public std::runtime_error {
                                (int)s__, __FILE__, __LINE__);                               \
     } while (0)
 
-#define KERNEL_CHECK() CU_CHECK(cudaGetLastError())
+// counts this library's kernel launches (reported per call in culsh_stats.launches)
+inline int& launch_counter() {
+    static thread_local int n = 0;
+    return n;
+}
+#define KERNEL_CHECK()                     \
+    do {                                   \
+        ++::culsh_b200::launch_counter();  \
+        CU_CHECK(cudaGetLastError());      \
+    } while (0)
 
 inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
 

@@ -82,7 +82,12 @@ struct StageTimer {
     int next = 0;
     explicit StageTimer(const CtxPtr& ctx) : c(ctx) {}
     void mark() {
-        if (c->profiling && next < 8) cudaEventRecord(c->ev[next++], c->stream);
+        if (c->profiling && next < 7) cudaEventRecord(c->ev[next++], c->stream);
+    }
+    float since_scatter_start(int b) const {  // ev[7] is recorded by the sort driver
+        float ms = 0.f;
+        if (c->profiling && b < next) cudaEventElapsedTime(&ms, c->ev[7], c->ev[b]);
+        return ms;
     }
     float between(int a, int b) const {
         float ms = 0.f;
@@ -361,6 +366,7 @@ template <typename HashFn>
 void fit_common(culsh_index& ix, HashFn&& hash_fn, DevBuf<int32_t>* item_to_bucket) {
     const CtxPtr& c = ix.ctx;
     c->stats = culsh_stats{};
+    launch_counter() = 0;
     int eb = ix.family == CULSH_PSLSH ? 1 : (ix.family == CULSH_MINHASH ? 4 : 0);
     const size_t items = (size_t)ix.n * ix.L;
     while (true) {
@@ -384,6 +390,7 @@ void fit_common(culsh_index& ix, HashFn&& hash_fn, DevBuf<int32_t>* item_to_buck
         check_error_word(err);
         c->stats.hash_ms = tm.between(0, 1);
         c->stats.sort_ms = tm.between(1, 2);
+        c->stats.scatter_ms = tm.since_scatter_start(2);
         c->stats.build_ms = tm.between(2, 3);
         c->stats.total_ms = tm.between(0, 3);
         break;
@@ -609,6 +616,7 @@ void query_dense(culsh_handle* h, int family, const T* Q, int n_q, const culsh_i
     DeviceGuard g(h->ctx->device);
     const CtxPtr& c = ix->ctx;
     c->stats = culsh_stats{};
+    launch_counter() = 0;
     auto res = std::make_unique<culsh_candidates>();
     if (n_q == 0) {
         empty_result(c, *res);
@@ -701,6 +709,7 @@ int culsh_get_stats(const culsh_handle* h, culsh_stats* out) {
     return guarded([&] {
         if (!h || !out) fail(CULSH_ERR_INVALID, "null argument");
         *out = h->ctx->stats;
+        out->launches = launch_counter();
     });
 }
 
@@ -796,6 +805,7 @@ int culsh_minhash_query(culsh_handle* h, const int32_t* indices, const int32_t* 
         DeviceGuard g(h->ctx->device);
         const CtxPtr& c = ix->ctx;
         c->stats = culsh_stats{};
+        launch_counter() = 0;
         auto res = std::make_unique<culsh_candidates>();
         if (n_q == 0) {
             empty_result(c, *res);

@@ -314,6 +314,7 @@ inline int radix_sort_tables_nw(const CtxPtr& c, uint32_t* keys[2], uint32_t* va
     KERNEL_CHECK();
     radix_bin_prefix_kernel<<<(unsigned)(L * KB), 256, 0, s>>>(ghist);
     KERNEL_CHECK();
+    if (c->profiling) cudaEventRecord(c->ev[7], s);  // start of the scatter passes
     auto k_first = radix_pass_kernel<NW, true>;
     auto k_next = radix_pass_kernel<NW, false>;
     CU_CHECK(cudaFuncSetAttribute(k_first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
