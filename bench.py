@@ -34,7 +34,7 @@ sys.path.insert(0, ROOT)
 
 N_ROWS, N_QUERIES, N_FEATURES = 1_000_000, 10_000, 128
 N_TABLES, N_HASHES, SEED = 32, 16, 0
-WORKLOAD = "RPLSH 1Mx128 fp32 SIFT-shaped synthetic, 32 tables x 16 hashes, 10k queries, batch 10k"
+WORKLOAD = "RPLSH 1Mx128 fp32 SIFT-shaped synthetic, 32 tables x 16 hashes, 10k queries, batch 10k"  # at the default --rows/--queries
 
 
 def load_peaks():
@@ -238,16 +238,18 @@ def run_ours(args):
     clocks = sampler.stop()
 
     # end to end: pinned host arrays in, CSR read back
-    for _ in range(min(args.warmup, 2)):
-        step(Xh_np, Qh_np, True)
-    barrier(torch, world)
-    t0 = time.perf_counter()
     d2h = 0
-    for _ in range(args.steps):
-        _, _, b = step(Xh_np, Qh_np, True)
-        d2h = max(d2h, b)
-    barrier(torch, world)
-    t_e2e = max_over_ranks(torch, time.perf_counter() - t0, world, device)
+    t_e2e = float("nan")
+    if not args.skip_e2e:
+        for _ in range(min(args.warmup, 2)):
+            step(Xh_np, Qh_np, True)
+        barrier(torch, world)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            _, _, b = step(Xh_np, Qh_np, True)
+            d2h = max(d2h, b)
+        barrier(torch, world)
+        t_e2e = max_over_ranks(torch, time.perf_counter() - t0, world, device)
 
     if rank != 0:
         return
@@ -263,7 +265,7 @@ def run_ours(args):
     passes = max(1, sf["sort_passes"])
     items = sf["n_items"]
     kb = 4 * sf["key_words"]
-    tf32 = measure_tf32_peak(torch, device)
+    tf32 = measure_tf32_peak(torch, device) if not args.skip_cpu else 690.0
     flops = 2.0 * N_ROWS * N_FEATURES * N_TABLES * N_HASHES
     proj = {"bound": "tensor", "achieved": flops / (hash_ms * 1e-3) / 1e12,
             "peak": tf32 / 3.0, "unit": "TFLOP/s",
@@ -306,7 +308,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": int(Xh_np.nbytes + Qh_np.nbytes), "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": launches, "clocks": clocks,
     }
-    if world == 1:
+    if world == 1 and not args.skip_cpu:
         line["cpu_baseline"] = cpu_baseline()
     print(json.dumps(line))
 
@@ -412,15 +414,21 @@ def run_reference(args):
 
 
 def main():
+    global N_ROWS, N_QUERIES
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--rows", type=int, default=N_ROWS, help="rows per GPU (default: the 1M-row workload)")
+    ap.add_argument("--queries", type=int, default=N_QUERIES)
+    ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: no host-input leg")
+    ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: no CPU baseline leg")
     ap.add_argument("--reference-cpu", action="store_true",
                     help="reference arm: time the NumPy restatement on the host cores instead of "
                          "upstream's CUDA build")
     args = ap.parse_args()
+    N_ROWS, N_QUERIES = args.rows, args.queries
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

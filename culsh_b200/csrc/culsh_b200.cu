@@ -199,7 +199,7 @@ void generate_params(culsh_index& ix) {
 // Hash dense rows (host or device memory) into keys[L][n_total][NW] at row_offset.
 template <typename T>
 void hash_dense(const culsh_index& ix, const KeySpec& ks, const T* X, int n, uint32_t* keys,
-                uint8_t* ovf_rows, int n_total, int row_offset) {
+                uint8_t* ovf_rows, int n_total, int row_offset, bool allow_fallback = false) {
     const CtxPtr& c = ix.ctx;
     if (n == 0) return;
     const T* P = reinterpret_cast<const T*>(ix.p0.p);
@@ -212,7 +212,7 @@ void hash_dense(const culsh_index& ix, const KeySpec& ks, const T* X, int n, uin
                                    reinterpret_cast<const float*>(bias), rows, ix.d, ix.L, ix.k, ks,
                                    keys, ovf_rows, off, n_total);
         if (!tc) {
-            if (c->projection_path == 2)
+            if (c->projection_path == 2 && !allow_fallback)
                 fail(CULSH_ERR_UNSUPPORTED, "tensor-core projection path is not available for this shape");
             launch_project_simt<T>(c, s, ix.family, Xd, P, bias, rows, ix.d, ix.L, ix.k, ks, keys,
                                    ovf_rows, off, n_total);
@@ -388,6 +388,7 @@ void fit_common(culsh_index& ix, HashFn&& hash_fn, DevBuf<int32_t>* item_to_buck
             continue;
         }
         check_error_word(err);
+        CU_CHECK(cudaStreamSynchronize(c->stream));  // the stage events must have completed
         c->stats.hash_ms = tm.between(0, 1);
         c->stats.sort_ms = tm.between(1, 2);
         c->stats.scatter_ms = tm.since_scatter_start(2);
@@ -401,7 +402,7 @@ void fit_common(culsh_index& ix, HashFn&& hash_fn, DevBuf<int32_t>* item_to_buck
 // Query from matched bucket ids (matched[q*L + t])
 // -----------------------------------------------------------------------------------------
 int bitmap_window_bits(const CtxPtr& c, int n_rows) {
-    size_t fixed = 3 * BM_MAX_L * sizeof(int) + 1024;
+    size_t fixed = bitmap_smem_bytes(0) + 1024;
     size_t max_bits = ((c->smem_optin > fixed ? c->smem_optin - fixed : 0) * 8) / 1024 * 1024;
     size_t want = ((size_t)n_rows + 1023) / 1024 * 1024;
     size_t cap = std::min<size_t>(max_bits, (size_t)1 << 20);
@@ -448,7 +449,7 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     }
     if (nb) {
         int wbits = bitmap_window_bits(c, ix.n);
-        size_t smem = (size_t)wbits / 8 + 3 * BM_MAX_L * sizeof(int);
+        size_t smem = bitmap_smem_bytes(wbits);
         CU_CHECK(cudaFuncSetAttribute(dedupe_bitmap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dedupe_bitmap_kernel<<<nb, BM_THREADS, smem, s>>>(big_list.p, matched, ix.bucket_offsets.p,
                                                           ix.cand.p, raw_off.p, L, ix.n, wbits, tmp.p,
@@ -548,7 +549,7 @@ void empty_result(const CtxPtr& c, culsh_candidates& out) {
 // -----------------------------------------------------------------------------------------
 void prepare_tc_split(culsh_index& ix) {
     if (ix.family == CULSH_MINHASH || ix.is_double) return;
-    prepare_project_tc(ix.ctx, reinterpret_cast<const float*>(ix.p0.p), ix.L * ix.k, ix.d, ix.p_split);
+    prepare_project_tc(ix.ctx, reinterpret_cast<const float*>(ix.p0.p), ix.L * ix.k, ix.d, ix.L, ix.k, ix.p_split);
 }
 
 template <typename T>
@@ -658,7 +659,6 @@ std::unique_ptr<culsh_index> new_minhash_index(culsh_handle* h, int n, int d, in
     return ix;
 }
 
-size_t copy_bytes_or_zero(size_t n, size_t esz) { return n * esz; }
 
 }  // namespace
 
@@ -867,9 +867,9 @@ int culsh_index_hash_dense(culsh_handle* h, const culsh_index* ix, const void* X
         size_t items = (size_t)n_rows * ix->L;
         DevBuf<uint32_t> keys(c, items * ks.key_words);
         if (ix->is_double)
-            hash_dense<double>(*ix, ks, static_cast<const double*>(X), n_rows, keys.p, nullptr, n_rows, 0);
+            hash_dense<double>(*ix, ks, static_cast<const double*>(X), n_rows, keys.p, nullptr, n_rows, 0, true);
         else
-            hash_dense<float>(*ix, ks, static_cast<const float*>(X), n_rows, keys.p, nullptr, n_rows, 0);
+            hash_dense<float>(*ix, ks, static_cast<const float*>(X), n_rows, keys.p, nullptr, n_rows, 0, true);
         unpack_and_copy(c, keys.p, items, ks, sig_out);
     });
 }

@@ -1,16 +1,534 @@
-// Tensor-core projection path (placeholder until the tcgen05 kernel lands).
+// Projection hash on the 5th-generation tensor cores: X . P^T as a 3xTF32 split GEMM
+// (tcgen05.mma kind::tf32, fp32 accumulators in TMEM, operands staged in shared memory by
+// TMA) with the sign-test / floor quantisation and the key packing fused into the epilogue,
+// so only packed signatures reach HBM.  Replaces cublasSgemm + compute_signatures_kernel
+// (rplsh/hash.cuh:24-48, 93-129) and + bias_floor_reorder_kernel (pslsh/hash.cuh:26-47,
+// 105-142) for fp32 inputs.
+//
+// 3xTF32: x = xh + xl with xh = x & 0xFFFFE000 (the 19 bits a TF32 operand keeps) and
+// xl = x - xh (exact in fp32); likewise p = ph + pl.  x.p ~= xh.ph + xh.pl + xl.ph, three
+// MMAs into one fp32 accumulator; the dropped xl.pl term is below 2^-22 relative.  P is split
+// once per index (prepare_project_tc); X tiles are split in shared memory by a transform
+// warpgroup after the TMA load lands (element-wise, so the TMA swizzle is preserved).  When a
+// tile's xl is identically zero (e.g. integer-valued data below 2^11) its third MMA is skipped.
+//
+// One persistent CTA per SM, 10 warps:
+//   warp 0      TMA producer (one lane)            full[s]  <- TMA bytes
+//   warp 1      MMA issuer (one lane), TMEM owner  ready[s] <- transform, empty[s] <- MMA done
+//   warps 2-5   split X tiles into hi / lo         acc_full[b] <- MMA done, acc_empty[b] <- epilogue
+//   warps 6-9   epilogue: tcgen05.ld -> quantise -> pack -> store
+// A work unit is (128-row tile, chunk of whole tables with <= 256 hash columns); two TMEM
+// accumulators of 256 columns alternate so the epilogue of one unit overlaps the MMAs of the
+// next.  Every mbarrier wait is bounded: when one runs out the CTA raises an abort flag,
+// records DEV_ERR_MBAR_TIMEOUT, and all roles leave their loops; TMEM is released at the end.
+// No TMA load uses cluster multicast.
 #pragma once
+
+#include <cuda.h>
 
 #include "common.cuh"
 
 namespace culsh_b200 {
 
-inline void prepare_project_tc(const CtxPtr&, const float*, int, int, DevBuf<uint8_t>&) {}
+constexpr int TC_BM = 128;          // rows per tile (MMA M)
+constexpr int TC_BN = 256;          // accumulator columns (max MMA N)
+constexpr int TC_THREADS = 320;
+constexpr int TC_TRANSFORM_THREADS = 128;
+constexpr int TC_EPI_THREADS = 128;
+constexpr long long TC_WAIT_CYCLES = 4000000000ll;  // ~2 s at 2 GHz
 
-inline bool launch_project_tc(const CtxPtr&, cudaStream_t, int, const float*, const float*,
-                              const uint8_t*, const float*, int, int, int, int, const KeySpec&,
-                              uint32_t*, uint8_t*, int, int) {
-    return false;
+template <int KBLK>
+struct TcCfg {
+    static constexpr int STAGES = KBLK == 32 ? 2 : 4;
+    static constexpr int SWIZZLE_BYTES = KBLK * 4;              // 128 or 64
+    static constexpr int X_BYTES = TC_BM * KBLK * 4;
+    static constexpr int P_BYTES = TC_BN * KBLK * 4;
+    static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * P_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*barriers*/ + 1024 /*alignment slack*/;
+};
+
+struct TcArgs {
+    uint32_t* keys;
+    uint8_t* ovf_rows;
+    int* d_error;
+    const float* bias;
+    int n, d, L, k;
+    int n_tiles, n_chunks, tables_per_chunk, n_mma, n_kblocks;
+    int key_words, elem_bytes, family;
+    int row_offset, n_total;
+};
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting (the caller leaves its loop).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* d_error) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > TC_WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicOr(d_error, DEV_ERR_MBAR_TIMEOUT);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x,
+                                            int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are one swizzle span wide
+// (KBLK fp32 = 128 B or 64 B): 8-row groups follow each other every 8 * span bytes.
+template <int KBLK>
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    constexpr uint64_t SBO = (8u * KBLK * 4u) >> 4;
+    constexpr uint64_t LAYOUT = KBLK == 32 ? 2ull /*SWIZZLE_128B*/ : 4ull /*SWIZZLE_64B*/;
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (SBO << 32) | (1ull << 46) | (LAYOUT << 61);
+}
+
+// kind::tf32, fp32 accumulate, both operands K-major: c_format=F32 (bit 4), a/b format TF32 (=2)
+__device__ __forceinline__ uint32_t make_idesc_tf32(int M, int N) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// 256-bit shift register that receives the key bytes / bits of one table, first element most
+// significant; after k elements it holds the right-aligned key (w[0] most significant).
+struct KeyReg {
+    uint64_t w[4];
+    __device__ __forceinline__ void clear() { w[0] = w[1] = w[2] = w[3] = 0; }
+    __device__ __forceinline__ void push(uint32_t v, int bits) {  // bits in {1, 8, 16, 32}
+        w[0] = (w[0] << bits) | (w[1] >> (64 - bits));
+        w[1] = (w[1] << bits) | (w[2] >> (64 - bits));
+        w[2] = (w[2] << bits) | (w[3] >> (64 - bits));
+        w[3] = (w[3] << bits) | (uint64_t)v;
+    }
+    __device__ __forceinline__ void store(uint32_t* dst, int NW) const {
+        if (NW == 1) { dst[0] = (uint32_t)w[3]; }
+        else if (NW == 2) { *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)(w[3] >> 32), (uint32_t)w[3]); }
+        else if (NW == 4) {
+            *reinterpret_cast<uint4*>(dst) =
+                make_uint4((uint32_t)(w[2] >> 32), (uint32_t)w[2], (uint32_t)(w[3] >> 32), (uint32_t)w[3]);
+        } else {
+            reinterpret_cast<uint4*>(dst)[0] =
+                make_uint4((uint32_t)(w[0] >> 32), (uint32_t)w[0], (uint32_t)(w[1] >> 32), (uint32_t)w[1]);
+            reinterpret_cast<uint4*>(dst)[1] =
+                make_uint4((uint32_t)(w[2] >> 32), (uint32_t)w[2], (uint32_t)(w[3] >> 32), (uint32_t)w[3]);
+        }
+    }
+};
+
+template <int KBLK>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmP, TcArgs a) {
+    using Cfg = TcCfg<KBLK>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    auto xh = [&](int s) { return reinterpret_cast<float*>(base + (size_t)s * Cfg::STAGE_BYTES); };
+    auto xl = [&](int s) { return reinterpret_cast<float*>(base + (size_t)s * Cfg::STAGE_BYTES + Cfg::X_BYTES); };
+    auto ph = [&](int s) { return reinterpret_cast<float*>(base + (size_t)s * Cfg::STAGE_BYTES + 2 * Cfg::X_BYTES); };
+    auto pl = [&](int s) {
+        return reinterpret_cast<float*>(base + (size_t)s * Cfg::STAGE_BYTES + 2 * Cfg::X_BYTES + Cfg::P_BYTES);
+    };
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + (size_t)STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full = bars;                   // [STAGES]
+    uint64_t* ready = bars + STAGES;         // [STAGES]
+    uint64_t* empty = bars + 2 * STAGES;     // [STAGES]
+    uint64_t* acc_full = bars + 3 * STAGES;  // [2]
+    uint64_t* acc_empty = acc_full + 2;      // [2]
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+    volatile int* s_lo_flag = s_abort + 1;   // [STAGES]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&ready[s], TC_TRANSFORM_THREADS);
+            mbar_init(&empty[s], 1);
+            s_lo_flag[s] = 0;
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], TC_EPI_THREADS);
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // whole warp: allocate all 512 TMEM columns (one CTA per SM)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    const int n_units_per_tile = a.n_chunks;
+    const uint32_t stage_tx = (uint32_t)(Cfg::X_BYTES + 2 * a.n_mma * KBLK * 4);
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool live = true;
+            for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
+                for (int c = 0; c < n_units_per_tile && live; ++c) {
+                    for (int kb = 0; kb < a.n_kblocks; ++kb, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t phs = (it / STAGES) & 1;
+                        if (!mbar_wait(&empty[s], phs ^ 1, s_abort, a.d_error)) { live = false; break; }
+                        mbar_expect_tx(&full[s], stage_tx);
+                        tma_load_2d(xh(s), &tmX, &full[s], kb * KBLK, tile * TC_BM);
+                        tma_load_2d(ph(s), &tmP, &full[s], kb * KBLK, (c * 2 + 0) * a.n_mma);
+                        tma_load_2d(pl(s), &tmP, &full[s], kb * KBLK, (c * 2 + 1) * a.n_mma);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_tf32(TC_BM, a.n_mma);
+            uint32_t it = 0, u = 0;
+            bool live = true;
+            for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
+                for (int c = 0; c < n_units_per_tile && live; ++c, ++u) {
+                    const int ab = u & 1;
+                    const uint32_t aph = (u >> 1) & 1;
+                    if (!mbar_wait(&acc_empty[ab], aph ^ 1, s_abort, a.d_error)) { live = false; break; }
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(ab * TC_BN);
+                    for (int kb = 0; kb < a.n_kblocks; ++kb, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t phs = (it / STAGES) & 1;
+                        if (!mbar_wait(&full[s], phs, s_abort, a.d_error) ||
+                            !mbar_wait(&ready[s], phs, s_abort, a.d_error)) { live = false; break; }
+                        tc_fence_after();
+                        const int use_lo = s_lo_flag[s];
+                        s_lo_flag[s] = 0;
+                        const uint64_t dxh = make_smem_desc<KBLK>(smem_u32(xh(s)));
+                        const uint64_t dxl = make_smem_desc<KBLK>(smem_u32(xl(s)));
+                        const uint64_t dph = make_smem_desc<KBLK>(smem_u32(ph(s)));
+                        const uint64_t dpl = make_smem_desc<KBLK>(smem_u32(pl(s)));
+#pragma unroll
+                        for (int ks = 0; ks < KBLK / 8; ++ks) {
+                            const uint64_t adv = (uint64_t)(ks * 2);  // 32 bytes per K step, in 16-byte units
+                            tc_mma_tf32(d_tmem, dxh + adv, dpl + adv, idesc, (kb | ks) != 0);
+                            if (use_lo) tc_mma_tf32(d_tmem, dxl + adv, dph + adv, idesc, 1u);
+                            tc_mma_tf32(d_tmem, dxh + adv, dph + adv, idesc, 1u);
+                        }
+                        tc_commit(&empty[s]);  // stage reusable once these MMAs have read it
+                    }
+                    if (live) tc_commit(&acc_full[ab]);
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- transform: split X tiles into hi / lo ----------------
+        const int tt = threadIdx.x - 64;  // 0..127
+        uint32_t it = 0;
+        bool live = true;
+        for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
+            for (int c = 0; c < n_units_per_tile && live; ++c) {
+                for (int kb = 0; kb < a.n_kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phs = (it / STAGES) & 1;
+                    if (!mbar_wait(&full[s], phs, s_abort, a.d_error)) { live = false; break; }
+                    uint4* h4 = reinterpret_cast<uint4*>(xh(s));
+                    uint4* l4 = reinterpret_cast<uint4*>(xl(s));
+                    bool any_lo = false;
+#pragma unroll
+                    for (int j = 0; j < Cfg::X_BYTES / 16 / TC_TRANSFORM_THREADS; ++j) {
+                        const int idx = tt + j * TC_TRANSFORM_THREADS;
+                        uint4 v = h4[idx];
+                        uint4 hi = make_uint4(v.x & 0xFFFFE000u, v.y & 0xFFFFE000u, v.z & 0xFFFFE000u,
+                                              v.w & 0xFFFFE000u);
+                        float lx = __uint_as_float(v.x) - __uint_as_float(hi.x);
+                        float ly = __uint_as_float(v.y) - __uint_as_float(hi.y);
+                        float lz = __uint_as_float(v.z) - __uint_as_float(hi.z);
+                        float lw = __uint_as_float(v.w) - __uint_as_float(hi.w);
+                        any_lo |= (lx != 0.f) | (ly != 0.f) | (lz != 0.f) | (lw != 0.f);
+                        h4[idx] = hi;
+                        l4[idx] = make_uint4(__float_as_uint(lx), __float_as_uint(ly), __float_as_uint(lz),
+                                             __float_as_uint(lw));
+                    }
+                    if (any_lo) s_lo_flag[s] = 1;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_arrive(&ready[s]);
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter ...
+        const int NW = a.key_words;
+        const int k = a.k;
+        const int bits = a.family == CULSH_RPLSH ? 1 : 8 * a.elem_bytes;
+        const int lim = a.elem_bytes == 1 ? 128 : (a.elem_bytes == 2 ? 32768 : 0);
+        uint32_t u = 0;
+        bool live = true;
+        bool any_ovf = false;
+        for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
+            const int row = tile * TC_BM + quarter * 32 + lane;
+            const bool row_ok = row < a.n;
+            for (int c = 0; c < n_units_per_tile && live; ++c, ++u) {
+                const int ab = u & 1;
+                const uint32_t aph = (u >> 1) & 1;
+                if (!mbar_wait(&acc_full[ab], aph, s_abort, a.d_error)) { live = false; break; }
+                tc_fence_after();
+                const int t0 = c * a.tables_per_chunk;
+                const int tables_here = min(a.tables_per_chunk, a.L - t0);
+                const int cols = tables_here * k;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * TC_BN);
+                KeyReg reg;
+                reg.clear();
+                int in_table = 0, tbl = t0;
+                bool ovf = false;
+                for (int g0 = 0; g0 < cols; g0 += 16) {
+                    uint32_t r[16];
+                    tc_ld16(taddr + (uint32_t)g0, r);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int col = g0 + j;
+                        if (col < cols) {
+                            const float v = __uint_as_float(r[j]);
+                            uint32_t e;
+                            if (a.family == CULSH_RPLSH) {
+                                e = (r[j] >> 31) ^ 1u;  // sign bit clear -> 1 (rplsh/hash.cuh:47)
+                            } else {
+                                const int q = (int)floorf(v + a.bias[t0 * k + col]);  // pslsh/hash.cuh:46
+                                if (lim && (q < -lim || q >= lim)) ovf = true;
+                                const uint32_t uq = (uint32_t)q;
+                                e = a.elem_bytes == 1 ? (uq & 0xFFu)
+                                    : a.elem_bytes == 2 ? (((uq & 0xFFu) << 8) | ((uq >> 8) & 0xFFu))
+                                                        : __byte_perm(uq, 0, 0x0123);
+                            }
+                            reg.push(e, bits);
+                            if (++in_table == k) {
+                                if (row_ok) {
+                                    const size_t item = (size_t)tbl * a.n_total + a.row_offset + row;
+                                    reg.store(a.keys + item * NW, NW);
+                                    if (a.family == CULSH_PSLSH) {
+                                        if (a.ovf_rows) a.ovf_rows[item] = ovf ? 1 : 0;
+                                        else any_ovf |= ovf;
+                                    }
+                                }
+                                reg.clear();
+                                in_table = 0;
+                                ovf = false;
+                                ++tbl;
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&acc_empty[ab]);
+            }
+        }
+        if (any_ovf) atomicOr(a.d_error, DEV_ERR_NARROW_OVERFLOW);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+struct TcPlan {
+    int kblk, d_pad, n_chunks, tables_per_chunk, n_mma;
+};
+
+inline int tc_kblk_choice() {
+    static int v = [] {
+        const char* e = getenv("CULSH_TC_KBLK");
+        int k = e ? atoi(e) : 16;
+        return k == 32 ? 32 : 16;
+    }();
+    return v;
+}
+
+inline bool tc_plan(int d, int L, int k, TcPlan& p) {
+    if (k > TC_BN || d % 4 != 0) return false;
+    p.kblk = tc_kblk_choice();
+    p.d_pad = (d + p.kblk - 1) / p.kblk * p.kblk;
+    p.tables_per_chunk = std::min(L, TC_BN / k);
+    p.n_chunks = (L + p.tables_per_chunk - 1) / p.tables_per_chunk;
+    p.n_mma = (p.tables_per_chunk * k + 15) / 16 * 16;
+    return true;
+}
+
+// P_split layout: [chunk][hi | lo][n_mma rows][d_pad] fp32, zero where padded.
+__global__ void split_projection_kernel(const float* __restrict__ P, int H, int d, int k, int d_pad,
+                                        int tables_per_chunk, int n_mma, int n_chunks, float* __restrict__ out) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t per_part = (size_t)n_mma * d_pad;
+    size_t total = (size_t)n_chunks * 2 * per_part;
+    if (idx >= total) return;
+    int c = (int)(idx / (2 * per_part));
+    size_t rem = idx - (size_t)c * 2 * per_part;
+    int part = (int)(rem / per_part);
+    size_t rr = rem - (size_t)part * per_part;
+    int r = (int)(rr / d_pad), col = (int)(rr - (size_t)r * d_pad);
+    int h = c * tables_per_chunk * k + r;
+    float v = 0.f;
+    if (r < tables_per_chunk * k && h < H && col < d) {
+        float p = P[(size_t)h * d + col];
+        float hi = __uint_as_float(__float_as_uint(p) & 0xFFFFE000u);
+        v = part == 0 ? hi : p - hi;
+    }
+    out[idx] = v;
+}
+
+inline void prepare_project_tc(const CtxPtr& c, const float* P, int H, int d, int L, int k,
+                               DevBuf<uint8_t>& out) {
+    TcPlan p;
+    if (c->projection_path == 1 || !tc_plan(d, L, k, p)) return;
+    size_t total = (size_t)p.n_chunks * 2 * p.n_mma * p.d_pad;
+    out.alloc(c, total * sizeof(float));
+    split_projection_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, c->stream>>>(
+        P, H, d, k, p.d_pad, p.tables_per_chunk, p.n_mma, p.n_chunks, reinterpret_cast<float*>(out.p));
+    KERNEL_CHECK();
+}
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+inline PFN_encodeTiled get_encode_tiled() {
+    static PFN_encodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        cudaGetLastError();
+        return reinterpret_cast<PFN_encodeTiled>(p);
+    }();
+    return fn;
+}
+
+inline bool make_map_2d(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+                        uint32_t box_inner, uint32_t box_rows, int kblk) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     kblk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// Returns false when this shape / pointer cannot take the tensor-core path (caller falls back).
+inline bool launch_project_tc(const CtxPtr& c, cudaStream_t stream, int family, const float* X, const float* P,
+                              const uint8_t* p_split, const float* bias, int n, int d, int L, int k,
+                              const KeySpec& ks, uint32_t* keys, uint8_t* ovf_rows, int row_offset,
+                              int n_total) {
+    (void)P;
+    TcPlan p;
+    if (!p_split || !tc_plan(d, L, k, p)) return false;
+    if (ks.key_words > 8) return false;                       // key wider than the 256-bit packer
+    if ((reinterpret_cast<uintptr_t>(X) & 15) != 0) return false;  // TMA base alignment
+    if (n <= 0) return true;
+    CUtensorMap tmX, tmP;
+    if (!make_map_2d(&tmX, X, (uint64_t)d, (uint64_t)n, (uint64_t)d * 4, (uint32_t)p.kblk, TC_BM, p.kblk))
+        return false;
+    if (!make_map_2d(&tmP, p_split, (uint64_t)p.d_pad, (uint64_t)p.n_chunks * 2 * p.n_mma, (uint64_t)p.d_pad * 4,
+                     (uint32_t)p.kblk, (uint32_t)p.n_mma, p.kblk))
+        return false;
+    TcArgs a{};
+    a.keys = keys; a.ovf_rows = ovf_rows; a.d_error = c->d_error; a.bias = bias;
+    a.n = n; a.d = d; a.L = L; a.k = k;
+    a.n_tiles = (int)ceil_div(n, TC_BM);
+    a.n_chunks = p.n_chunks; a.tables_per_chunk = p.tables_per_chunk; a.n_mma = p.n_mma;
+    a.n_kblocks = p.d_pad / p.kblk;
+    a.key_words = ks.key_words; a.elem_bytes = ks.elem_bytes; a.family = family;
+    a.row_offset = row_offset; a.n_total = n_total;
+    int grid = std::min(a.n_tiles, c->sm_count);
+    if (p.kblk == 32) {
+        size_t smem = TcCfg<32>::SMEM;
+        if (smem > c->smem_optin) return false;
+        CU_CHECK(cudaFuncSetAttribute(project_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        project_tc_kernel<32><<<grid, TC_THREADS, smem, stream>>>(tmX, tmP, a);
+    } else {
+        size_t smem = TcCfg<16>::SMEM;
+        if (smem > c->smem_optin) return false;
+        CU_CHECK(cudaFuncSetAttribute(project_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        project_tc_kernel<16><<<grid, TC_THREADS, smem, stream>>>(tmX, tmP, a);
+    }
+    KERNEL_CHECK();
+    return true;
 }
 
 }  // namespace culsh_b200

@@ -145,9 +145,10 @@ dedupe_small_kernel(const int32_t* __restrict__ matched, const int32_t* __restri
 // every bucket list is ascending each window's slice of a list is found by binary search.
 // A pop-count scan of the bitmap then emits the window's ids sorted and unique.
 // ---------------------------------------------------------------------------------------
-constexpr int BM_THREADS = 512;
+constexpr int BM_THREADS = 1024;
 constexpr int BM_WARPS = BM_THREADS / 32;
-constexpr int BM_MAX_L = 1024;  // lists kept in shared memory
+constexpr int BM_MAX_L = 1024;   // lists kept in shared memory
+constexpr int BM_STAGE = 256;    // ids staged per warp before a coalesced flush
 
 __device__ __forceinline__ int lower_bound_i32(const int32_t* __restrict__ a, int lo, int hi, int32_t v) {
     while (lo < hi) {
@@ -157,16 +158,21 @@ __device__ __forceinline__ int lower_bound_i32(const int32_t* __restrict__ a, in
     return lo;
 }
 
+inline size_t bitmap_smem_bytes(int window_bits) {
+    return (size_t)window_bits / 8 + 3 * BM_MAX_L * sizeof(int) + (size_t)BM_WARPS * BM_STAGE * sizeof(int32_t);
+}
+
 __global__ void __launch_bounds__(BM_THREADS)
 dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __restrict__ matched,
                      const int32_t* __restrict__ bucket_offsets, const int32_t* __restrict__ cand,
                      const uint64_t* __restrict__ raw_off, int L, int n_rows, int window_bits,
                      int32_t* __restrict__ tmp, uint64_t* __restrict__ uniq_cnt) {
     extern __shared__ __align__(16) uint32_t s_dyn[];
-    uint32_t* bitmap = s_dyn;                                // [window_bits / 32]
-    int* s_lo = reinterpret_cast<int*>(bitmap + window_bits / 32);  // [Lc] cursor (global position)
-    int* s_hi = s_lo + BM_MAX_L;                              // [Lc] end of list
-    int* s_we = s_hi + BM_MAX_L;                              // [Lc] end of the window's slice
+    uint32_t* bitmap = s_dyn;                                       // [window_bits / 32]
+    int* s_lo = reinterpret_cast<int*>(bitmap + window_bits / 32);  // [Lc] slice start (global position)
+    int* s_hi = s_lo + BM_MAX_L;                                    // [Lc] end of list
+    int* s_we = s_hi + BM_MAX_L;                                    // [Lc] end of the window's slice
+    int32_t* s_stage = reinterpret_cast<int32_t*>(s_we + BM_MAX_L); // [BM_WARPS][BM_STAGE]
     __shared__ uint32_t s_wtot[BM_WARPS];
     __shared__ int s_any;
 
@@ -174,10 +180,11 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
     const int q = (int)big_list[blockIdx.x];
     const int words = window_bits / 32;
     int32_t* out = tmp + raw_off[q];
+    int32_t* stage = s_stage + warp * BM_STAGE;
     uint32_t written = 0;  // uniform across the block
 
-    // L may exceed BM_MAX_L: process tables in groups; groups after the first need the
-    // bitmap of the same window, so the group loop sits inside the window loop.
+    // L may exceed BM_MAX_L: tables are processed in groups inside the window loop, because
+    // every group marks the bitmap of the same window.
     for (int win_lo = 0; win_lo < n_rows; win_lo += window_bits) {
         const int win_hi = min(n_rows, win_lo + window_bits);
         bool cleared = false;
@@ -205,7 +212,8 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
             __syncthreads();  // s_any is rewritten at the top of the next group
             if (!any) continue;  // uniform
             if (!cleared) {
-                for (int w = tid; w < words; w += BM_THREADS) bitmap[w] = 0;
+                uint4* b4 = reinterpret_cast<uint4*>(bitmap);
+                for (int w = tid; w < words / 4; w += BM_THREADS) b4[w] = make_uint4(0, 0, 0, 0);
                 cleared = true;
                 __syncthreads();
             }
@@ -235,26 +243,50 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
             if (i < warp) wbase += x;
             wtotal += x;
         }
-        uint32_t pos = written + wbase;
+        // ---- emit: ids are staged in the warp's slice of shared memory and flushed in
+        // coalesced runs; a 32-word group denser than the stage is written directly ----
+        uint32_t out_pos = written + wbase;  // global position of stage[0]
+        uint32_t fill = 0;
         for (int w0 = w_begin; w0 < w_end; w0 += 32) {
             const int w = w0 + lane;
             uint32_t bits = w < w_end ? bitmap[w] : 0u;
-            uint32_t c = __popc(bits);
+            const uint32_t c = __popc(bits);
             uint32_t inc = c;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
                 if (lane >= o) inc += x;
             }
-            uint32_t o_pos = pos + inc - c;
+            const uint32_t tot = __shfl_sync(0xFFFFFFFFu, inc, 31);
+            if (tot == 0) continue;
             const int32_t id0 = win_lo + w * 32;
-            while (bits) {
-                int b = __ffs(bits) - 1;
-                bits &= bits - 1;
-                out[o_pos++] = id0 + b;
+            if (tot > BM_STAGE || fill + tot > BM_STAGE) {  // flush what is staged
+                __syncwarp();
+                for (uint32_t i = lane; i < fill; i += 32) out[out_pos + i] = stage[i];
+                out_pos += fill;
+                fill = 0;
+                __syncwarp();
             }
-            pos += __shfl_sync(0xFFFFFFFFu, inc, 31);
+            if (tot > BM_STAGE) {
+                uint32_t o_pos = out_pos + inc - c;
+                while (bits) {
+                    int b = __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    out[o_pos++] = id0 + b;
+                }
+                out_pos += tot;
+            } else {
+                uint32_t s_pos = fill + inc - c;
+                while (bits) {
+                    int b = __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    stage[s_pos++] = id0 + b;
+                }
+                fill += tot;
+            }
         }
+        __syncwarp();
+        for (uint32_t i = lane; i < fill; i += 32) out[out_pos + i] = stage[i];
         written += wtotal;
         __syncthreads();
     }

@@ -88,28 +88,19 @@ __global__ void __launch_bounds__(RS_THREADS)
 radix_hist_kernel(const uint32_t* __restrict__ keys, int n, int KB, uint32_t* __restrict__ ghist) {
     extern __shared__ uint32_t sh_hist[];  // [KB][256]
     const int t = blockIdx.y;
-    const int lane = threadIdx.x & 31;
     for (int i = threadIdx.x; i < KB * 256; i += RS_THREADS) sh_hist[i] = 0;
     __syncthreads();
     const int begin = blockIdx.x * RS_HIST_CHUNK;
     const int end = min(n, begin + RS_HIST_CHUNK);
     const int n_words = (KB + 3) / 4;
-    // all lanes of a warp iterate together so the match below is convergent
-    for (int i0 = begin + (threadIdx.x & ~31); i0 < end; i0 += RS_THREADS) {
-        const int i = i0 + lane;
-        const bool valid = i < end;
-        const uint32_t* kp = keys + ((size_t)t * n + (valid ? i : begin)) * NW;
+    for (int i = begin + threadIdx.x; i < end; i += RS_THREADS) {
+        const uint32_t* kp = keys + ((size_t)t * n + i) * NW;
         for (int w = 0; w < n_words; ++w) {
-            uint32_t word = kp[NW - 1 - w];
+            const uint32_t word = kp[NW - 1 - w];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                int p = w * 4 + b;
-                if (p < KB) {
-                    uint32_t d = valid ? ((word >> (8 * b)) & 0xFFu) : 0x100u;
-                    uint32_t peers = __match_any_sync(0xFFFFFFFFu, d);
-                    if (valid && (peers & ((1u << lane) - 1)) == 0)
-                        atomicAdd(&sh_hist[p * 256 + d], (uint32_t)__popc(peers));
-                }
+                const int p = w * 4 + b;
+                if (p < KB) atomicAdd(&sh_hist[p * 256 + ((word >> (8 * b)) & 0xFFu)], 1u);
             }
         }
     }
@@ -184,7 +175,7 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
     const int count = min(TILE, n - item0);
     const size_t base = (size_t)t * n + item0;
 
-    // ---- load + rank inside the warp -------------------------------------------------
+    // ---- load (all loads in flight together), then rank inside the warp ---------------
     uint32_t key[IPT][NW];
     uint32_t val[IPT];
     uint16_t rank[IPT];
@@ -192,8 +183,7 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
         const int li = warp * (32 * IPT) + i * 32 + lane;
-        const bool valid = li < count;
-        if (valid) {
+        if (li < count) {
             load_key<NW>(keys_in + (base + li) * NW, key[i]);
             val[i] = FIRST ? (uint32_t)(item0 + li) : vals_in[base + li];
         } else {
@@ -201,6 +191,11 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
             for (int w = 0; w < NW; ++w) key[i][w] = 0;
             val[i] = 0;
         }
+    }
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+        const int li = warp * (32 * IPT) + i * 32 + lane;
+        const bool valid = li < count;
         const uint32_t d = valid ? key_digit<NW>(key[i], p) : 0x100u;
         const uint32_t peers = __match_any_sync(0xFFFFFFFFu, d);
         const uint32_t below = __popc(peers & ((1u << lane) - 1));

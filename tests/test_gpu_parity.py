@@ -30,6 +30,19 @@ def _sig_matrix(sig_lnk):
     return np.ascontiguousarray(sig_lnk.transpose(1, 0, 2)).reshape(n, L * k)
 
 
+def _index_row_signatures(index, fam):
+    """[n][L*k] signatures recovered from a fitted index (bucket signature of every member)."""
+    n, L, s = index.n_samples, index.n_hash_tables, index.sig_nbytes
+    bco = index.get_bucket_candidate_offsets().astype(np.int64)
+    bs = index.get_bucket_signatures().reshape(-1, s)
+    cand = index.get_candidate_indices()
+    bucket_of_item = np.repeat(np.arange(len(bco) - 1), np.diff(bco))
+    raw = np.empty((L, n, s), dtype=np.uint8)
+    raw[np.arange(len(cand)) // n, cand] = bs[bucket_of_item]
+    elem = np.uint8 if fam == "rplsh" else np.int32
+    return np.ascontiguousarray(raw.transpose(1, 0, 2)).view(elem).reshape(n, -1)
+
+
 def _assert_index_equals_oracle(index, sig_nH, L, k):
     want = oracle.fit_index(sig_nH, L, k)
     assert index.n_total_buckets == want.n_total_buckets
@@ -426,3 +439,45 @@ def test_shard_merge_equals_unsharded(eng):
         assert np.array_equal(merged.get_indices(), whole.get_indices())
         assert np.array_equal(merged.get_offsets(), whole.get_offsets())
         assert np.array_equal(merged.get_counts(), whole.get_counts())
+
+
+# ------------------------------------------------------------------------------------------
+# tensor-core projection (tcgen05 3xTF32) against the CUDA-core projection and the oracle
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("fam,n,d,L,k", [("rplsh", 5000, 128, 32, 16), ("rplsh", 1000, 100, 8, 12),
+                                         ("rplsh", 3333, 256, 48, 24), ("rplsh", 130, 64, 3, 40),
+                                         ("pslsh", 4097, 96, 16, 8), ("pslsh", 999, 32, 5, 3),
+                                         ("pslsh", 2000, 128, 4, 16)])
+@pytest.mark.parametrize("kblk", [16, 32])
+def test_tensor_core_projection(eng, fam, n, d, L, k, kblk):
+    culsh, core_mod = eng
+    if kblk != int(os.environ.get("CULSH_TC_KBLK", "16")):
+        pytest.skip("the K-block variant is chosen per process (CULSH_TC_KBLK)")
+    rng = np.random.RandomState(n + d + L)
+    X = rng.randn(n, d).astype(np.float32)
+    X[: n // 4] = np.round(X[: n // 4] * (50 if fam == "rplsh" else 4))  # integer rows: zero-lo fast path
+    if fam == "rplsh":
+        lsh, core = culsh.RPLSH(L, k, seed=31), core_mod.RPLSHCore(L, k, 31)
+    else:
+        lsh, core = culsh.PStableLSH(L, k, window_size=4, seed=31), core_mod.PSLSHCore(L, k, 4, 31)
+    try:
+        core.set_projection_path(2)  # tensor cores required: an unsupported shape is an error
+        model = lsh.fit(X)
+        assert core.last_stats()["hash_path"] == 1
+        sig_tc = _index_row_signatures(model.index, fam)  # what the tensor-core fit really stored
+        core.set_projection_path(1)
+        model_simt = lsh.fit(X)
+        assert core.last_stats()["hash_path"] == 0
+        sig_simt = _index_row_signatures(model_simt.index, fam)
+    finally:
+        core.set_projection_path(0)
+    P = model.index.get_projection_matrix().reshape(L * k, d)
+    if fam == "rplsh":
+        near, want = oracle.rplsh_near_boundary(X, P, REL_BAND), oracle.rplsh_signatures(X, P)
+    else:
+        b = model.index.get_bias()
+        near, want = oracle.pslsh_near_boundary(X, P, b, REL_BAND), oracle.pslsh_signatures(X, P, b)
+    assert np.array_equal(sig_tc[~near], want[~near])
+    assert np.array_equal(sig_simt[~near], want[~near])
+    assert (sig_tc != sig_simt).mean() < 1e-4
+    _assert_index_equals_oracle(model.index, sig_tc, L, k)
