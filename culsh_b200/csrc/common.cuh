@@ -127,8 +127,20 @@ struct ParamKey {
     }
 };
 
+// Scratch slots: every temporary of the pipeline has its own grow-only device buffer that
+// lives as long as the handle, so steady-state calls allocate nothing for temporaries and
+// the stream-ordered pool only ever sees the (repeating) sizes of results.
+enum ScratchSlot {
+    SL_STAGE0, SL_STAGE1, SL_CSR_INDPTR, SL_CSR_INDICES, SL_KEYS0, SL_KEYS1, SL_VALS, SL_GHIST,
+    SL_STATUS, SL_COUNTER, SL_TILE_HEADS, SL_TILE_BASE, SL_SCAN, SL_RAW_CNT, SL_RAW_OFF,
+    SL_BIG_LIST, SL_NBIG, SL_TMP, SL_QKEYS, SL_QOVF, SL_MATCHED, SL_I2B, SL_MISC0, SL_MISC1,
+    SL_MISC2, SL_COUNT
+};
+
 struct Ctx {
     int device = 0;
+    void* slot_ptr[SL_COUNT] = {};
+    size_t slot_cap[SL_COUNT] = {};
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t ev[8] = {};
@@ -148,6 +160,8 @@ struct Ctx {
         for (auto& e : ev) if (e) cudaEventDestroy(e);
         for (auto& e : copy_done) if (e) cudaEventDestroy(e);
         for (auto& e : chunk_free) if (e) cudaEventDestroy(e);
+        if (copy_stream) cudaStreamSynchronize(copy_stream);
+        for (auto& q : slot_ptr) if (q) cudaFree(q);
         if (pinned) cudaFreeHost(pinned);
         if (d_error) cudaFree(d_error);
         if (copy_stream) cudaStreamDestroy(copy_stream);
@@ -201,6 +215,39 @@ struct DevBuf {
         }
         p = nullptr;
         n = 0;
+    }
+    size_t bytes() const { return n * sizeof(T); }
+};
+
+// Temporary in a scratch slot of the handle (see ScratchSlot).  Two live Scratch objects must
+// not share a slot.  Growing a slot waits for the handle's streams, frees the old block and
+// allocates the new size; contents are not preserved.
+template <typename T>
+struct Scratch {
+    T* p = nullptr;
+    size_t n = 0;
+    Scratch() = default;
+    Scratch(const CtxPtr& c, ScratchSlot slot, size_t count) { reserve(c, slot, count); }
+    void reserve(const CtxPtr& c, ScratchSlot slot, size_t count) {
+        n = count;
+        const size_t need = count * sizeof(T);
+        if (need > c->slot_cap[slot]) {
+            CU_CHECK(cudaStreamSynchronize(c->stream));
+            CU_CHECK(cudaStreamSynchronize(c->copy_stream));
+            if (c->slot_ptr[slot]) CU_CHECK(cudaFree(c->slot_ptr[slot]));
+            c->slot_ptr[slot] = nullptr;
+            c->slot_cap[slot] = 0;
+            const size_t cap = (need + 255) / 256 * 256;
+            void* q = nullptr;
+            cudaError_t e = cudaMalloc(&q, cap);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                fail(CULSH_ERR_ALLOC, "device allocation of %zu bytes failed: %s", cap, cudaGetErrorString(e));
+            }
+            c->slot_ptr[slot] = q;
+            c->slot_cap[slot] = cap;
+        }
+        p = count ? static_cast<T*>(c->slot_ptr[slot]) : nullptr;
     }
     size_t bytes() const { return n * sizeof(T); }
 };

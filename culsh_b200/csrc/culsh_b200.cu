@@ -8,7 +8,8 @@
 #include "radix_sort.cuh"
 
 #include <algorithm>
-#include <mutex>
+#include <chrono>
+#include <cstdlib>
 
 using namespace culsh_b200;
 
@@ -93,6 +94,29 @@ struct StageTimer {
         float ms = 0.f;
         if (c->profiling && b < next) cudaEventElapsedTime(&ms, c->ev[a], c->ev[b]);
         return ms;
+    }
+};
+
+// Optional host-side trace (CULSH_TRACE=1): wall-clock of host steps, printed to stderr.
+struct HostTrace {
+    bool on;
+    std::chrono::steady_clock::time_point t;
+    HostTrace() : on(getenv("CULSH_TRACE") != nullptr), t(std::chrono::steady_clock::now()) {}
+    void lap(const char* what) {
+        if (!on) return;
+        auto now = std::chrono::steady_clock::now();
+        uint64_t reserved = 0, used = 0;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaMemPool_t pool;
+        if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+            cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &reserved);
+            cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemCurrent, &used);
+        }
+        fprintf(stderr, "[culsh trace] %-28s %9.1f us   pool reserved %7.1f MB used %7.1f MB\n", what,
+                std::chrono::duration<double, std::micro>(now - t).count(), reserved / 1048576.0,
+                used / 1048576.0);
+        t = std::chrono::steady_clock::now();
     }
 };
 
@@ -229,9 +253,9 @@ void hash_dense(const culsh_index& ix, const KeySpec& ks, const T* X, int n, uin
     size_t chunk_rows = std::max<size_t>(1024, (size_t)(32u << 20) / row_bytes);
     chunk_rows = std::min<size_t>(chunk_rows, (size_t)n);
     chunk_rows = (chunk_rows + 127) / 128 * 128;
-    DevBuf<uint8_t> stage[2];
-    stage[0].alloc(c, chunk_rows * row_bytes);
-    stage[1].alloc(c, chunk_rows * row_bytes);
+    Scratch<uint8_t> stage[2];
+    stage[0].reserve(c, SL_STAGE0, chunk_rows * row_bytes);
+    stage[1].reserve(c, SL_STAGE1, chunk_rows * row_bytes);
     // the staging buffers were allocated on the main stream: order the copy stream after it
     CU_CHECK(cudaEventRecord(c->chunk_free[0], c->stream));
     CU_CHECK(cudaEventRecord(c->chunk_free[1], c->stream));
@@ -254,11 +278,11 @@ void hash_csr(const culsh_index& ix, const KeySpec& ks, const int32_t* indices, 
               int n, uint32_t* keys, int n_total, int row_offset) {
     const CtxPtr& c = ix.ctx;
     if (n == 0) return;
-    DevBuf<int32_t> d_indptr, d_indices;
+    Scratch<int32_t> d_indptr, d_indices;
     const int32_t* ip = indptr;
     const int32_t* ii = indices;
     if (!is_device_pointer(indptr)) {
-        d_indptr.alloc(c, (size_t)n + 1);
+        d_indptr.reserve(c, SL_CSR_INDPTR, (size_t)n + 1);
         CU_CHECK(cudaMemcpyAsync(d_indptr.p, indptr, sizeof(int32_t) * ((size_t)n + 1),
                                  cudaMemcpyHostToDevice, c->stream));
         ip = d_indptr.p;
@@ -269,7 +293,7 @@ void hash_csr(const culsh_index& ix, const KeySpec& ks, const int32_t* indices, 
         else nnz = indptr[n];
         if (nnz < 0) fail(CULSH_ERR_INVALID, "indptr[n] is negative");
         if (nnz > 0 && !indices) fail(CULSH_ERR_INVALID, "indices is null");
-        d_indices.alloc(c, (size_t)nnz);
+        d_indices.reserve(c, SL_CSR_INDICES, (size_t)nnz);
         if (nnz)
             CU_CHECK(cudaMemcpyAsync(d_indices.p, indices, sizeof(int32_t) * (size_t)nnz,
                                      cudaMemcpyHostToDevice, c->stream));
@@ -285,35 +309,41 @@ void hash_csr(const culsh_index& ix, const KeySpec& ks, const int32_t* indices, 
 // Index build from hashed keys
 // -----------------------------------------------------------------------------------------
 struct SortBuffers {
-    DevBuf<uint32_t> keys[2];
-    DevBuf<uint32_t> vals[2];
-    DevBuf<uint32_t> ghist, status, counter;
+    Scratch<uint32_t> keys[2];
+    uint32_t* vals[2] = {nullptr, nullptr};
+    DevBuf<uint32_t> vals_out;   // receives the sorted row ids: becomes the index's candidate array
+    Scratch<uint32_t> vals_tmp;
+    Scratch<uint32_t> ghist, status, counter;
+    int final_buf = 0;
     void alloc(const CtxPtr& c, size_t items, const KeySpec& ks, int n, int L) {
-        keys[0].alloc(c, items * ks.key_words);
-        keys[1].alloc(c, items * ks.key_words);
-        vals[0].alloc(c, items);
-        vals[1].alloc(c, items);
-        ghist.alloc(c, (size_t)L * ks.key_bytes * 256);
-        status.alloc(c, radix_sort_status_words(n, L, ks.key_words));
-        counter.alloc(c, 1);
+        keys[0].reserve(c, SL_KEYS0, items * ks.key_words);
+        keys[1].reserve(c, SL_KEYS1, items * ks.key_words);
+        final_buf = ks.key_bytes & 1;  // one buffer flip per radix pass
+        vals_out.alloc(c, items);
+        vals_tmp.reserve(c, SL_VALS, items);
+        vals[final_buf] = vals_out.p;
+        vals[final_buf ^ 1] = vals_tmp.p;
+        ghist.reserve(c, SL_GHIST, (size_t)L * ks.key_bytes * 256);
+        status.reserve(c, SL_STATUS, radix_sort_status_words(n, L, ks.key_words));
+        counter.reserve(c, SL_COUNTER, 1);
     }
 };
 
 // Sort + bucket construction.  On return ix holds cand/bucket arrays; if want_i2b the
 // (row, table) -> bucket map is filled.  Returns the device error word read at the one
 // host synchronisation of the build.
-int build_index(culsh_index& ix, SortBuffers& sb, DevBuf<int32_t>* item_to_bucket, StageTimer& tm) {
+int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_bucket, StageTimer& tm) {
     const CtxPtr& c = ix.ctx;
     const int n = ix.n, L = ix.L, NW = ix.ks.key_words;
     uint32_t* kp[2] = {sb.keys[0].p, sb.keys[1].p};
-    uint32_t* vp[2] = {sb.vals[0].p, sb.vals[1].p};
+    uint32_t* vp[2] = {sb.vals[0], sb.vals[1]};
     int cur = radix_sort_tables(c, NW, kp, vp, n, L, ix.ks.key_bytes, sb.ghist.p, sb.status.p,
                                 sb.counter.p);
     tm.mark();
     const int tpt = (int)ceil_div(n, IB_TILE);
     const size_t n_tiles = (size_t)tpt * L;
-    DevBuf<uint32_t> tile_heads(c, n_tiles), tile_base(c, n_tiles + 1),
-        scratch(c, scan_scratch_elems(n_tiles));
+    Scratch<uint32_t> tile_heads(c, SL_TILE_HEADS, n_tiles), tile_base(c, SL_TILE_BASE, n_tiles + 1),
+        scratch(c, SL_SCAN, scan_scratch_elems(n_tiles) * 2);
     CULSH_DISPATCH_NW(NW, launch_bucket_count<NW>(c->stream, kp[cur], n, L, tile_heads.p));
     exclusive_scan<uint32_t, uint32_t>(c->stream, tile_heads.p, n_tiles, tile_base.p, scratch.p);
     // the one host round trip of the build: bucket total + self-check word
@@ -329,14 +359,15 @@ int build_index(culsh_index& ix, SortBuffers& sb, DevBuf<int32_t>* item_to_bucke
     ix.bucket_keys.alloc(c, (size_t)B * NW);
     ix.bucket_offsets.alloc(c, (size_t)B + 1);
     ix.table_offsets.alloc(c, (size_t)L + 1);
-    if (item_to_bucket) item_to_bucket->alloc(c, (size_t)n * L);
+    if (item_to_bucket) item_to_bucket->reserve(c, SL_I2B, (size_t)n * L);
     CULSH_DISPATCH_NW(NW, launch_bucket_write<NW>(c->stream, kp[cur], vp[cur], n, L, tile_base.p,
                                                   ix.bucket_keys.p, ix.bucket_offsets.p,
                                                   ix.table_offsets.p,
                                                   item_to_bucket ? item_to_bucket->p : nullptr));
     // the sorted row ids are the candidate array: adopt the buffer
     static_assert(sizeof(int32_t) == sizeof(uint32_t), "");
-    DevBuf<uint32_t>& v = sb.vals[cur];
+    if (cur != sb.final_buf) fail(CULSH_ERR_INTERNAL, "radix sort ended in the scratch buffer");
+    DevBuf<uint32_t>& v = sb.vals_out;
     ix.cand.p = reinterpret_cast<int32_t*>(v.p);
     ix.cand.n = v.n;
     ix.cand.ctx = v.ctx;
@@ -363,7 +394,7 @@ void validate_shape(int n, int d, int L, int k) {
 
 // Hash + sort + build.  `hash_fn(ks, keys)` fills the key array for a given key layout.
 template <typename HashFn>
-void fit_common(culsh_index& ix, HashFn&& hash_fn, DevBuf<int32_t>* item_to_bucket) {
+void fit_common(culsh_index& ix, HashFn&& hash_fn, Scratch<int32_t>* item_to_bucket) {
     const CtxPtr& c = ix.ctx;
     c->stats = culsh_stats{};
     launch_counter() = 0;
@@ -403,8 +434,9 @@ void fit_common(culsh_index& ix, HashFn&& hash_fn, DevBuf<int32_t>* item_to_buck
 // -----------------------------------------------------------------------------------------
 int bitmap_window_bits(const CtxPtr& c, int n_rows) {
     size_t fixed = bitmap_smem_bytes(0) + 1024;
-    size_t max_bits = ((c->smem_optin > fixed ? c->smem_optin - fixed : 0) * 8) / 1024 * 1024;
-    size_t want = ((size_t)n_rows + 1023) / 1024 * 1024;
+    // a multiple of 4096 bits: the emission walks the window in 128-word groups
+    size_t max_bits = ((c->smem_optin > fixed ? c->smem_optin - fixed : 0) * 8) / 4096 * 4096;
+    size_t want = ((size_t)n_rows + 4095) / 4096 * 4096;
     size_t cap = std::min<size_t>(max_bits, (size_t)1 << 20);
     return (int)std::min(want, cap);
 }
@@ -414,12 +446,14 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     const CtxPtr& c = ix.ctx;
     cudaStream_t s = c->stream;
     const int L = ix.L;
+    HostTrace tr;
     out.ctx = c;
     out.n_queries = n_q;
     out.counts.alloc(c, (size_t)n_q);
     out.offsets.alloc(c, (size_t)n_q + 1);
-    DevBuf<uint64_t> raw_cnt(c, n_q), raw_off(c, (size_t)n_q + 1), scratch(c, scan_scratch_elems(n_q));
-    DevBuf<uint32_t> big_list(c, n_q), n_big(c, 1);
+    Scratch<uint64_t> raw_cnt(c, SL_RAW_CNT, n_q), raw_off(c, SL_RAW_OFF, (size_t)n_q + 1),
+        scratch(c, SL_SCAN, scan_scratch_elems(n_q));
+    Scratch<uint32_t> big_list(c, SL_BIG_LIST, n_q), n_big(c, SL_NBIG, 1);
     CU_CHECK(cudaMemsetAsync(n_big.p, 0, sizeof(uint32_t), s));
     raw_count_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(matched, ix.bucket_offsets.p, n_q, L,
                                                                  raw_cnt.p, big_list.p, n_big.p);
@@ -432,6 +466,7 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     CU_CHECK(cudaStreamSynchronize(s));
     std::memcpy(&raw_total, c->pinned, sizeof(uint64_t));
     std::memcpy(&nb, c->pinned + 1, sizeof(uint32_t));
+    tr.lap("count+scan+sync");
     c->stats.raw_candidates += raw_total;
     if (raw_total == 0) {
         CU_CHECK(cudaMemsetAsync(out.counts.p, 0, out.counts.bytes(), s));
@@ -440,7 +475,8 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
         CU_CHECK(cudaStreamSynchronize(s));
         return;
     }
-    DevBuf<int32_t> tmp(c, raw_total);
+    Scratch<int32_t> tmp(c, SL_TMP, raw_total);
+    tr.lap("alloc tmp");
     {
         size_t blocks = std::min<size_t>(ceil_div(n_q, SM_WARPS), (size_t)c->sm_count * 16);
         dedupe_small_kernel<<<(unsigned)blocks, SM_THREADS, 0, s>>>(
@@ -459,10 +495,12 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     exclusive_scan<uint64_t, uint64_t>(s, out.counts.p, n_q, out.offsets.p, scratch.p);
     uint64_t total = 0;
     read_words(c, out.offsets.p + n_q, sizeof(uint64_t), &total);
+    tr.lap("dedupe+scan+sync");
     out.total = total;
     c->stats.unique_candidates += total;
     if (total) {
         out.indices.alloc(c, total);
+        tr.lap("alloc indices");
         size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
         compact_small_kernel<<<(unsigned)blocks, 256, 0, s>>>(tmp.p, raw_cnt.p, raw_off.p, out.counts.p,
                                                              out.offsets.p, n_q, out.indices.p);
@@ -475,6 +513,7 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     }
     tm.mark();
     CU_CHECK(cudaStreamSynchronize(s));
+    tr.lap("compact+sync");
 }
 
 // Hash a batch of queries, look the buckets up, gather + dedupe.
@@ -484,10 +523,10 @@ void query_batch(const culsh_index& ix, int n_q, HashFn&& hash_fn, culsh_candida
     const int NW = ix.ks.key_words;
     StageTimer tm(c);
     const size_t pairs = (size_t)n_q * ix.L;
-    DevBuf<uint32_t> qkeys(c, pairs * NW);
-    DevBuf<uint8_t> ovf;
-    if (ix.family == CULSH_PSLSH && ix.ks.elem_bytes < 4) ovf.alloc(c, pairs);
-    DevBuf<int32_t> matched(c, pairs);
+    Scratch<uint32_t> qkeys(c, SL_QKEYS, pairs * NW);
+    Scratch<uint8_t> ovf;
+    if (ix.family == CULSH_PSLSH && ix.ks.elem_bytes < 4) ovf.reserve(c, SL_QOVF, pairs);
+    Scratch<int32_t> matched(c, SL_MATCHED, pairs);
     tm.mark();
     hash_fn(ix.ks, qkeys.p, ovf.p);
     tm.mark();
@@ -590,7 +629,7 @@ void fit_query_dense(culsh_handle* h, int family, const T* X, int n, int d, int 
     if (!X) fail(CULSH_ERR_INVALID, "X is null");
     DeviceGuard g(h->ctx->device);
     auto ix = new_dense_index<T>(h, family, n, d, L, k, window, seed);
-    DevBuf<int32_t> i2b;
+    Scratch<int32_t> i2b;
     fit_common(*ix, [&](const KeySpec& ks, uint32_t* keys) {
         hash_dense<T>(*ix, ks, X, n, keys, nullptr, n, 0);
     }, &i2b);
@@ -831,7 +870,7 @@ int culsh_minhash_fit_query(culsh_handle* h, const int32_t* indices, const int32
         if (!indptr) fail(CULSH_ERR_INVALID, "indptr is null");
         DeviceGuard g(h->ctx->device);
         auto ix = new_minhash_index(h, n, d, L, k, seed);
-        DevBuf<int32_t> i2b;
+        Scratch<int32_t> i2b;
         fit_common(*ix, [&](const KeySpec& ks, uint32_t* keys) {
             hash_csr(*ix, ks, indices, indptr, n, keys, n, 0);
         }, &i2b);
@@ -847,7 +886,7 @@ int culsh_minhash_fit_query(culsh_handle* h, const int32_t* indices, const int32
 // ---- signatures only --------------------------------------------------------------------
 static void unpack_and_copy(const CtxPtr& c, const uint32_t* keys, size_t count, const KeySpec& ks,
                             void* dst) {
-    DevBuf<uint8_t> raw(c, count * ks.sig_nbytes);
+    Scratch<uint8_t> raw(c, SL_MISC0, count * ks.sig_nbytes);
     unpack_keys_kernel<<<(unsigned)ceil_div(count, 256), 256, 0, c->stream>>>(
         keys, count, ks.family, ks.n_hashes, ks.key_words, ks.elem_bytes, raw.p);
     KERNEL_CHECK();
@@ -865,7 +904,7 @@ int culsh_index_hash_dense(culsh_handle* h, const culsh_index* ix, const void* X
         KeySpec ks = make_key_spec(ix->family, ix->k, 4);  // full-width elements: nothing saturates
         if (ks.key_words < 0) fail(CULSH_ERR_UNSUPPORTED, "signature wider than 64 bytes");
         size_t items = (size_t)n_rows * ix->L;
-        DevBuf<uint32_t> keys(c, items * ks.key_words);
+        Scratch<uint32_t> keys(c, SL_KEYS0, items * ks.key_words);
         if (ix->is_double)
             hash_dense<double>(*ix, ks, static_cast<const double*>(X), n_rows, keys.p, nullptr, n_rows, 0, true);
         else
@@ -883,7 +922,7 @@ int culsh_index_hash_csr(culsh_handle* h, const culsh_index* ix, const int32_t* 
         DeviceGuard g(h->ctx->device);
         const CtxPtr& c = ix->ctx;
         size_t items = (size_t)n_rows * ix->L;
-        DevBuf<uint32_t> keys(c, items * ix->ks.key_words);
+        Scratch<uint32_t> keys(c, SL_KEYS0, items * ix->ks.key_words);
         hash_csr(*ix, ix->ks, indices, indptr, n_rows, keys.p, n_rows, 0);
         unpack_and_copy(c, keys.p, items, ix->ks, sig_out);
     });
@@ -1028,11 +1067,11 @@ int culsh_index_load(culsh_handle* h, int family, int is_double, const int32_t* 
         CU_CHECK(cudaMemcpyAsync(ix->p0.p, param0, ix->p0.bytes(), cudaMemcpyDefault, s));
         if (ix->p1.n) CU_CHECK(cudaMemcpyAsync(ix->p1.p, param1, ix->p1.bytes(), cudaMemcpyDefault, s));
         // raw signatures -> packed keys (p-stable: narrowest element width that holds them)
-        DevBuf<uint8_t> raw(c, B * sig_nbytes);
+        Scratch<uint8_t> raw(c, SL_MISC0, B * sig_nbytes);
         CU_CHECK(cudaMemcpyAsync(raw.p, bucket_signatures, raw.bytes(), cudaMemcpyDefault, s));
         int eb = family == CULSH_MINHASH ? 4 : 0;
         if (family == CULSH_PSLSH) {
-            DevBuf<int> width(c, 1);
+            Scratch<int> width(c, SL_MISC1, 1);
             int one = 1;
             CU_CHECK(cudaMemcpyAsync(width.p, &one, sizeof(int), cudaMemcpyHostToDevice, s));
             size_t cnt = B * k;
@@ -1130,9 +1169,9 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
             *out = res.release();
             return;
         }
-        DevBuf<const int32_t*> d_idx(c, n_shards);
-        DevBuf<const uint64_t*> d_off(c, n_shards);
-        DevBuf<int64_t> d_base(c, n_shards);
+        Scratch<const int32_t*> d_idx(c, SL_MISC0, n_shards);
+        Scratch<const uint64_t*> d_off(c, SL_MISC1, n_shards);
+        Scratch<int64_t> d_base(c, SL_MISC2, n_shards);
         CU_CHECK(cudaMemcpyAsync(d_idx.p, shard_indices, sizeof(void*) * n_shards, cudaMemcpyHostToDevice, s));
         CU_CHECK(cudaMemcpyAsync(d_off.p, shard_offsets, sizeof(void*) * n_shards, cudaMemcpyHostToDevice, s));
         CU_CHECK(cudaMemcpyAsync(d_base.p, row_base, sizeof(int64_t) * n_shards, cudaMemcpyHostToDevice, s));
@@ -1140,7 +1179,7 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
         res->n_queries = n_q;
         res->counts.alloc(c, n_q);
         res->offsets.alloc(c, (size_t)n_q + 1);
-        DevBuf<uint64_t> scratch(c, scan_scratch_elems(n_q));
+        Scratch<uint64_t> scratch(c, SL_SCAN, scan_scratch_elems(n_q));
         shard_counts_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(d_off.p, n_shards, n_q, res->counts.p);
         KERNEL_CHECK();
         exclusive_scan<uint64_t, uint64_t>(s, res->counts.p, n_q, res->offsets.p, scratch.p);

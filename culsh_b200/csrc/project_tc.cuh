@@ -12,11 +12,11 @@
 // warpgroup after the TMA load lands (element-wise, so the TMA swizzle is preserved).  When a
 // tile's xl is identically zero (e.g. integer-valued data below 2^11) its third MMA is skipped.
 //
-// One persistent CTA per SM, 10 warps:
+// One persistent CTA per SM, 14 warps:
 //   warp 0      TMA producer (one lane)            full[s]  <- TMA bytes
 //   warp 1      MMA issuer (one lane), TMEM owner  ready[s] <- transform, empty[s] <- MMA done
 //   warps 2-5   split X tiles into hi / lo         acc_full[b] <- MMA done, acc_empty[b] <- epilogue
-//   warps 6-9   epilogue: tcgen05.ld -> quantise -> pack -> store
+//   warps 6-13  epilogue: tcgen05.ld -> quantise -> pack -> store
 // A work unit is (128-row tile, chunk of whole tables with <= 256 hash columns); two TMEM
 // accumulators of 256 columns alternate so the epilogue of one unit overlaps the MMAs of the
 // next.  Every mbarrier wait is bounded: when one runs out the CTA raises an abort flag,
@@ -32,9 +32,10 @@ namespace culsh_b200 {
 
 constexpr int TC_BM = 128;          // rows per tile (MMA M)
 constexpr int TC_BN = 256;          // accumulator columns (max MMA N)
-constexpr int TC_THREADS = 320;
 constexpr int TC_TRANSFORM_THREADS = 128;
-constexpr int TC_EPI_THREADS = 128;
+constexpr int TC_EPI_WARPS = 8;     // two warps per TMEM lane quarter, each takes half of the tables
+constexpr int TC_EPI_THREADS = TC_EPI_WARPS * 32;
+constexpr int TC_THREADS = 64 + TC_TRANSFORM_THREADS + TC_EPI_THREADS;
 constexpr long long TC_WAIT_CYCLES = 4000000000ll;  // ~2 s at 2 GHz
 
 template <int KBLK>
@@ -173,7 +174,93 @@ struct KeyReg {
     }
 };
 
-template <int KBLK>
+// Epilogue of one work unit for one warp: stream the accumulator columns [c_begin, c_end) of
+// this warp's 32 TMEM lanes (= 32 rows), quantise each value and shift it into the key of its
+// table; a finished table is stored as NW words.  KW selects the key register: 1 = 32-bit,
+// 2 = 64-bit, 0 = 256-bit.  All control flow is warp-uniform (every lane walks the same
+// columns), as tcgen05.ld requires.
+template <int FAMILY, int KW>
+__device__ __forceinline__ bool epilogue_columns(const TcArgs& a, uint32_t taddr, int c_begin, int c_end,
+                                                 int first_table, int bias_base, int row, bool row_ok) {
+    const int k = a.k, NW = a.key_words;
+    const int bits = FAMILY == CULSH_RPLSH ? 1 : 8 * a.elem_bytes;
+    const int lim = a.elem_bytes == 1 ? 128 : (a.elem_bytes == 2 ? 32768 : 0);
+    uint32_t acc32 = 0;
+    uint64_t acc64 = 0;
+    KeyReg wide;
+    wide.clear();
+    int cnt = 0, tbl = first_table;
+    bool ovf = false, any_ovf = false;
+    const int g_begin = c_begin & ~15;
+    for (int g0 = g_begin; g0 < c_end; g0 += 16) {
+        uint32_t r[16];
+        tc_ld16(taddr + (uint32_t)g0, r);
+        tc_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int col = g0 + j;
+            if ((unsigned)(col - c_begin) < (unsigned)(c_end - c_begin)) {
+                uint32_t e;
+                if (FAMILY == CULSH_RPLSH) {
+                    e = r[j] >> 31;  // sign bit; inverted when the key is stored
+                } else {
+                    const int q = (int)floorf(__uint_as_float(r[j]) + a.bias[bias_base + col]);  // pslsh/hash.cuh:46
+                    if (lim && (unsigned)(q + lim) >= (unsigned)(2 * lim)) ovf = true;
+                    const uint32_t uq = (uint32_t)q;
+                    e = a.elem_bytes == 1 ? (uq & 0xFFu)
+                        : a.elem_bytes == 2 ? (((uq & 0xFFu) << 8) | ((uq >> 8) & 0xFFu))
+                                            : __byte_perm(uq, 0, 0x0123);
+                }
+                if (KW == 1) {
+                    if (FAMILY == CULSH_RPLSH) acc32 = __funnelshift_l(r[j], acc32, 1);
+                    else acc32 = bits == 32 ? e : ((acc32 << bits) | e);
+                } else if (KW == 2) {
+                    acc64 = (acc64 << bits) | (uint64_t)e;
+                } else {
+                    wide.push(e, bits);
+                }
+                if (++cnt == k) {
+                    if (row_ok) {
+                        const size_t item = (size_t)tbl * a.n_total + a.row_offset + row;
+                        uint32_t* dst = a.keys + item * NW;
+                        if (KW == 1) {
+                            // RPLSH: stored bit = 1 where the sign bit is clear (rplsh/hash.cuh:47)
+                            dst[0] = FAMILY == CULSH_RPLSH ? (~acc32 & (k == 32 ? 0xFFFFFFFFu : ((1u << k) - 1u)))
+                                                           : acc32;
+                        } else if (KW == 2) {
+                            uint64_t v = acc64;
+                            if (FAMILY == CULSH_RPLSH) v = ~v & (k == 64 ? ~0ull : ((1ull << k) - 1ull));
+                            *reinterpret_cast<uint2*>(dst) = make_uint2((uint32_t)(v >> 32), (uint32_t)v);
+                        } else {
+                            if (FAMILY == CULSH_RPLSH) {  // invert the k low bits of the 256-bit register
+#pragma unroll
+                                for (int w = 0; w < 4; ++w) {
+                                    const int lo_bit = 64 * (3 - w);
+                                    uint64_t m = k >= lo_bit + 64 ? ~0ull : (k > lo_bit ? ((1ull << (k - lo_bit)) - 1ull) : 0ull);
+                                    wide.w[w] = ~wide.w[w] & m;
+                                }
+                            }
+                            wide.store(dst, NW);
+                        }
+                        if (FAMILY == CULSH_PSLSH) {
+                            if (a.ovf_rows) a.ovf_rows[item] = ovf ? 1 : 0;
+                            else any_ovf |= ovf;
+                        }
+                    }
+                    acc32 = 0;
+                    acc64 = 0;
+                    if (KW == 0) wide.clear();
+                    cnt = 0;
+                    ovf = false;
+                    ++tbl;
+                }
+            }
+        }
+    }
+    return any_ovf;
+}
+
+template <int KBLK, int FAMILY>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmP, TcArgs a) {
     using Cfg = TcCfg<KBLK>;
@@ -321,11 +408,10 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
     } else {
         // ---------------- epilogue ----------------
-        const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter ...
+        const int quarter = warp & 3;        // TMEM lanes this warp may read: 32*quarter ...
+        const int half = (warp - 6) >> 2;    // which half of the unit's tables this warp packs
         const int NW = a.key_words;
         const int k = a.k;
-        const int bits = a.family == CULSH_RPLSH ? 1 : 8 * a.elem_bytes;
-        const int lim = a.elem_bytes == 1 ? 128 : (a.elem_bytes == 2 ? 32768 : 0);
         uint32_t u = 0;
         bool live = true;
         bool any_ovf = false;
@@ -339,49 +425,15 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 tc_fence_after();
                 const int t0 = c * a.tables_per_chunk;
                 const int tables_here = min(a.tables_per_chunk, a.L - t0);
-                const int cols = tables_here * k;
+                const int split = (tables_here + 1) >> 1;
+                const int tb = half == 0 ? 0 : split, te = half == 0 ? split : tables_here;
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * TC_BN);
-                KeyReg reg;
-                reg.clear();
-                int in_table = 0, tbl = t0;
-                bool ovf = false;
-                for (int g0 = 0; g0 < cols; g0 += 16) {
-                    uint32_t r[16];
-                    tc_ld16(taddr + (uint32_t)g0, r);
-                    tc_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int col = g0 + j;
-                        if (col < cols) {
-                            const float v = __uint_as_float(r[j]);
-                            uint32_t e;
-                            if (a.family == CULSH_RPLSH) {
-                                e = (r[j] >> 31) ^ 1u;  // sign bit clear -> 1 (rplsh/hash.cuh:47)
-                            } else {
-                                const int q = (int)floorf(v + a.bias[t0 * k + col]);  // pslsh/hash.cuh:46
-                                if (lim && (q < -lim || q >= lim)) ovf = true;
-                                const uint32_t uq = (uint32_t)q;
-                                e = a.elem_bytes == 1 ? (uq & 0xFFu)
-                                    : a.elem_bytes == 2 ? (((uq & 0xFFu) << 8) | ((uq >> 8) & 0xFFu))
-                                                        : __byte_perm(uq, 0, 0x0123);
-                            }
-                            reg.push(e, bits);
-                            if (++in_table == k) {
-                                if (row_ok) {
-                                    const size_t item = (size_t)tbl * a.n_total + a.row_offset + row;
-                                    reg.store(a.keys + item * NW, NW);
-                                    if (a.family == CULSH_PSLSH) {
-                                        if (a.ovf_rows) a.ovf_rows[item] = ovf ? 1 : 0;
-                                        else any_ovf |= ovf;
-                                    }
-                                }
-                                reg.clear();
-                                in_table = 0;
-                                ovf = false;
-                                ++tbl;
-                            }
-                        }
-                    }
+                if (te > tb) {
+                    bool o;
+                    if (NW == 1) o = epilogue_columns<FAMILY, 1>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (NW == 2) o = epilogue_columns<FAMILY, 2>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else o = epilogue_columns<FAMILY, 0>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    any_ovf |= o;
                 }
                 tc_fence_before();
                 mbar_arrive(&acc_empty[ab]);
@@ -516,17 +568,13 @@ inline bool launch_project_tc(const CtxPtr& c, cudaStream_t stream, int family, 
     a.key_words = ks.key_words; a.elem_bytes = ks.elem_bytes; a.family = family;
     a.row_offset = row_offset; a.n_total = n_total;
     int grid = std::min(a.n_tiles, c->sm_count);
-    if (p.kblk == 32) {
-        size_t smem = TcCfg<32>::SMEM;
-        if (smem > c->smem_optin) return false;
-        CU_CHECK(cudaFuncSetAttribute(project_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        project_tc_kernel<32><<<grid, TC_THREADS, smem, stream>>>(tmX, tmP, a);
-    } else {
-        size_t smem = TcCfg<16>::SMEM;
-        if (smem > c->smem_optin) return false;
-        CU_CHECK(cudaFuncSetAttribute(project_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        project_tc_kernel<16><<<grid, TC_THREADS, smem, stream>>>(tmX, tmP, a);
-    }
+    auto kern = p.kblk == 32
+                    ? (family == CULSH_RPLSH ? project_tc_kernel<32, CULSH_RPLSH> : project_tc_kernel<32, CULSH_PSLSH>)
+                    : (family == CULSH_RPLSH ? project_tc_kernel<16, CULSH_RPLSH> : project_tc_kernel<16, CULSH_PSLSH>);
+    size_t smem = p.kblk == 32 ? (size_t)TcCfg<32>::SMEM : (size_t)TcCfg<16>::SMEM;
+    if (smem > c->smem_optin) return false;
+    CU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, TC_THREADS, smem, stream>>>(tmX, tmP, a);
     KERNEL_CHECK();
     return true;
 }

@@ -228,11 +228,17 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
             __syncthreads();
         }
         if (!cleared) continue;  // uniform: nothing in this window
-        // ---- pop-count scan: warp w owns words [w*per_warp, (w+1)*per_warp) ----
-        const int per_warp = (words + BM_WARPS - 1) / BM_WARPS;
-        const int w_begin = warp * per_warp, w_end = min(words, w_begin + per_warp);
+        // ---- pop-count scan.  The window is cut into groups of 128 words (one uint4 per lane);
+        // warp w owns groups [w*gpw, (w+1)*gpw). ----
+        const uint4* b4 = reinterpret_cast<const uint4*>(bitmap);
+        const int groups = words / 128;
+        const int gpw = (groups + BM_WARPS - 1) / BM_WARPS;
+        const int g_begin = warp * gpw, g_end = min(groups, g_begin + gpw);
         uint32_t wsum = 0;
-        for (int w = w_begin + lane; w < w_end; w += 32) wsum += __popc(bitmap[w]);
+        for (int g = g_begin; g < g_end; ++g) {
+            const uint4 v = b4[g * 32 + lane];
+            wsum += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xFFFFFFFFu, wsum, o);
         if (lane == 0) s_wtot[warp] = wsum;
@@ -243,14 +249,15 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
             if (i < warp) wbase += x;
             wtotal += x;
         }
-        // ---- emit: ids are staged in the warp's slice of shared memory and flushed in
-        // coalesced runs; a 32-word group denser than the stage is written directly ----
+        // ---- emit: each lane expands its four words; ids are staged in the warp's slice of
+        // shared memory and flushed in coalesced runs; a group denser than the stage is
+        // written directly ----
         uint32_t out_pos = written + wbase;  // global position of stage[0]
         uint32_t fill = 0;
-        for (int w0 = w_begin; w0 < w_end; w0 += 32) {
-            const int w = w0 + lane;
-            uint32_t bits = w < w_end ? bitmap[w] : 0u;
-            const uint32_t c = __popc(bits);
+        for (int g = g_begin; g < g_end; ++g) {
+            const uint4 v = b4[g * 32 + lane];
+            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+            const uint32_t c = __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
             uint32_t inc = c;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -259,7 +266,7 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
             }
             const uint32_t tot = __shfl_sync(0xFFFFFFFFu, inc, 31);
             if (tot == 0) continue;
-            const int32_t id0 = win_lo + w * 32;
+            const int32_t id0 = win_lo + (g * 128 + lane * 4) * 32;
             if (tot > BM_STAGE || fill + tot > BM_STAGE) {  // flush what is staged
                 __syncwarp();
                 for (uint32_t i = lane; i < fill; i += 32) out[out_pos + i] = stage[i];
@@ -267,23 +274,17 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
                 fill = 0;
                 __syncwarp();
             }
-            if (tot > BM_STAGE) {
-                uint32_t o_pos = out_pos + inc - c;
+            int32_t* dst = tot > BM_STAGE ? out + out_pos + (inc - c) : stage + fill + (inc - c);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t bits = wv[j];
                 while (bits) {
-                    int b = __ffs(bits) - 1;
+                    const int b = __ffs(bits) - 1;
                     bits &= bits - 1;
-                    out[o_pos++] = id0 + b;
+                    *dst++ = id0 + j * 32 + b;
                 }
-                out_pos += tot;
-            } else {
-                uint32_t s_pos = fill + inc - c;
-                while (bits) {
-                    int b = __ffs(bits) - 1;
-                    bits &= bits - 1;
-                    stage[s_pos++] = id0 + b;
-                }
-                fill += tot;
             }
+            if (tot > BM_STAGE) out_pos += tot; else fill += tot;
         }
         __syncwarp();
         for (uint32_t i = lane; i < fill; i += 32) out[out_pos + i] = stage[i];

@@ -174,6 +174,7 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
     const int item0 = lt * TILE;
     const int count = min(TILE, n - item0);
     const size_t base = (size_t)t * n + item0;
+    const uint32_t my_gbase = gbase[((size_t)t * KB + p) * 256 + tid];  // needed late: fetch early
 
     // ---- load (all loads in flight together), then rank inside the warp ---------------
     uint32_t key[IPT][NW];
@@ -239,28 +240,43 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
 
     uint32_t excl = 0;
     if (lt != 0) {
+        // Walk back over the preceding tiles of this table, eight status words per round so
+        // their latencies overlap; stop at the first tile that published an inclusive prefix.
         int j = (int)tile - 1;
         const int first = (int)tile - lt;
-        bool timed_out = false;
-        while (true) {
-            const uint32_t* sp = status + (size_t)j * 256 + tid;
-            uint32_t s = ld_volatile_u32(sp);
-            int spins = 0;
-            while ((s >> 30) == 0) {
-                if (++spins > RS_SPIN_LIMIT) { timed_out = true; break; }
-                if (spins > 64) __nanosleep(64);
-                s = ld_volatile_u32(sp);
+        bool timed_out = false, done = false;
+        while (!done && !timed_out) {
+            uint32_t sv[8];
+            const int avail = min(8, j - first + 1);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                sv[u] = u < avail ? ld_volatile_u32(status + (size_t)(j - u) * 256 + tid) : 0u;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (u < avail && !done && !timed_out) {
+                    uint32_t s = sv[u];
+                    if ((s >> 30) == 0) {
+                        const uint32_t* sp = status + (size_t)(j - u) * 256 + tid;
+                        int spins = 0;
+                        while ((s >> 30) == 0) {
+                            if (++spins > RS_SPIN_LIMIT) { timed_out = true; break; }
+                            if (spins > 32) __nanosleep(40);
+                            s = ld_volatile_u32(sp);
+                        }
+                    }
+                    if (!timed_out) {
+                        excl += s & RS_VAL_MASK;
+                        if ((s >> 30) == 2u || j - u == first) done = true;
+                    }
+                }
             }
-            if (timed_out) break;
-            excl += s & RS_VAL_MASK;
-            if ((s >> 30) == 2u || j == first) break;
-            --j;
+            j -= 8;
         }
         if (timed_out) atomicOr(d_error, DEV_ERR_LOOKBACK_TIMEOUT);
         st_volatile_u32(my_status, RS_FLAG_INC | ((excl + cnt) & RS_VAL_MASK));
     }
     s_binstart[tid] = binstart;
-    s_gdst[tid] = (uint32_t)((size_t)t * n) + gbase[((size_t)t * KB + p) * 256 + tid] + excl - binstart;
+    s_gdst[tid] = (uint32_t)((size_t)t * n) + my_gbase + excl - binstart;
     __syncthreads();
 
     // ---- reorder inside shared memory ------------------------------------------------
