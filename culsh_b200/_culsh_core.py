@@ -486,3 +486,24 @@ def merge_shard_candidates(shard_indices_ptrs, shard_offsets_ptrs, row_base, n_q
     out = C.c_void_p()
     _lib.check(h.lib.culsh_merge_shard_candidates(h.ptr, R, int(n_queries), idx, off, base, C.byref(out)))
     return Candidates(out, h)
+
+
+def merge_shard_candidates_into(shard_indices_ptrs, shard_offsets_ptrs, row_base, n_queries,
+                                out_indices_ptr, out_capacity, out_counts_ptr, out_offsets_ptr,
+                                device: Optional[int] = None) -> int:
+    """Allocation-free form of :func:`merge_shard_candidates` for hosts that may not allocate
+    device memory at merge time (the framework owns the whole device, or cudaMalloc's implicit
+    synchronisation is not acceptable there): the caller supplies the three result arrays as
+    device addresses and gets the merged id count back.  At most 64 shards and 4,194,304
+    queries; calls that overlap on one GPU must be serialised (they share a small fixed
+    scratch array inside the library)."""
+    h = get_handle(device)
+    R = len(shard_indices_ptrs)
+    idx = (C.c_void_p * R)(*[C.c_void_p(int(p)) for p in shard_indices_ptrs])
+    off = (C.c_void_p * R)(*[C.c_void_p(int(p)) for p in shard_offsets_ptrs])
+    base = (C.c_int64 * R)(*[int(b) for b in row_base])
+    total = C.c_uint64(0)
+    _lib.check(h.lib.culsh_merge_shard_candidates_noalloc(
+        h.ptr, R, int(n_queries), idx, off, base, int(out_indices_ptr) or None, int(out_capacity),
+        int(out_counts_ptr), int(out_offsets_ptr), C.byref(total)))
+    return int(total.value)

@@ -80,6 +80,8 @@ SIGNATURES = {
     "culsh_candidates_get_offsets": [VP, VP],
     "culsh_candidates_device_ptrs": [VP, PP, PP, PP],
     "culsh_merge_shard_candidates": [VP, I, I, PP, PP, C.POINTER(C.c_int64), PP],
+    "culsh_merge_shard_candidates_noalloc": [VP, I, I, PP, PP, C.POINTER(C.c_int64), VP, U64, VP, VP,
+                                             C.POINTER(C.c_uint64)],
 }
 _VOID = {"culsh_index_free": [VP], "culsh_candidates_free": [VP]}
 _CHARP = {"culsh_last_error": []}

@@ -1198,4 +1198,80 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
     });
 }
 
+// ---- shard merge without any allocation -------------------------------------------------
+// Scratch of the allocation-free merge: the three per-shard tables (pointers and row bases)
+// and the block sums of the offset scan.  It is a fixed part of the module image, so every
+// GPU that loads the library carries these 32 KB until the process exits.
+constexpr int NOALLOC_MAX_SHARDS = 64;
+constexpr int NOALLOC_MAX_QUERIES = 1 << 22;
+constexpr size_t NOALLOC_TABLE_BYTES = 512;  // one table: 64 entries of 8 bytes
+constexpr size_t NOALLOC_SCAN_OFFSET = 2048;
+constexpr size_t NOALLOC_SCRATCH_BYTES = 32768;
+static_assert(NOALLOC_SCAN_OFFSET + (NOALLOC_MAX_QUERIES / SCAN_TILE + 2) * sizeof(uint64_t) <= NOALLOC_SCRATCH_BYTES,
+              "scan block sums must fit the static scratch");
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+static void* g_noalloc_scratch_addr[64] = {};  // device address of the array, per device ordinal
+
+int culsh_merge_shard_candidates_noalloc(culsh_handle* h, int n_shards, int n_q,
+                                         const int32_t* const* shard_indices,
+                                         const uint64_t* const* shard_offsets, const int64_t* row_base,
+                                         int32_t* out_indices, uint64_t out_capacity, uint64_t* out_counts,
+                                         uint64_t* out_offsets, uint64_t* total_out) {
+    return guarded([&] {
+        if (!h || !shard_indices || !shard_offsets || !row_base || !out_counts || !out_offsets || !total_out)
+            fail(CULSH_ERR_INVALID, "null argument");
+        if (n_shards <= 0 || n_q < 0) fail(CULSH_ERR_INVALID, "bad shard or query count");
+        if (n_shards > NOALLOC_MAX_SHARDS)
+            fail(CULSH_ERR_UNSUPPORTED, "allocation-free merge takes at most %d shards (got %d)",
+                 NOALLOC_MAX_SHARDS, n_shards);
+        if (n_q > NOALLOC_MAX_QUERIES)
+            fail(CULSH_ERR_UNSUPPORTED, "allocation-free merge takes at most %d queries (got %d)",
+                 NOALLOC_MAX_QUERIES, n_q);
+        const CtxPtr& c = h->ctx;
+        if (c->device < 0 || c->device >= 64) fail(CULSH_ERR_UNSUPPORTED, "device ordinal out of range");
+        DeviceGuard g(c->device);
+        cudaStream_t s = c->stream;
+        // Set-up, once per device and with that device current: in host code the array's name is
+        // only a handle for the runtime, the kernels need its address in device memory.
+        if (!g_noalloc_scratch_addr[c->device]) {
+            void* addr = nullptr;
+            CU_CHECK(cudaGetSymbolAddress(&addr, g_noalloc_scratch));
+            g_noalloc_scratch_addr[c->device] = addr;
+        }
+        unsigned char* base = static_cast<unsigned char*>(g_noalloc_scratch_addr[c->device]);
+        *total_out = 0;
+        if (n_q == 0) {
+            CU_CHECK(cudaMemsetAsync(out_offsets, 0, sizeof(uint64_t), s));
+            CU_CHECK(cudaStreamSynchronize(s));
+            return;
+        }
+        auto** d_idx = reinterpret_cast<const int32_t**>(base);
+        auto** d_off = reinterpret_cast<const uint64_t**>(base + NOALLOC_TABLE_BYTES);
+        auto* d_base = reinterpret_cast<int64_t*>(base + 2 * NOALLOC_TABLE_BYTES);
+        auto* d_sums = reinterpret_cast<uint64_t*>(base + NOALLOC_SCAN_OFFSET);
+        // every scratch word read below is written first by these copies or by the scan's own
+        // reduce step, so nothing has to be cleared between calls
+        CU_CHECK(cudaMemcpyAsync(d_idx, shard_indices, sizeof(void*) * n_shards, cudaMemcpyHostToDevice, s));
+        CU_CHECK(cudaMemcpyAsync(d_off, shard_offsets, sizeof(void*) * n_shards, cudaMemcpyHostToDevice, s));
+        CU_CHECK(cudaMemcpyAsync(d_base, row_base, sizeof(int64_t) * n_shards, cudaMemcpyHostToDevice, s));
+        shard_counts_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(d_off, n_shards, n_q, out_counts);
+        KERNEL_CHECK();
+        exclusive_scan<uint64_t, uint64_t>(s, out_counts, n_q, out_offsets, d_sums);
+        uint64_t total = 0;
+        read_words(c, out_offsets + n_q, sizeof(uint64_t), &total);
+        *total_out = total;
+        if (total > out_capacity)
+            fail(CULSH_ERR_INVALID, "out_indices holds %llu ids but the merged result has %llu",
+                 (unsigned long long)out_capacity, (unsigned long long)total);
+        if (total) {
+            if (!out_indices) fail(CULSH_ERR_INVALID, "out_indices is null");
+            size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
+            shard_interleave_kernel<<<(unsigned)blocks, 256, 0, s>>>(d_idx, d_off, d_base, n_shards, n_q,
+                                                                    out_offsets, out_indices);
+            KERNEL_CHECK();
+        }
+        CU_CHECK(cudaStreamSynchronize(s));
+    });
+}
+
 }  // extern "C"

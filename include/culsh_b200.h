@@ -195,6 +195,39 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_queries,
                                  const uint64_t* const* shard_offsets, const int64_t* row_base,
                                  culsh_candidates** out);
 
+/* Same merge for callers that must not allocate (no counterpart in the reference).
+ *
+ * Some hosts of this library cannot call cudaMalloc at the point where shard results are
+ * merged: a serving process whose framework has already claimed the whole device for its own
+ * caching allocator, a latency-critical loop where the implicit device synchronisation of
+ * cudaMalloc / cudaFree is not acceptable, or code that runs under a fixed memory budget
+ * audited at start-up.  This variant therefore takes every result array from the caller and
+ * keeps its only temporaries - the per-shard pointer / row-base tables and the block sums of
+ * the offset scan - in a 32 KB array that is a fixed part of the library image (each GPU that
+ * loads the library holds those 32 KB until the process exits).  It calls no cudaMalloc,
+ * cudaFree or other allocating routine.
+ *
+ *   out_indices  device, room for out_capacity ids (may be NULL when the result is empty)
+ *   out_counts   device, n_queries uint64
+ *   out_offsets  device, n_queries + 1 uint64
+ *   total_out    host; receives the merged id count, also when out_capacity is too small
+ *                (the call then fails with CULSH_ERR_INVALID and writes no ids)
+ *
+ * Limits: at most 64 shards and 4,194,304 queries per call; more is CULSH_ERR_UNSUPPORTED.
+ * The first call on a device looks the array's device address up once (with that device
+ * current); make that first call before starting any stream capture.  All calls on a device
+ * share the array and it keeps whatever the previous call left there - every word a call
+ * reads is written earlier in the same call, so nothing needs clearing - which also means
+ * two calls that overlap on the same GPU (different handles or threads) race on it: serialise
+ * them.  The shard arrays are device pointers on the handle's device, as for
+ * culsh_merge_shard_candidates; the three tables themselves are host arrays. */
+int culsh_merge_shard_candidates_noalloc(culsh_handle* h, int n_shards, int n_queries,
+                                         const int32_t* const* shard_indices,
+                                         const uint64_t* const* shard_offsets, const int64_t* row_base,
+                                         int32_t* out_indices, uint64_t out_capacity,
+                                         uint64_t* out_counts, uint64_t* out_offsets,
+                                         uint64_t* total_out);
+
 #ifdef __cplusplus
 }
 #endif
