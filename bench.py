@@ -11,8 +11,9 @@ with inputs resident in HBM; `e2e` is the same step through the public Python AP
 pinned HOST arrays in and the candidates CSR read back to the host.
 
 At N > 1 (torchrun, one rank per GPU) each rank holds its own 1M-row shard (weak scaling),
-the queries are the same on every rank, and the per-shard candidates are shifted to global
-row ids and gathered on rank 0 over NCCL, then interleaved into one CSR.
+the queries are the same on every rank, and the per-shard candidates are exchanged over NCCL
+(one all-to-all) so that rank j holds the merged CSR, with global row ids, of the j-th slice
+of the queries.
 
 `--impl reference` times upstream cuLSH's own CUDA build (oracle/_ref, compiled from the
 upstream sources by oracle/Makefile) on the same workload when that module loads, else the
@@ -211,8 +212,8 @@ def run_ours(args):
         s_fit = core.last_stats()
         cand = model.query(Q, batch_size=N_QUERIES)
         s_q = core.last_stats()
-        if world > 1:
-            cand = sharded.gather_candidates(cand, row_base=rank * N_ROWS, dst=0)
+        if world > 1:  # each rank receives the merged lists of its slice of the queries
+            cand, _ = sharded.exchange_by_query(cand, row_base=rank * N_ROWS)
         d2h = 0
         if host_out and cand is not None:
             off = cand.get_offsets()

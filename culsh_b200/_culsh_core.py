@@ -98,6 +98,64 @@ def _is_device_obj(obj) -> bool:
     return type(obj).__module__.startswith("torch") and bool(getattr(obj, "is_cuda", False))
 
 
+class _PinnedBlock:
+    """A page-locked host block lent to one NumPy result array; it goes back to the pool when
+    the last view of that array dies."""
+
+    def __init__(self, pool, ptr, cap):
+        self._pool, self.ptr, self.cap = pool, ptr, cap
+        self.__array_interface__ = {"shape": (cap,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+    def __del__(self):
+        try:
+            self._pool._release(self.ptr, self.cap)
+        except Exception:  # interpreter shutdown
+            pass
+
+
+class _PinnedPool:
+    """Recycles page-locked blocks for large result arrays, so that steady-state getters copy
+    device -> pinned host memory at full PCIe rate instead of into fresh pageable pages.
+    CULSH_PINNED_POOL_MB bounds the bytes kept idle (default 2048, 0 disables pinning)."""
+    MIN_BYTES = 1 << 20
+
+    def __init__(self):
+        import os
+        self.limit = int(os.environ.get("CULSH_PINNED_POOL_MB", "2048")) << 20
+        self.free = []  # (cap, ptr)
+        self.idle = 0
+        self.lock = threading.Lock()
+
+    def acquire(self, nbytes):
+        if self.limit <= 0 or nbytes < self.MIN_BYTES:
+            return None
+        with self.lock:
+            best = None
+            for i, (cap, ptr) in enumerate(self.free):
+                if nbytes <= cap <= 2 * nbytes and (best is None or cap < self.free[best][0]):
+                    best = i
+            if best is not None:
+                cap, ptr = self.free.pop(best)
+                self.idle -= cap
+                return _PinnedBlock(self, ptr, cap)
+        cap = (nbytes + (1 << 20) - 1) >> 20 << 20
+        out = C.c_void_p()
+        if _lib.load().culsh_host_alloc(cap, C.byref(out)) != 0:
+            return None  # fall back to pageable memory
+        return _PinnedBlock(self, out.value, cap)
+
+    def _release(self, ptr, cap):
+        with self.lock:
+            if self.idle + cap <= self.limit:
+                self.free.append((cap, ptr))
+                self.idle += cap
+                return
+        _lib.load().culsh_host_free(C.c_void_p(ptr))
+
+
+_pinned_pool = _PinnedPool()
+
+
 def _alloc_out(n, dtype, as_cupy=False, as_torch=False, device=0):
     if as_cupy:
         import cupy as cp  # upstream imports cupy lazily too (bindings.cu:272)
@@ -110,6 +168,11 @@ def _alloc_out(n, dtype, as_cupy=False, as_torch=False, device=0):
                np.dtype(np.float32): torch.float32, np.dtype(np.float64): torch.float64}[np.dtype(dtype)]
         arr = torch.empty(int(n), dtype=tdt, device=f"cuda:{device}")
         return arr, int(arr.data_ptr())
+    nbytes = int(n) * np.dtype(dtype).itemsize
+    block = _pinned_pool.acquire(nbytes)
+    if block is not None:
+        arr = np.asarray(block)[:nbytes].view(dtype)  # arr.base chain keeps the block alive
+        return arr, int(block.ptr)
     arr = np.empty(int(n), dtype=dtype)
     return arr, int(arr.ctypes.data)
 

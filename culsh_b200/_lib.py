@@ -79,6 +79,8 @@ SIGNATURES = {
     "culsh_candidates_get_counts": [VP, VP],
     "culsh_candidates_get_offsets": [VP, VP],
     "culsh_candidates_device_ptrs": [VP, PP, PP, PP],
+    "culsh_host_alloc": [C.c_size_t, PP],
+    "culsh_host_free": [VP],
     "culsh_merge_shard_candidates": [VP, I, I, PP, PP, C.POINTER(C.c_int64), PP],
     "culsh_merge_shard_candidates_noalloc": [VP, I, I, PP, PP, C.POINTER(C.c_int64), VP, U64, VP, VP,
                                              C.POINTER(C.c_uint64)],

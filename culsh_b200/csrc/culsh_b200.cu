@@ -1151,6 +1151,26 @@ void culsh_candidates_free(culsh_candidates* c) {
     if (prev >= 0) cudaSetDevice(prev);
 }
 
+// ---- pinned host buffers ----------------------------------------------------------------
+int culsh_host_alloc(size_t bytes, void** out) {
+    return guarded([&] {
+        if (!out || bytes == 0) fail(CULSH_ERR_INVALID, "bad argument");
+        void* p = nullptr;
+        cudaError_t e = cudaHostAlloc(&p, bytes, cudaHostAllocPortable);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            fail(CULSH_ERR_ALLOC, "pinned host allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+        }
+        *out = p;
+    });
+}
+
+int culsh_host_free(void* p) {
+    return guarded([&] {
+        if (p) CU_CHECK(cudaFreeHost(p));
+    });
+}
+
 // ---- shard merge ------------------------------------------------------------------------
 int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
                                  const int32_t* const* shard_indices,

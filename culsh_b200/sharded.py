@@ -86,3 +86,53 @@ def gather_candidates(cand, row_base: int, dst: int = 0, group=None, row_bases: 
         [t.data_ptr() if t.numel() else 0 for t in idx_list], [t.data_ptr() for t in off_list],
         row_bases, cand.n_queries, device=idx.device.index)
     return merged
+
+
+def exchange_by_query(cand, row_base: int, group=None, row_bases: Optional[List[int]] = None):
+    """Balanced form of the exchange: rank j ends up with the merged CSR (global row ids) of the
+    query slice ``shard_bounds(n_queries, world, j)``; returns ``(Candidates, (q_lo, q_hi))``.
+
+    Every rank sends each peer only the lists of that peer's queries - a contiguous piece of its
+    own CSR - in one all-to-all, so no GPU receives more than one shard's worth of ids, where
+    gathering on a single root receives all of them.
+    """
+    import torch
+    import torch.distributed as dist
+    from . import _culsh_core
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    nq = cand.n_queries
+    idx = cand.get_indices(as_torch=True)
+    off = cand.get_offsets(as_torch=True).view(torch.int64)
+    dev = off.device
+    bounds = [shard_bounds(nq, world, j) for j in range(world)]
+    cuts = torch.tensor([b[0] for b in bounds] + [nq], dtype=torch.int64, device=dev)
+    cut_vals = off[cuts].tolist()                      # world + 1 numbers to the host
+    send_counts = [cut_vals[j + 1] - cut_vals[j] for j in range(world)]
+    if row_bases is None:
+        b = torch.tensor([row_base], dtype=torch.int64, device=dev)
+        bs = [torch.zeros_like(b) for _ in range(world)]
+        dist.all_gather(bs, b, group=group)
+        row_bases = [int(x.item()) for x in bs]
+    sc = torch.tensor(send_counts, dtype=torch.int64, device=dev)
+    rc = torch.empty_like(sc)
+    dist.all_to_all_single(rc, sc, group=group)
+    recv_counts = [int(x) for x in rc.tolist()]
+    recv_idx = torch.empty(max(1, sum(recv_counts)), dtype=torch.int32, device=dev)
+    dist.all_to_all_single(recv_idx[:sum(recv_counts)], idx, output_split_sizes=recv_counts,
+                           input_split_sizes=send_counts, group=group)
+    send_off = torch.cat([off[lo:hi + 1] - off[lo] for lo, hi in bounds])
+    lo_r, hi_r = bounds[rank]
+    my_len = hi_r - lo_r + 1
+    recv_off = torch.empty(world * my_len, dtype=torch.int64, device=dev)
+    dist.all_to_all_single(recv_off, send_off, output_split_sizes=[my_len] * world,
+                           input_split_sizes=[hi - lo + 1 for lo, hi in bounds], group=group)
+    torch.cuda.synchronize()
+    idx_ptrs, off_ptrs, start = [], [], 0
+    for s in range(world):
+        idx_ptrs.append(recv_idx.data_ptr() + 4 * start)
+        off_ptrs.append(recv_off.data_ptr() + 8 * s * my_len)
+        start += recv_counts[s]
+    merged = _culsh_core.merge_shard_candidates(idx_ptrs, off_ptrs, row_bases, my_len - 1,
+                                                device=dev.index)
+    return merged, (lo_r, hi_r)

@@ -185,6 +185,13 @@ int culsh_candidates_device_ptrs(const culsh_candidates* c, const int32_t** indi
                                  const uint64_t** counts, const uint64_t** offsets);
 void culsh_candidates_free(culsh_candidates* c);
 
+/* ---- pinned host buffers for results --------------------------------------------------- */
+/* Upstream's getters copy into freshly allocated pageable NumPy memory (bindings.cu:268-338),
+ * which caps the device->host read of a large CSR at a few GB/s.  These two calls let a
+ * binding keep a pool of page-locked blocks for result arrays (culsh_b200/_culsh_core.py does). */
+int culsh_host_alloc(size_t bytes, void** out);
+int culsh_host_free(void* p);
+
 /* ---- row-sharded indexes (no upstream counterpart: upstream is single-GPU) ------------- */
 /* Interleave R per-shard CSR results that were produced for the same queries into one CSR
  * with global row ids: shard r's ids are shifted by row_base[r]; per query the shard lists
