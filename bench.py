@@ -213,7 +213,8 @@ def run_ours(args):
         cand = model.query(Q, batch_size=N_QUERIES)
         s_q = core.last_stats()
         if world > 1:  # each rank receives the merged lists of its slice of the queries
-            cand, _ = sharded.exchange_by_query(cand, row_base=rank * N_ROWS)
+            cand, _ = sharded.exchange_by_query(cand, row_base=rank * N_ROWS,
+                                                    row_bases=[r * N_ROWS for r in range(world)])
         d2h = 0
         if host_out and cand is not None:
             off = cand.get_offsets()
@@ -276,10 +277,10 @@ def run_ours(args):
             "tf32_tflops_measured": tf32, "traffic": None}
     proj["frac"] = proj["achieved"] / proj["peak"]
     sort_bytes = items * (kb + 4) * 2.0
-    sort = {"bound": "hbm", "achieved": sort_bytes * passes / (scatter_ms * 1e-3) / 1e9,
-            "peak": peaks["hbm_gbs"], "unit": "GB/s", "kernel": "radix_pass_kernel",
-            "note": f"(key {kb} B + row id 4 B) read + written per item per pass, {passes} passes, "
-                    f"over the CUDA-event time of the passes; peak {peaks['source']}", "traffic": None}
+    sort = {"bound": "hbm", "achieved": sort_bytes / (scatter_ms * 1e-3) / 1e9,
+            "peak": peaks["hbm_gbs"], "unit": "GB/s", "kernel": "radix_scatter_kernel",
+            "note": f"(key {kb} B + row id 4 B) read + written per item, one launch (the scatter of the "
+                    f"last of {passes} passes) timed with CUDA events; peak {peaks['source']}", "traffic": None}
     sort["frac"] = sort["achieved"] / sort["peak"]
     gat_bytes = 4.0 * (sq["raw_candidates"] + 3 * sq["unique_candidates"])
     gather = {"bound": "hbm", "achieved": gat_bytes / (gather_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],

@@ -85,9 +85,9 @@ struct StageTimer {
     void mark() {
         if (c->profiling && next < 7) cudaEventRecord(c->ev[next++], c->stream);
     }
-    float since_scatter_start(int b) const {  // ev[7] is recorded by the sort driver
+    float last_scatter() const {  // ev_pass[] are recorded by the sort driver
         float ms = 0.f;
-        if (c->profiling && b < next) cudaEventElapsedTime(&ms, c->ev[7], c->ev[b]);
+        if (c->profiling) cudaEventElapsedTime(&ms, c->ev_pass[0], c->ev_pass[1]);
         return ms;
     }
     float between(int a, int b) const {
@@ -313,7 +313,7 @@ struct SortBuffers {
     uint32_t* vals[2] = {nullptr, nullptr};
     DevBuf<uint32_t> vals_out;   // receives the sorted row ids: becomes the index's candidate array
     Scratch<uint32_t> vals_tmp;
-    Scratch<uint32_t> ghist, status, counter;
+    Scratch<uint32_t> tile_hist;
     int final_buf = 0;
     void alloc(const CtxPtr& c, size_t items, const KeySpec& ks, int n, int L) {
         keys[0].reserve(c, SL_KEYS0, items * ks.key_words);
@@ -323,9 +323,7 @@ struct SortBuffers {
         vals_tmp.reserve(c, SL_VALS, items);
         vals[final_buf] = vals_out.p;
         vals[final_buf ^ 1] = vals_tmp.p;
-        ghist.reserve(c, SL_GHIST, (size_t)L * ks.key_bytes * 256);
-        status.reserve(c, SL_STATUS, radix_sort_status_words(n, L, ks.key_words));
-        counter.reserve(c, SL_COUNTER, 1);
+        tile_hist.reserve(c, SL_STATUS, radix_sort_tile_words(n, L, ks.key_words));
     }
 };
 
@@ -337,8 +335,7 @@ int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_buck
     const int n = ix.n, L = ix.L, NW = ix.ks.key_words;
     uint32_t* kp[2] = {sb.keys[0].p, sb.keys[1].p};
     uint32_t* vp[2] = {sb.vals[0], sb.vals[1]};
-    int cur = radix_sort_tables(c, NW, kp, vp, n, L, ix.ks.key_bytes, sb.ghist.p, sb.status.p,
-                                sb.counter.p);
+    int cur = radix_sort_tables(c, NW, kp, vp, n, L, ix.ks.key_bytes, sb.tile_hist.p);
     tm.mark();
     const int tpt = (int)ceil_div(n, IB_TILE);
     const size_t n_tiles = (size_t)tpt * L;
@@ -422,7 +419,7 @@ void fit_common(culsh_index& ix, HashFn&& hash_fn, Scratch<int32_t>* item_to_buc
         CU_CHECK(cudaStreamSynchronize(c->stream));  // the stage events must have completed
         c->stats.hash_ms = tm.between(0, 1);
         c->stats.sort_ms = tm.between(1, 2);
-        c->stats.scatter_ms = tm.since_scatter_start(2);
+        c->stats.scatter_ms = tm.last_scatter();
         c->stats.build_ms = tm.between(2, 3);
         c->stats.total_ms = tm.between(0, 3);
         break;
@@ -720,6 +717,7 @@ int culsh_create(int device, culsh_handle** out) {
         CU_CHECK(cudaStreamCreate(&c->stream));  // blocking stream, as upstream (cuda_utils.cuh:38)
         CU_CHECK(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
         for (auto& e : c->ev) CU_CHECK(cudaEventCreate(&e));
+        for (auto& e : c->ev_pass) CU_CHECK(cudaEventCreate(&e));
         for (auto& e : c->copy_done) CU_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         for (auto& e : c->chunk_free) CU_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         CU_CHECK(cudaMallocHost(&c->pinned, 64 * sizeof(uint64_t)));

@@ -2,13 +2,11 @@
 // per 8-bit digit.  Replaces upstream's loop of extract_byte_key_kernel +
 // cub::DeviceRadixSort::SortPairs per signature byte plus the table-id pass
 // (core/fit.cuh:254-282): here the packed key travels with the row id, so no pass gathers
-// signature bytes at random, tables never mix (a tile belongs to one table), and a pass
-// reads and writes each pair exactly once (single-sweep scatter whose tile prefixes come
-// from a decoupled look-back over the preceding tiles of the same table).
-//
-// Every wait on another tile's status word is bounded: when it runs out the kernel records
-// DEV_ERR_LOOKBACK_TIMEOUT in the handle's error word and carries on to completion; the
-// host then reports CULSH_ERR_INTERNAL.
+// signature bytes at random, and tables never mix (a tile belongs to one table).  A pass is
+// three launches - tile histograms, a per-table scan that turns them into destination
+// offsets, and the stable scatter - so no CTA ever waits on another one: a chained
+// look-back between tiles was measured to cost more than the extra 4 bytes per item that
+// the histogram read adds at this bandwidth.
 #pragma once
 
 #include "common.cuh"
@@ -78,81 +76,88 @@ __device__ __forceinline__ void store_key(uint32_t* __restrict__ dst, const uint
 }
 
 // ---------------------------------------------------------------------------------------
-// Digit histograms of every byte position, one read of the keys.
-// ghist layout: [L][KB][256].
+// Pass step 1: digit histogram of every tile (a tile is TILE consecutive items of one
+// table).  tile_hist layout: [tile][256].
 // ---------------------------------------------------------------------------------------
-constexpr int RS_HIST_CHUNK = 16384;
-
 template <int NW>
 __global__ void __launch_bounds__(RS_THREADS)
-radix_hist_kernel(const uint32_t* __restrict__ keys, int n, int KB, uint32_t* __restrict__ ghist) {
-    extern __shared__ uint32_t sh_hist[];  // [KB][256]
-    const int t = blockIdx.y;
-    for (int i = threadIdx.x; i < KB * 256; i += RS_THREADS) sh_hist[i] = 0;
+radix_tile_hist_kernel(const uint32_t* __restrict__ keys, int n, int tiles_per_table, int p,
+                       uint32_t* __restrict__ tile_hist) {
+    using Cfg = SortCfg<NW>;
+    __shared__ uint32_t s_hist[256];
+    const int tile = blockIdx.x;
+    const int t = tile / tiles_per_table;
+    const int lt = tile - t * tiles_per_table;
+    const int item0 = lt * Cfg::TILE;
+    const int count = min(Cfg::TILE, n - item0);
+    const uint32_t* base = keys + ((size_t)t * n + item0) * NW + (NW - 1 - (p >> 2));
+    const int shift = 8 * (p & 3);
+    s_hist[threadIdx.x] = 0;
     __syncthreads();
-    const int begin = blockIdx.x * RS_HIST_CHUNK;
-    const int end = min(n, begin + RS_HIST_CHUNK);
-    const int n_words = (KB + 3) / 4;
-    for (int i = begin + threadIdx.x; i < end; i += RS_THREADS) {
-        const uint32_t* kp = keys + ((size_t)t * n + i) * NW;
-        for (int w = 0; w < n_words; ++w) {
-            const uint32_t word = kp[NW - 1 - w];
+#pragma unroll 4
+    for (int i = threadIdx.x; i < count; i += RS_THREADS)
+        atomicAdd(&s_hist[(base[(size_t)i * NW] >> shift) & 0xFFu], 1u);
+    __syncthreads();
+    tile_hist[(size_t)tile * 256 + threadIdx.x] = s_hist[threadIdx.x];
+}
+
+// ---------------------------------------------------------------------------------------
+// Pass step 2: one block per table turns the tile histograms into the offset (inside the
+// table) at which each tile's run of each digit starts:
+//   off[tile][d] = sum over d' < d of total[d'] + sum over earlier tiles of hist[tile'][d].
+// 1024 threads = 4 tile segments x 256 digits.
+// ---------------------------------------------------------------------------------------
+constexpr int RS_SCAN_THREADS = 1024;
+constexpr int RS_SCAN_SEGS = RS_SCAN_THREADS / 256;
+
+__global__ void __launch_bounds__(RS_SCAN_THREADS)
+radix_tile_scan_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table) {
+    __shared__ uint32_t s_seg[RS_SCAN_SEGS][256];
+    __shared__ uint32_t s_base[256];
+    __shared__ uint32_t s_warp[8];
+    const int d = threadIdx.x & 255, seg = threadIdx.x >> 8;
+    uint32_t* h = tile_hist + (size_t)blockIdx.x * tiles_per_table * 256 + d;
+    const int per_seg = (tiles_per_table + RS_SCAN_SEGS - 1) / RS_SCAN_SEGS;
+    const int i0 = seg * per_seg, i1 = min(tiles_per_table, i0 + per_seg);
+    uint32_t sum = 0;
+#pragma unroll 8
+    for (int i = i0; i < i1; ++i) sum += h[(size_t)i * 256];
+    s_seg[seg][d] = sum;
+    __syncthreads();
+    if (seg == 0) {  // exclusive scan of the digit totals over the 256 digits
+        uint32_t tot = 0;
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const int p = w * 4 + b;
-                if (p < KB) atomicAdd(&sh_hist[p * 256 + ((word >> (8 * b)) & 0xFFu)], 1u);
-            }
+        for (int g = 0; g < RS_SCAN_SEGS; ++g) tot += s_seg[g][d];
+        const int lane = d & 31, w = d >> 5;
+        uint32_t inc = tot;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += x;
         }
+        if (lane == 31) s_warp[w] = inc;
+        s_base[d] = inc - tot;  // exclusive inside the warp; the warp bases are added below
     }
     __syncthreads();
-    uint32_t* g = ghist + (size_t)t * KB * 256;
-    for (int i = threadIdx.x; i < KB * 256; i += RS_THREADS) {
-        uint32_t v = sh_hist[i];
-        if (v) atomicAdd(&g[i], v);
+    uint32_t run = s_base[d];
+    for (int w = 0; w < (d >> 5); ++w) run += s_warp[w];
+    for (int g = 0; g < seg; ++g) run += s_seg[g][d];
+#pragma unroll 8
+    for (int i = i0; i < i1; ++i) {
+        uint32_t x = h[(size_t)i * 256];
+        h[(size_t)i * 256] = run;
+        run += x;
     }
-}
-
-// In-place exclusive scan of each 256-bin histogram: one block per (table, byte).
-__global__ void __launch_bounds__(256) radix_bin_prefix_kernel(uint32_t* __restrict__ ghist) {
-    __shared__ uint32_t warp_tot[8];
-    uint32_t* h = ghist + (size_t)blockIdx.x * 256;
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    uint32_t v = h[threadIdx.x];
-    uint32_t inc = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-        if (lane >= o) inc += x;
-    }
-    if (lane == 31) warp_tot[w] = inc;
-    __syncthreads();
-    uint32_t base = 0;
-    for (int i = 0; i < w; ++i) base += warp_tot[i];
-    h[threadIdx.x] = base + inc - v;
 }
 
 // ---------------------------------------------------------------------------------------
-// One scatter pass on byte `p`.
+// Pass step 3: stable scatter of one tile on byte `p`.
 // ---------------------------------------------------------------------------------------
-constexpr uint32_t RS_FLAG_AGG = 1u << 30;
-constexpr uint32_t RS_FLAG_INC = 2u << 30;
-constexpr uint32_t RS_VAL_MASK = (1u << 30) - 1;
-constexpr int RS_SPIN_LIMIT = 1 << 22;
-
-__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) {
-    return *reinterpret_cast<const volatile uint32_t*>(p);
-}
-__device__ __forceinline__ void st_volatile_u32(uint32_t* p, uint32_t v) {
-    *reinterpret_cast<volatile uint32_t*>(p) = v;
-}
-
 template <int NW, bool FIRST>
 __global__ void __launch_bounds__(RS_THREADS)
-radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
-                  uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int n,
-                  int tiles_per_table, int p, int KB, const uint32_t* __restrict__ gbase,
-                  uint32_t* __restrict__ status, uint32_t* __restrict__ tile_counter,
-                  int* __restrict__ d_error) {
+radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+                     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int n,
+                     int tiles_per_table, int p, const uint32_t* __restrict__ tile_off) {
     using Cfg = SortCfg<NW>;
     constexpr int IPT = Cfg::IPT;
     constexpr int TILE = Cfg::TILE;
@@ -165,18 +170,16 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
     uint32_t* s_misc = s_binstart + 256;           // [32]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) s_misc[0] = atomicAdd(tile_counter, 1u);
-    for (int i = tid; i < RS_WARPS * 256; i += RS_THREADS) s_whist[i] = 0;
-    __syncthreads();
-    const uint32_t tile = s_misc[0];
+    const int tile = blockIdx.x;
     const int t = tile / tiles_per_table;
     const int lt = tile - t * tiles_per_table;
     const int item0 = lt * TILE;
     const int count = min(TILE, n - item0);
     const size_t base = (size_t)t * n + item0;
-    const uint32_t my_gbase = gbase[((size_t)t * KB + p) * 256 + tid];  // needed late: fetch early
+    const uint32_t my_off = tile_off[(size_t)tile * 256 + tid];  // needed late: fetch early
+    for (int i = tid; i < RS_WARPS * 256; i += RS_THREADS) s_whist[i] = 0;
 
-    // ---- load (all loads in flight together), then rank inside the warp ---------------
+    // ---- load (all loads in flight together) ------------------------------------------
     uint32_t key[IPT][NW];
     uint32_t val[IPT];
     uint16_t rank[IPT];
@@ -193,23 +196,26 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
             val[i] = 0;
         }
     }
+    __syncthreads();
+    // ---- rank inside the warp: lanes holding the same digit elect their lowest lane, which
+    // bumps the warp's counter once; lane order inside the group keeps the sort stable ----
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
         const int li = warp * (32 * IPT) + i * 32 + lane;
         const bool valid = li < count;
         const uint32_t d = valid ? key_digit<NW>(key[i], p) : 0x100u;
         const uint32_t peers = __match_any_sync(0xFFFFFFFFu, d);
+        const int leader = __ffs(peers) - 1;
         const uint32_t below = __popc(peers & ((1u << lane) - 1));
-        uint32_t old = valid ? s_whist[warp * 256 + d] : 0u;
-        __syncwarp();
-        if (valid && below == 0) s_whist[warp * 256 + d] = old + __popc(peers);
-        __syncwarp();
+        uint32_t old = 0;
+        if (valid && lane == leader) old = atomicAdd(&s_whist[warp * 256 + d], (uint32_t)__popc(peers));
+        old = __shfl_sync(0xFFFFFFFFu, old, leader);
         rank[i] = (uint16_t)(old + below);
         dig[i] = (uint16_t)d;
     }
     __syncthreads();
 
-    // ---- per-bin: warp offsets, tile count, look-back --------------------------------
+    // ---- per bin: exclusive offsets of the warps, tile count, start inside the tile ----
     uint32_t cnt = 0;
     {
         const int b = tid;
@@ -220,12 +226,6 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
             cnt += x;
         }
     }
-    // publish as early as possible so later tiles can move on
-    uint32_t* my_status = status + (size_t)tile * 256 + tid;
-    if (lt == 0) st_volatile_u32(my_status, RS_FLAG_INC | cnt);
-    else st_volatile_u32(my_status, RS_FLAG_AGG | cnt);
-
-    // block exclusive scan of cnt over the 256 bins
     uint32_t inc = cnt;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -237,46 +237,8 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
     uint32_t wbase = 0;
     for (int i = 0; i < warp; ++i) wbase += s_misc[1 + i];
     const uint32_t binstart = wbase + inc - cnt;
-
-    uint32_t excl = 0;
-    if (lt != 0) {
-        // Walk back over the preceding tiles of this table, eight status words per round so
-        // their latencies overlap; stop at the first tile that published an inclusive prefix.
-        int j = (int)tile - 1;
-        const int first = (int)tile - lt;
-        bool timed_out = false, done = false;
-        while (!done && !timed_out) {
-            uint32_t sv[8];
-            const int avail = min(8, j - first + 1);
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                sv[u] = u < avail ? ld_volatile_u32(status + (size_t)(j - u) * 256 + tid) : 0u;
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                if (u < avail && !done && !timed_out) {
-                    uint32_t s = sv[u];
-                    if ((s >> 30) == 0) {
-                        const uint32_t* sp = status + (size_t)(j - u) * 256 + tid;
-                        int spins = 0;
-                        while ((s >> 30) == 0) {
-                            if (++spins > RS_SPIN_LIMIT) { timed_out = true; break; }
-                            if (spins > 32) __nanosleep(40);
-                            s = ld_volatile_u32(sp);
-                        }
-                    }
-                    if (!timed_out) {
-                        excl += s & RS_VAL_MASK;
-                        if ((s >> 30) == 2u || j - u == first) done = true;
-                    }
-                }
-            }
-            j -= 8;
-        }
-        if (timed_out) atomicOr(d_error, DEV_ERR_LOOKBACK_TIMEOUT);
-        st_volatile_u32(my_status, RS_FLAG_INC | ((excl + cnt) & RS_VAL_MASK));
-    }
     s_binstart[tid] = binstart;
-    s_gdst[tid] = (uint32_t)((size_t)t * n) + my_gbase + excl - binstart;
+    s_gdst[tid] = (uint32_t)((size_t)t * n) + my_off - binstart;
     __syncthreads();
 
     // ---- reorder inside shared memory ------------------------------------------------
@@ -307,60 +269,53 @@ radix_pass_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restri
 // ---------------------------------------------------------------------------------------
 // Host driver.  keys[0]/vals[0] hold the input (vals[0] is never read: the first pass
 // takes the row id from the position); returns which buffer (0/1) holds the result.
+// tile_hist must hold radix_sort_tile_words(n, L, NW) words.
 // ---------------------------------------------------------------------------------------
 template <int NW>
 inline int radix_sort_tables_nw(const CtxPtr& c, uint32_t* keys[2], uint32_t* vals[2], int n, int L,
-                                int KB, uint32_t* ghist, uint32_t* status, uint32_t* tile_counter) {
+                                int KB, uint32_t* tile_hist) {
     using Cfg = SortCfg<NW>;
     cudaStream_t s = c->stream;
     const int tiles_per_table = (int)ceil_div(n, Cfg::TILE);
     const size_t total_tiles = (size_t)tiles_per_table * L;
-    CU_CHECK(cudaMemsetAsync(ghist, 0, sizeof(uint32_t) * (size_t)L * KB * 256, s));
-    dim3 hgrid((unsigned)ceil_div(n, RS_HIST_CHUNK), (unsigned)L);
-    const size_t hist_smem = sizeof(uint32_t) * KB * 256;
-    if (hist_smem > 48 * 1024)
-        CU_CHECK(cudaFuncSetAttribute(radix_hist_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)hist_smem));
-    radix_hist_kernel<NW><<<hgrid, RS_THREADS, hist_smem, s>>>(keys[0], n, KB, ghist);
-    KERNEL_CHECK();
-    radix_bin_prefix_kernel<<<(unsigned)(L * KB), 256, 0, s>>>(ghist);
-    KERNEL_CHECK();
-    if (c->profiling) cudaEventRecord(c->ev[7], s);  // start of the scatter passes
-    auto k_first = radix_pass_kernel<NW, true>;
-    auto k_next = radix_pass_kernel<NW, false>;
+    auto k_first = radix_scatter_kernel<NW, true>;
+    auto k_next = radix_scatter_kernel<NW, false>;
     CU_CHECK(cudaFuncSetAttribute(k_first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     CU_CHECK(cudaFuncSetAttribute(k_next, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     int cur = 0;
     for (int p = 0; p < KB; ++p) {
-        CU_CHECK(cudaMemsetAsync(status, 0, sizeof(uint32_t) * total_tiles * 256, s));
-        CU_CHECK(cudaMemsetAsync(tile_counter, 0, sizeof(uint32_t), s));
+        radix_tile_hist_kernel<NW><<<(unsigned)total_tiles, RS_THREADS, 0, s>>>(keys[cur], n, tiles_per_table,
+                                                                              p, tile_hist);
+        KERNEL_CHECK();
+        radix_tile_scan_kernel<<<(unsigned)L, RS_SCAN_THREADS, 0, s>>>(tile_hist, tiles_per_table);
+        KERNEL_CHECK();
+        const bool last = p == KB - 1;
+        if (last && c->profiling) cudaEventRecord(c->ev_pass[0], s);
         if (p == 0)
             k_first<<<(unsigned)total_tiles, RS_THREADS, Cfg::SMEM, s>>>(
-                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, KB, ghist,
-                status, tile_counter, c->d_error);
+                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, tile_hist);
         else
             k_next<<<(unsigned)total_tiles, RS_THREADS, Cfg::SMEM, s>>>(
-                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, KB, ghist,
-                status, tile_counter, c->d_error);
+                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, tile_hist);
         KERNEL_CHECK();
+        if (last && c->profiling) cudaEventRecord(c->ev_pass[1], s);
         cur ^= 1;
     }
     return cur;
 }
 
-inline size_t radix_sort_status_words(int n, int L, int NW) {
+inline size_t radix_sort_tile_words(int n, int L, int NW) {
     return ceil_div(n, sort_tile_items(NW)) * (size_t)L * 256;
 }
 
 inline int radix_sort_tables(const CtxPtr& c, int NW, uint32_t* keys[2], uint32_t* vals[2], int n,
-                             int L, int KB, uint32_t* ghist, uint32_t* status,
-                             uint32_t* tile_counter) {
+                             int L, int KB, uint32_t* tile_hist) {
     switch (NW) {
-        case 1: return radix_sort_tables_nw<1>(c, keys, vals, n, L, KB, ghist, status, tile_counter);
-        case 2: return radix_sort_tables_nw<2>(c, keys, vals, n, L, KB, ghist, status, tile_counter);
-        case 4: return radix_sort_tables_nw<4>(c, keys, vals, n, L, KB, ghist, status, tile_counter);
-        case 8: return radix_sort_tables_nw<8>(c, keys, vals, n, L, KB, ghist, status, tile_counter);
-        case 16: return radix_sort_tables_nw<16>(c, keys, vals, n, L, KB, ghist, status, tile_counter);
+        case 1: return radix_sort_tables_nw<1>(c, keys, vals, n, L, KB, tile_hist);
+        case 2: return radix_sort_tables_nw<2>(c, keys, vals, n, L, KB, tile_hist);
+        case 4: return radix_sort_tables_nw<4>(c, keys, vals, n, L, KB, tile_hist);
+        case 8: return radix_sort_tables_nw<8>(c, keys, vals, n, L, KB, tile_hist);
+        case 16: return radix_sort_tables_nw<16>(c, keys, vals, n, L, KB, tile_hist);
     }
     fail(CULSH_ERR_UNSUPPORTED, "unsupported key width: %d words", NW);
 }

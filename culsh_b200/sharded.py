@@ -15,6 +15,27 @@ from __future__ import annotations
 from typing import List, Optional, Tuple
 
 
+class _DeviceView:
+    """Zero-copy window on an array owned by a Candidates object (kept alive through `owner`)."""
+
+    def __init__(self, ptr: int, n: int, typestr: str, owner):
+        self.__cuda_array_interface__ = {"shape": (int(n),), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 3, "strides": None}
+        self._owner = owner
+
+
+def _csr_tensors(cand):
+    """(indices int32, offsets int64) torch tensors that alias the result's device arrays."""
+    import torch
+    ip, _, op = cand.device_pointers()
+    dev = f"cuda:{cand._h.device}"
+    n = cand.n_total_candidates
+    idx = (torch.as_tensor(_DeviceView(ip, n, "<i4", cand), device=dev) if n
+           else torch.empty(0, dtype=torch.int32, device=dev))
+    off = torch.as_tensor(_DeviceView(op, cand.n_queries + 1, "<i8", cand), device=dev)
+    return idx, off
+
+
 def shard_bounds(n_rows: int, world: int, rank: int) -> Tuple[int, int]:
     """Row range [lo, hi) of `rank`: ceil(n/world) rows per rank, the last ranks may be short."""
     per = -(-n_rows // world)
@@ -70,8 +91,7 @@ def gather_candidates(cand, row_base: int, dst: int = 0, group=None, row_bases: 
     from . import _culsh_core
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
-    idx = cand.get_indices(as_torch=True)
-    off = cand.get_offsets(as_torch=True).view(torch.int64)  # uint64 payload, int64 for the backend
+    idx, off = _csr_tensors(cand)  # uint64 offsets travel as int64
     if row_bases is None:
         b = torch.tensor([row_base], dtype=torch.int64, device=idx.device)
         bs = [torch.zeros_like(b) for _ in range(world)]
@@ -102,8 +122,7 @@ def exchange_by_query(cand, row_base: int, group=None, row_bases: Optional[List[
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     nq = cand.n_queries
-    idx = cand.get_indices(as_torch=True)
-    off = cand.get_offsets(as_torch=True).view(torch.int64)
+    idx, off = _csr_tensors(cand)
     dev = off.device
     bounds = [shard_bounds(nq, world, j) for j in range(world)]
     cuts = torch.tensor([b[0] for b in bounds] + [nq], dtype=torch.int64, device=dev)

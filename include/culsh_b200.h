@@ -72,7 +72,7 @@ typedef struct culsh_index_meta {
 /* Per-stage figures of the last fit / query on a handle (device time from CUDA events). */
 typedef struct culsh_stats {
     float hash_ms, sort_ms, build_ms, lookup_ms, gather_ms, total_ms;
-    float scatter_ms; /* the radix scatter passes alone (sort_ms also holds the histogram) */
+    float scatter_ms; /* the scatter launch of the last radix pass alone */
     float reserved0;
     uint64_t n_items, n_buckets, raw_candidates, unique_candidates;
     int32_t sort_passes, key_words, elem_bytes, hash_path; /* hash_path: 0 SIMT, 1 tcgen05 */
