@@ -333,6 +333,7 @@ struct SortBuffers {
 int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_bucket, StageTimer& tm) {
     const CtxPtr& c = ix.ctx;
     const int n = ix.n, L = ix.L, NW = ix.ks.key_words;
+    HostTrace tr;
     uint32_t* kp[2] = {sb.keys[0].p, sb.keys[1].p};
     uint32_t* vp[2] = {sb.vals[0], sb.vals[1]};
     int cur = radix_sort_tables(c, NW, kp, vp, n, L, ix.ks.key_bytes, sb.tile_hist.p);
@@ -352,11 +353,13 @@ int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_buck
     std::memcpy(&B, c->pinned, sizeof(uint32_t));
     std::memcpy(&err, c->pinned + 1, sizeof(int));
     if (err) return err;
+    tr.lap("sort+count+scan+sync");
     ix.n_buckets = (int)B;
     ix.bucket_keys.alloc(c, (size_t)B * NW);
     ix.bucket_offsets.alloc(c, (size_t)B + 1);
     ix.table_offsets.alloc(c, (size_t)L + 1);
     if (item_to_bucket) item_to_bucket->reserve(c, SL_I2B, (size_t)n * L);
+    tr.lap("alloc bucket arrays");
     CULSH_DISPATCH_NW(NW, launch_bucket_write<NW>(c->stream, kp[cur], vp[cur], n, L, tile_base.p,
                                                   ix.bucket_keys.p, ix.bucket_offsets.p,
                                                   ix.table_offsets.p,
@@ -450,19 +453,25 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     out.offsets.alloc(c, (size_t)n_q + 1);
     Scratch<uint64_t> raw_cnt(c, SL_RAW_CNT, n_q), raw_off(c, SL_RAW_OFF, (size_t)n_q + 1),
         scratch(c, SL_SCAN, scan_scratch_elems(n_q));
-    Scratch<uint32_t> big_list(c, SL_BIG_LIST, n_q), n_big(c, SL_NBIG, 1);
-    CU_CHECK(cudaMemsetAsync(n_big.p, 0, sizeof(uint32_t), s));
+    Scratch<uint32_t> big_list(c, SL_BIG_LIST, 2 * (size_t)n_q), n_big(c, SL_NBIG, 2);
+    uint32_t* mid_list = big_list.p + n_q;
+    const int wbits = bitmap_window_bits(c, ix.n);
+    // with more rows than two bitmap windows, mid-sized candidate sets are sorted in shared memory
+    const int mid_max = (size_t)ix.n > 2 * (size_t)wbits ? MID_MAX : 0;
+    CU_CHECK(cudaMemsetAsync(n_big.p, 0, 2 * sizeof(uint32_t), s));
     raw_count_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(matched, ix.bucket_offsets.p, n_q, L,
-                                                                 raw_cnt.p, big_list.p, n_big.p);
+                                                                 raw_cnt.p, big_list.p, mid_list, n_big.p,
+                                                                 mid_max);
     KERNEL_CHECK();
     exclusive_scan<uint64_t, uint64_t>(s, raw_cnt.p, n_q, raw_off.p, scratch.p);
     uint64_t raw_total = 0;
-    uint32_t nb = 0;
+    uint32_t nb = 0, nm = 0;
     CU_CHECK(cudaMemcpyAsync(c->pinned, raw_off.p + n_q, sizeof(uint64_t), cudaMemcpyDeviceToHost, s));
-    CU_CHECK(cudaMemcpyAsync(c->pinned + 1, n_big.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    CU_CHECK(cudaMemcpyAsync(c->pinned + 1, n_big.p, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
     CU_CHECK(cudaStreamSynchronize(s));
     std::memcpy(&raw_total, c->pinned, sizeof(uint64_t));
     std::memcpy(&nb, c->pinned + 1, sizeof(uint32_t));
+    std::memcpy(&nm, reinterpret_cast<const char*>(c->pinned + 1) + sizeof(uint32_t), sizeof(uint32_t));
     tr.lap("count+scan+sync");
     c->stats.raw_candidates += raw_total;
     if (raw_total == 0) {
@@ -480,8 +489,16 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
             matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, raw_off.p, n_q, L, tmp.p, out.counts.p);
         KERNEL_CHECK();
     }
+    if (nm) {
+        int id_bytes = 1;
+        while (id_bytes < 4 && ((uint64_t)ix.n - 1) >> (8 * id_bytes)) ++id_bytes;
+        size_t smem = sort_path_smem_bytes();
+        CU_CHECK(cudaFuncSetAttribute(dedupe_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dedupe_sort_kernel<<<nm, MS_THREADS, smem, s>>>(mid_list, matched, ix.bucket_offsets.p, ix.cand.p,
+                                                       raw_cnt.p, raw_off.p, L, id_bytes, tmp.p, out.counts.p);
+        KERNEL_CHECK();
+    }
     if (nb) {
-        int wbits = bitmap_window_bits(c, ix.n);
         size_t smem = bitmap_smem_bytes(wbits);
         CU_CHECK(cudaFuncSetAttribute(dedupe_bitmap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dedupe_bitmap_kernel<<<nb, BM_THREADS, smem, s>>>(big_list.p, matched, ix.bucket_offsets.p,
@@ -504,6 +521,11 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
         KERNEL_CHECK();
         if (nb) {
             compact_big_kernel<<<nb, 256, 0, s>>>(big_list.p, tmp.p, raw_off.p, out.counts.p,
+                                                  out.offsets.p, out.indices.p);
+            KERNEL_CHECK();
+        }
+        if (nm) {
+            compact_big_kernel<<<nm, 256, 0, s>>>(mid_list, tmp.p, raw_off.p, out.counts.p,
                                                   out.offsets.p, out.indices.p);
             KERNEL_CHECK();
         }

@@ -49,7 +49,11 @@ bucket_count_kernel(const uint32_t* __restrict__ keys, int n, int tiles_per_tabl
     if (threadIdx.x == 0) tile_heads[blockIdx.x] = total;
 }
 
-// tile_base: exclusive scan of tile_heads (tile_base[n_tiles] = B)
+// tile_base: exclusive scan of tile_heads (tile_base[n_tiles] = B).
+// Items are visited in warp-coalesced order twice: the first sweep records the head flags of
+// the tile as one ballot word per 32 consecutive items, a prefix over those words then gives
+// every item its bucket id, and the second sweep writes bucket keys / offsets (consecutive
+// heads -> consecutive addresses) and the optional (row, table) -> bucket map.
 template <int NW>
 __global__ void __launch_bounds__(IB_THREADS)
 bucket_write_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ rows, int n,
@@ -57,25 +61,41 @@ bucket_write_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restric
                     uint32_t n_tiles, uint32_t* __restrict__ bucket_keys,
                     int32_t* __restrict__ bucket_offsets, int32_t* __restrict__ table_offsets,
                     int32_t* __restrict__ item_to_bucket) {
-    __shared__ uint32_t s_warp[32];
+    constexpr int WORDS = IB_TILE / 32;
+    __shared__ uint32_t s_bits[WORDS];
+    __shared__ uint32_t s_pref[WORDS];
     const int t = blockIdx.x / tiles_per_table;
     const int lt = blockIdx.x - t * tiles_per_table;
     const size_t tbase = (size_t)t * n;
-    const int li0 = lt * IB_TILE + threadIdx.x * IB_IPT;  // contiguous items per thread
-    bool head[IB_IPT];
-    uint32_t c = 0;
+    const int lane = threadIdx.x & 31;
+    const uint32_t base_bucket = tile_base[blockIdx.x];
 #pragma unroll
     for (int i = 0; i < IB_IPT; ++i) {
-        int li = li0 + i;
-        head[i] = false;
+        const int local = i * IB_THREADS + threadIdx.x;
+        const int li = lt * IB_TILE + local;
+        bool head = false;
         if (li < n)
-            head[i] = li == 0 ||
-                      keys_differ<NW>(keys + (tbase + li) * NW, keys + (tbase + li - 1) * NW);
-        c += head[i] ? 1u : 0u;
+            head = li == 0 || keys_differ<NW>(keys + (tbase + li) * NW, keys + (tbase + li - 1) * NW);
+        const uint32_t word = __ballot_sync(0xFFFFFFFFu, head);
+        if (lane == 0) s_bits[local >> 5] = word;
     }
-    uint32_t total;
-    uint32_t ex = block_exclusive_scan<uint32_t>(c, s_warp, total) + tile_base[blockIdx.x];
-    if (lt == 0 && threadIdx.x == 0) table_offsets[t] = (int32_t)tile_base[blockIdx.x];
+    __syncthreads();
+    if (threadIdx.x < 32) {  // exclusive prefix of the pop-counts of the WORDS ballot words
+        uint32_t run = 0;
+        for (int w0 = 0; w0 < WORDS; w0 += 32) {
+            const uint32_t c = __popc(s_bits[w0 + lane]);
+            uint32_t inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+                if (lane >= o) inc += x;
+            }
+            s_pref[w0 + lane] = run + inc - c;
+            run += __shfl_sync(0xFFFFFFFFu, inc, 31);
+        }
+    }
+    __syncthreads();
+    if (lt == 0 && threadIdx.x == 0) table_offsets[t] = (int32_t)base_bucket;
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         uint32_t B = tile_base[n_tiles];
         table_offsets[L] = (int32_t)B;
@@ -83,18 +103,21 @@ bucket_write_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restric
     }
 #pragma unroll
     for (int i = 0; i < IB_IPT; ++i) {
-        int li = li0 + i;
-        if (li >= n) break;
-        if (head[i]) {
+        const int local = i * IB_THREADS + threadIdx.x;
+        const int li = lt * IB_TILE + local;
+        if (li >= n) continue;
+        const uint32_t word = s_bits[local >> 5];
+        const bool head = (word >> lane) & 1u;
+        // heads up to and including this item, minus one = bucket of the item
+        const uint32_t bid = base_bucket + s_pref[local >> 5] + __popc(word & (0xFFFFFFFFu >> (31 - lane))) - 1u;
+        if (head) {
             const uint32_t* kp = keys + (tbase + li) * NW;
-            uint32_t* dst = bucket_keys + (size_t)ex * NW;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) dst[w] = kp[w];
-            bucket_offsets[ex] = (int32_t)(tbase + li);
-            ++ex;
+            uint32_t kk[NW];
+            load_key<NW>(kp, kk);
+            store_key<NW>(bucket_keys + (size_t)bid * NW, kk);
+            bucket_offsets[bid] = (int32_t)(tbase + li);
         }
-        // ex - 1 is the bucket of item li (its head has been counted)
-        if (item_to_bucket) item_to_bucket[(size_t)rows[tbase + li] * L + t] = (int32_t)(ex - 1);
+        if (item_to_bucket) item_to_bucket[(size_t)rows[tbase + li] * L + t] = (int32_t)bid;
     }
 }
 

@@ -55,10 +55,12 @@ lookup_kernel(const uint32_t* __restrict__ qkeys, const uint8_t* __restrict__ q_
 // ---------------------------------------------------------------------------------------
 constexpr int SMALL_MAX = 512;  // largest raw count handled by the warp path
 
+// counters[0] = queries for the bitmap path (big_list), counters[1] = queries for the
+// shared-memory sort path (mid_list; only used when mid_max > SMALL_MAX)
 __global__ void __launch_bounds__(256)
 raw_count_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
                  int n_q, int L, uint64_t* __restrict__ raw_cnt, uint32_t* __restrict__ big_list,
-                 uint32_t* __restrict__ n_big) {
+                 uint32_t* __restrict__ mid_list, uint32_t* __restrict__ counters, int mid_max) {
     int q = blockIdx.x * blockDim.x + threadIdx.x;
     if (q >= n_q) return;
     uint64_t c = 0;
@@ -67,7 +69,10 @@ raw_count_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict_
         if (b >= 0) c += (uint64_t)(bucket_offsets[b + 1] - bucket_offsets[b]);
     }
     raw_cnt[q] = c;
-    if (c > SMALL_MAX) big_list[atomicAdd(n_big, 1u)] = (uint32_t)q;
+    if (c > SMALL_MAX) {
+        if (c <= (uint64_t)mid_max) mid_list[atomicAdd(&counters[1], 1u)] = (uint32_t)q;
+        else big_list[atomicAdd(&counters[0], 1u)] = (uint32_t)q;
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -137,6 +142,134 @@ dedupe_small_kernel(const int32_t* __restrict__ matched, const int32_t* __restri
         if (lane == 0) uniq_cnt[q] = (uint64_t)written;
         __syncwarp();
     }
+}
+
+// ---------------------------------------------------------------------------------------
+// Sort path: one CTA per query of mid_list (SMALL_MAX < raw <= MID_MAX), used when the index
+// has so many rows that a bitmap would need several windows.  The ids are gathered into
+// shared memory, LSD radix sorted there on 8-bit digits (as many passes as the row ids have
+// bytes), then adjacent duplicates are dropped while writing out.
+// ---------------------------------------------------------------------------------------
+constexpr int MS_THREADS = 512;
+constexpr int MS_WARPS = MS_THREADS / 32;
+constexpr int MS_IPT = 16;
+constexpr int MID_MAX = MS_THREADS * MS_IPT;  // 8192
+
+inline size_t sort_path_smem_bytes() {
+    return sizeof(uint32_t) * (2 * (size_t)MID_MAX + MS_WARPS * 256 + 256 + 64);
+}
+
+__global__ void __launch_bounds__(MS_THREADS)
+dedupe_sort_kernel(const uint32_t* __restrict__ mid_list, const int32_t* __restrict__ matched,
+                   const int32_t* __restrict__ bucket_offsets, const int32_t* __restrict__ cand,
+                   const uint64_t* __restrict__ raw_cnt, const uint64_t* __restrict__ raw_off, int L,
+                   int id_bytes, int32_t* __restrict__ tmp, uint64_t* __restrict__ uniq_cnt) {
+    extern __shared__ __align__(16) uint32_t s_ms[];
+    uint32_t* bufA = s_ms;
+    uint32_t* bufB = bufA + MID_MAX;
+    uint32_t* s_whist = bufB + MID_MAX;       // [MS_WARPS][256]
+    uint32_t* s_binstart = s_whist + MS_WARPS * 256;  // [256]
+    uint32_t* s_misc = s_binstart + 256;      // [64]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int q = (int)mid_list[blockIdx.x];
+    const int r = (int)raw_cnt[q];
+    // gather the bucket lists one after another
+    int fill = 0;
+    for (int t = 0; t < L; ++t) {
+        const int b = matched[(size_t)q * L + t];
+        if (b < 0) continue;
+        const int s = bucket_offsets[b], e = bucket_offsets[b + 1];
+        for (int i = s + tid; i < e; i += MS_THREADS) bufA[fill + (i - s)] = (uint32_t)cand[i];
+        fill += e - s;
+    }
+    __syncthreads();
+    const int n_iter = (r + MS_THREADS - 1) / MS_THREADS;  // uniform
+    uint32_t* src = bufA;
+    uint32_t* dst = bufB;
+    for (int p = 0; p < id_bytes; ++p) {
+        for (int i = tid; i < MS_WARPS * 256; i += MS_THREADS) s_whist[i] = 0;
+        __syncthreads();
+        uint32_t key[MS_IPT];
+        uint16_t rank[MS_IPT];
+#pragma unroll
+        for (int i = 0; i < MS_IPT; ++i) {
+            if (i < n_iter) {
+                const int li = warp * (32 * n_iter) + i * 32 + lane;
+                const bool valid = li < r;
+                key[i] = valid ? src[li] : 0u;
+                const uint32_t d = valid ? ((key[i] >> (8 * p)) & 0xFFu) : 0x100u;
+                const uint32_t peers = __match_any_sync(0xFFFFFFFFu, d);
+                const int leader = __ffs(peers) - 1;
+                const uint32_t below = __popc(peers & ((1u << lane) - 1));
+                uint32_t old = 0;
+                if (valid && lane == leader) old = atomicAdd(&s_whist[warp * 256 + d], (uint32_t)__popc(peers));
+                old = __shfl_sync(0xFFFFFFFFu, old, leader);
+                rank[i] = (uint16_t)(old + below);
+            }
+        }
+        __syncthreads();
+        if (tid < 256) {
+            uint32_t cnt = 0;
+#pragma unroll
+            for (int w = 0; w < MS_WARPS; ++w) {
+                uint32_t x = s_whist[w * 256 + tid];
+                s_whist[w * 256 + tid] = cnt;
+                cnt += x;
+            }
+            uint32_t inc = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+                if (lane >= o) inc += x;
+            }
+            if (lane == 31) s_misc[warp] = inc;
+            s_binstart[tid] = inc - cnt;  // exclusive inside the warp; warp bases added below
+        }
+        __syncthreads();
+        if (tid < 256) {
+            uint32_t wb = 0;
+            for (int w = 0; w < warp; ++w) wb += s_misc[w];
+            s_binstart[tid] += wb;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < MS_IPT; ++i) {
+            if (i < n_iter) {
+                const int li = warp * (32 * n_iter) + i * 32 + lane;
+                if (li < r) {
+                    const uint32_t d = (key[i] >> (8 * p)) & 0xFFu;
+                    dst[s_binstart[d] + s_whist[warp * 256 + d] + rank[i]] = key[i];
+                }
+            }
+        }
+        __syncthreads();
+        uint32_t* tsw = src; src = dst; dst = tsw;
+    }
+    // adjacent-unique + block compaction, ascending order kept
+    int32_t* out = tmp + raw_off[q];
+    uint32_t written = 0;  // uniform
+    for (int i0 = 0; i0 < r; i0 += MS_THREADS) {
+        const int i = i0 + tid;
+        bool keep = false;
+        uint32_t v = 0;
+        if (i < r) {
+            v = src[i];
+            keep = i == 0 || src[i - 1] != v;
+        }
+        const uint32_t mask = __ballot_sync(0xFFFFFFFFu, keep);
+        if (lane == 0) s_misc[32 + warp] = __popc(mask);
+        __syncthreads();
+        uint32_t wb = 0, tot = 0;
+        for (int w = 0; w < MS_WARPS; ++w) {
+            const uint32_t x = s_misc[32 + w];
+            if (w < warp) wb += x;
+            tot += x;
+        }
+        if (keep) out[written + wb + __popc(mask & ((1u << lane) - 1))] = (int32_t)v;
+        written += tot;
+        __syncthreads();
+    }
+    if (tid == 0) uniq_cnt[q] = (uint64_t)written;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -18,7 +18,9 @@ constexpr int RS_WARPS = RS_THREADS / 32;
 
 template <int NW>
 struct SortCfg {
-    static constexpr int IPT = NW <= 4 ? 16 : (NW == 8 ? 8 : 4);  // items per thread
+    // items per thread: fewer for wide keys so that the tile's keys stay in registers at an
+    // occupancy of 2-3 CTAs per SM
+    static constexpr int IPT = NW == 1 ? 16 : (NW == 2 ? 12 : (NW == 4 ? 8 : (NW == 8 ? 4 : 2)));
     static constexpr int TILE = RS_THREADS * IPT;
     static constexpr size_t SMEM =
         sizeof(uint32_t) * ((size_t)TILE * NW + TILE + RS_WARPS * 256 + 256 + 256 + 32);

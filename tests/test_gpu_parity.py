@@ -259,6 +259,29 @@ def test_bitmap_windows_beyond_one_window(eng):
     _assert_candidates_equal(model.query(X[sel]), oracle.query_index(oidx, sig[sel]))
 
 
+def test_sort_path_for_mid_sized_sets_on_a_large_index(eng):
+    """More rows than two bitmap windows: candidate sets between the warp path's and the sort
+    path's limits are merged by the shared-memory radix sort; larger ones by windowed bitmaps."""
+    culsh, core_mod = eng
+    rng = np.random.RandomState(21)
+    n, d, L, k = 2_300_000, 8, 4, 16
+    X = rng.randn(n, d).astype(np.float32)
+    model = culsh.RPLSH(L, k, seed=8).fit(X)
+    core = core_mod.RPLSHCore(L, k, 8)
+    sig = _sig_matrix(core.hash(X, model.index))
+    oidx = oracle.fit_index(sig, L, k)
+    sel = rng.randint(0, n, 24)
+    cand = model.query(X[sel])
+    want = oracle.query_index(oidx, sig[sel])
+    counts = want[2].astype(np.int64)
+    assert ((counts > 512) & (counts <= 8192)).mean() >= 0.3  # a good share takes the sort path
+    _assert_candidates_equal(cand, want)
+    # one-table, few-bit index on the same rows: sets far above the sort path's limit
+    m2 = culsh.RPLSH(2, 3, seed=8).fit(X)
+    sig2 = _sig_matrix(core_mod.RPLSHCore(2, 3, 8).hash(X, m2.index))
+    _assert_candidates_equal(m2.query(X[sel[:3]]), oracle.query_index(oracle.fit_index(sig2, 2, 3), sig2[sel[:3]]))
+
+
 def test_no_match_and_zero_queries(eng):
     culsh, _ = eng
     rng = np.random.RandomState(3)
