@@ -1,19 +1,27 @@
 #!/usr/bin/env python
-"""Benchmark of the LSH hot path on the SIFT-shaped RPLSH workload.
+"""Benchmark of the LSH hot path (hash -> bucket index -> lookup -> gather/dedupe -> CSR).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2]
 
-One step = fit(X) then query(Q): X is 1,000,000 x 128 fp32 with components
-clip(round(Gamma(0.5, 40)), 0, 255) (SIFT-shaped synthetic; the SIFT1M files are not
-available offline), Q is 10,000 rows of the same law, RPLSH with 32 tables x 16 hashes,
-seed 0, query batch 10,000.  `value` is rows indexed-and-queried per second over all GPUs
-with inputs resident in HBM; `e2e` is the same step through the public Python API with
-pinned HOST arrays in and the candidates CSR read back to the host.
+Default workload "c2" (the one the headline metric is quoted on): one step = fit(X) then
+query(Q); X is 1,000,000 x 128 fp32 with components clip(round(Gamma(0.5, 40)), 0, 255)
+(SIFT-shaped synthetic; the SIFT1M files are not available offline), Q is 10,000 rows of the
+same law, RPLSH with 32 tables x 16 hashes, seed 0, query batch 10,000.  `value` is rows
+indexed-and-queried per second over all GPUs with inputs resident in HBM; `e2e` is the same
+step with pinned HOST arrays in and the candidates CSR read back to the host.
 
-At N > 1 (torchrun, one rank per GPU) each rank holds its own 1M-row shard (weak scaling),
-the queries are the same on every rank, and the per-shard candidates are exchanged over NCCL
-(one all-to-all) so that rank j holds the merged CSR, with global row ids, of the j-th slice
-of the queries.
+Other workloads (same JSON line, for the remaining benchmark configurations):
+  c1  PStableLSH 10,000 x 128 N(0,1), 100 queries, 16 x 8, window "auto" (= 11), seed 42
+  c3  MinHashLSH 2,000,000 rows x 2^20 columns, row nnz ~ U[20,200], Zipf(1.1) column ids,
+      10,000 queries (half fresh, half perturbed copies), 32 x 4, seed 1
+  c4  PStableLSH, one 12,500,000 x 96 shard per GPU of the 100M-row mixture of 4,096 Gaussians
+      (sigma 0.15), 10,000 queries, 16 x 8, window 4, seed 2
+  c5  RPLSH fit_query self-join, 10,000,000 x 256 unit-sphere rows, 48 x 24, seed 3 (1 GPU)
+
+At N > 1 (torchrun, one rank per GPU) each rank holds its own shard (weak scaling), the
+queries are the same on every rank, and the per-shard candidates are exchanged over NCCL (one
+all-to-all) so that rank j holds the merged CSR, with global row ids, of the j-th slice of the
+queries.
 
 `--impl reference` times upstream cuLSH's own CUDA build (oracle/_ref, compiled from the
 upstream sources by oracle/Makefile) on the same workload when that module loads, else the
@@ -33,9 +41,25 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-N_ROWS, N_QUERIES, N_FEATURES = 1_000_000, 10_000, 128
-N_TABLES, N_HASHES, SEED = 32, 16, 0
-WORKLOAD = "RPLSH 1Mx128 fp32 SIFT-shaped synthetic, 32 tables x 16 hashes, 10k queries, batch 10k"  # at the default --rows/--queries
+WORKLOADS = {
+    "c1": dict(family="pslsh", n=10_000, nq=100, d=128, L=16, k=8, w=11, seed=42, mode="fit+query",
+               name="PStableLSH 10kx128 N(0,1), 16 tables x 8 hashes, window auto(=11), 100 queries"),
+    "c2": dict(family="rplsh", n=1_000_000, nq=10_000, d=128, L=32, k=16, seed=0, mode="fit+query",
+               name="RPLSH 1Mx128 fp32 SIFT-shaped synthetic, 32 tables x 16 hashes, 10k queries, batch 10k"),
+    "c3": dict(family="minhash", n=2_000_000, nq=10_000, d=1 << 20, L=32, k=4, seed=1, mode="fit+query",
+               name="MinHashLSH 2M rows x 2^20 cols, nnz U[20,200], Zipf(1.1) ids, 32 tables x 4 hashes, 10k queries"),
+    "c4": dict(family="pslsh", n=12_500_000, nq=10_000, d=96, L=16, k=8, w=4, seed=2, mode="fit+query",
+               name="PStableLSH 12.5Mx96 shard per GPU (100M-row mixture of 4096 Gaussians), 16x8, w=4, 10k queries"),
+    "c5": dict(family="rplsh", n=10_000_000, nq=0, d=256, L=48, k=24, seed=3, mode="fit_query",
+               name="RPLSH fit_query self-join 10Mx256 unit sphere, 48 tables x 24 hashes"),
+}
+METRICS = {
+    "c1": "PStableLSH 10kx128 16x8: fit + 100-query rows/s",
+    "c2": "RPLSH 1Mx128 32x16: fit + 10k-query rows/s",
+    "c3": "MinHashLSH 2Mx2^20 32x4: fit + 10k-query rows/s",
+    "c4": "PStableLSH 12.5Mx96 shard 16x8: fit + 10k-query rows/s",
+    "c5": "RPLSH 10Mx256 48x24: fit_query rows/s",
+}
 
 
 def load_peaks():
@@ -96,17 +120,104 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def make_inputs(torch, device, rank):
-    """Seeded synthetic data generated on the device (NumPy's gamma sampler needs ~15 s for X)."""
+# ------------------------------------------------------------------------------------------
+# synthetic inputs (seeded, generated on the device)
+# ------------------------------------------------------------------------------------------
+def _csr_from_pairs(torch, rows, cols, n_rows):
+    """Sorted, duplicate-free CSR (int32 indices / indptr) from (row, col) pairs."""
+    key = torch.unique(rows.to(torch.int64) << 32 | cols.to(torch.int64))
+    r = (key >> 32)
+    indices = (key & 0xFFFFFFFF).to(torch.int32)
+    indptr = torch.zeros(n_rows + 1, dtype=torch.int64, device=key.device)
+    indptr[1:] = torch.cumsum(torch.bincount(r, minlength=n_rows), 0)
+    return indices.contiguous(), indptr.to(torch.int32).contiguous()
+
+
+def _zipf_columns(torch, count, n_cols, g, device, s=1.1):
+    """Column ids with P(id = i) ~ (i+1)^-s, by inverting the continuous CDF."""
+    u = torch.rand(count, device=device, generator=g, dtype=torch.float64)
+    a = 1.0 - s
+    x = (1.0 - u * (1.0 - float(n_cols) ** a)) ** (1.0 / a)
+    return torch.clamp(x.to(torch.int64) - 1, 0, n_cols - 1)
+
+
+def make_inputs(torch, device, rank, wl, spec):
+    """Returns (X, Q): dense fp32 tensors, or (indices, indptr) tuples for MinHash."""
     g = torch.Generator(device=device)
+    n, nq, d = spec["n"], spec["nq"], spec["d"]
+    if wl == "c1":
+        X = torch.from_numpy(np.random.RandomState(42).randn(n, d).astype(np.float32)).to(device)
+        Q = torch.from_numpy(np.random.RandomState(7).randn(nq, d).astype(np.float32)).to(device)
+        return X, Q
+    if wl == "c2":
+        def draw(rows, seed):
+            g.manual_seed(seed)
+            conc = torch.full((rows, d), 0.5, device=device)
+            x = torch._standard_gamma(conc, generator=g) * 40.0
+            return torch.clamp(torch.round(x), 0, 255).to(torch.float32).contiguous()
+        return draw(n, 100 + rank), draw(nq, 99)
+    if wl == "c3":
+        def rows_csr(n_rows, seed):
+            g.manual_seed(seed)
+            nnz = torch.randint(20, 201, (n_rows,), device=device, generator=g)
+            rows = torch.repeat_interleave(torch.arange(n_rows, device=device), nnz)
+            cols = _zipf_columns(torch, int(rows.numel()), d, g, device)
+            return rows, cols
+        rows, cols = rows_csr(n, 300 + rank)
+        X = _csr_from_pairs(torch, rows, cols, n)
+        # queries: half fresh rows, half copies of random X rows with ~10% of the columns
+        # dropped and ~10% new Zipf columns added
+        half = nq // 2
+        fr, fc = rows_csr(half, 299)
+        g.manual_seed(298)
+        src = torch.randint(0, n, (nq - half,), device=device, generator=g)
+        xi, xp = X[0].to(torch.int64), X[1].to(torch.int64)
+        lens = xp[src + 1] - xp[src]
+        qrow = torch.repeat_interleave(torch.arange(nq - half, device=device), lens)
+        start = torch.repeat_interleave(xp[src], lens)
+        within = torch.arange(int(lens.sum()), device=device) - torch.repeat_interleave(torch.cumsum(lens, 0) - lens, lens)
+        ccol = xi[start + within]
+        keep = torch.rand(ccol.numel(), device=device, generator=g) >= 0.1
+        add_n = torch.clamp((lens.to(torch.float32) * 0.1).round().to(torch.int64), min=1)
+        arow = torch.repeat_interleave(torch.arange(nq - half, device=device), add_n)
+        acol = _zipf_columns(torch, int(arow.numel()), d, g, device)
+        qr = torch.cat([fr, qrow[keep] + half, arow + half])
+        qc = torch.cat([fc, ccol[keep], acol])
+        return X, _csr_from_pairs(torch, qr, qc, nq)
+    if wl == "c4":
+        g.manual_seed(2)
+        centres = torch.randn(4096, d, device=device, generator=g)
+        g.manual_seed(400 + rank)
+        X = centres[torch.randint(0, 4096, (n,), device=device, generator=g)]
+        X = (X + 0.15 * torch.randn(n, d, device=device, generator=g)).contiguous()
+        g.manual_seed(399)
+        Q = centres[torch.randint(0, 4096, (nq,), device=device, generator=g)]
+        Q = (Q + 0.15 * torch.randn(nq, d, device=device, generator=g)).contiguous()
+        return X, Q
+    if wl == "c5":
+        g.manual_seed(3)
+        X = torch.randn(n, d, device=device, generator=g)
+        X = (X / X.norm(dim=1, keepdim=True)).contiguous()
+        return X, None
+    raise ValueError(wl)
 
-    def draw(rows, seed):
-        g.manual_seed(seed)
-        conc = torch.full((rows, N_FEATURES), 0.5, device=device)
-        x = torch._standard_gamma(conc, generator=g) * 40.0
-        return torch.clamp(torch.round(x), 0, 255).to(torch.float32).contiguous()
 
-    return draw(N_ROWS, 100 + rank), draw(N_QUERIES, 99)
+def to_pinned_host(torch, t):
+    if t is None:
+        return None
+    if isinstance(t, tuple):
+        return tuple(to_pinned_host(torch, x) for x in t)
+    h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+    h.copy_(t)
+    return h.numpy()
+
+
+def nbytes_of(x):
+    if x is None:
+        return 0
+    if isinstance(x, tuple):
+        return sum(nbytes_of(y) for y in x)
+    return int(x.nbytes) if hasattr(x, "nbytes") else int(x.numel() * x.element_size())
 
 
 def measure_tf32_peak(torch, device):
@@ -133,36 +244,35 @@ def measure_tf32_peak(torch, device):
 
 
 def cpu_baseline(sample_rows=200_000, sample_queries=2_000):
-    """NumPy restatement of the path (oracle/) on a bounded sample of the workload."""
+    """NumPy restatement of the path (oracle/) on a bounded sample of the c2 workload."""
     from oracle import oracle
+    s = WORKLOADS["c2"]
     rng = np.random.default_rng(100)
-    X = np.clip(np.round(rng.gamma(0.5, 40.0, (sample_rows, N_FEATURES))), 0, 255).astype(np.float32)
-    Q = np.clip(np.round(rng.gamma(0.5, 40.0, (sample_queries, N_FEATURES))), 0, 255).astype(np.float32)
-    P = np.random.default_rng(0).standard_normal((N_TABLES * N_HASHES, N_FEATURES)).astype(np.float32)
+    X = np.clip(np.round(rng.gamma(0.5, 40.0, (sample_rows, s["d"]))), 0, 255).astype(np.float32)
+    Q = np.clip(np.round(rng.gamma(0.5, 40.0, (sample_queries, s["d"]))), 0, 255).astype(np.float32)
+    P = np.random.default_rng(0).standard_normal((s["L"] * s["k"], s["d"])).astype(np.float32)
     t0 = time.perf_counter()
     bits = (~np.signbit(X @ P.T)).astype(np.uint8)
-    tables = oracle.fast_fit_packed(oracle.pack_bits_msb_first(bits, N_TABLES, N_HASHES))
+    tables = oracle.fast_fit_packed(oracle.pack_bits_msb_first(bits, s["L"], s["k"]))
     t1 = time.perf_counter()
     qbits = (~np.signbit(Q @ P.T)).astype(np.uint8)
-    oracle.fast_query_packed(tables, oracle.pack_bits_msb_first(qbits, N_TABLES, N_HASHES))
+    oracle.fast_query_packed(tables, oracle.pack_bits_msb_first(qbits, s["L"], s["k"]))
     t2 = time.perf_counter()
     return {"value": sample_rows / (t2 - t0), "unit": "rows/s", "cores": os.cpu_count(), "kind": "port",
             "fit_rows_per_s": sample_rows / (t1 - t0), "query_qps": sample_queries / (t2 - t1),
-            "sample": f"{sample_rows} rows + {sample_queries} queries of the same law, same 32x16 RPLSH "
+            "sample": f"{sample_rows} rows + {sample_queries} queries of the c2 law, same 32x16 RPLSH "
                       f"(NumPy matmul/argsort/searchsorted/unique, BLAS threads = all cores)"}
 
 
-def dist_setup(args):
+def dist_setup():
     import torch
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist
-        torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-    else:
-        torch.cuda.set_device(local)
     return world, rank, local
 
 
@@ -184,44 +294,64 @@ def barrier(torch, world):
 
 
 # ------------------------------------------------------------------------------------------
+# one step of a workload on either implementation's core classes (same class surface)
+# ------------------------------------------------------------------------------------------
+def make_core(mod, spec):
+    if spec["family"] == "rplsh":
+        return mod.RPLSHCore(spec["L"], spec["k"], spec["seed"])
+    if spec["family"] == "pslsh":
+        return mod.PSLSHCore(spec["L"], spec["k"], spec["w"], spec["seed"])
+    return mod.MinHashCore(spec["L"], spec["k"], spec["seed"])
+
+
+def core_fit(core, spec, X):
+    if spec["family"] == "minhash":
+        return core.fit(X[0], X[1], spec["n"], spec["d"])
+    return core.fit_float(X, spec["n"], spec["d"])
+
+
+def core_query(core, spec, Q, index, batch):
+    if spec["family"] == "minhash":
+        return core.query(Q[0], Q[1], spec["nq"], index)
+    return core.query_float(Q, spec["nq"], index, batch)
+
+
+def read_back(cand):
+    a, b, c = cand.get_offsets(), cand.get_counts(), cand.get_indices()
+    return a.nbytes + b.nbytes + c.nbytes
+
+
+# ------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------
-def run_ours(args):
+def run_ours(args, wl, spec):
     import torch
-    world, rank, local = dist_setup(args)
+    world, rank, local = dist_setup()
     device = torch.device(f"cuda:{local}")
-    import culsh_b200
     from culsh_b200 import _culsh_core, sharded
-
-    Xd, Qd = make_inputs(torch, device, rank)
-    Xh = torch.empty(Xd.shape, dtype=torch.float32, pin_memory=True)
-    Qh = torch.empty(Qd.shape, dtype=torch.float32, pin_memory=True)
-    Xh.copy_(Xd)
-    Qh.copy_(Qd)
-    torch.cuda.synchronize()
-    Xh_np, Qh_np = Xh.numpy(), Qh.numpy()
-
-    lsh = culsh_b200.RPLSH(N_TABLES, N_HASHES, seed=SEED)
-    core = _culsh_core.RPLSHCore(N_TABLES, N_HASHES, SEED)
+    if wl == "c5" and world > 1:
+        raise SystemExit("workload c5 is single-GPU in this benchmark")
+    n, nq = spec["n"], spec["nq"]
+    Xd, Qd = make_inputs(torch, device, rank, wl, spec)
+    core = make_core(_culsh_core, spec)
     core.set_profiling(True)
-
+    batch = nq if wl == "c2" else None
     stage = {"fit": [], "query": []}
 
     def step(X, Q, host_out):
-        model = lsh.fit(X)
-        s_fit = core.last_stats()
-        cand = model.query(Q, batch_size=N_QUERIES)
-        s_q = core.last_stats()
-        if world > 1:  # each rank receives the merged lists of its slice of the queries
-            cand, _ = sharded.exchange_by_query(cand, row_base=rank * N_ROWS,
-                                                    row_bases=[r * N_ROWS for r in range(world)])
-        d2h = 0
-        if host_out and cand is not None:
-            off = cand.get_offsets()
-            cnt = cand.get_counts()
-            idx = cand.get_indices()
-            d2h = off.nbytes + cnt.nbytes + idx.nbytes
-        return s_fit, s_q, d2h
+        if spec["mode"] == "fit_query":
+            cand = core.fit_query_float(X, n, spec["d"])
+            s_fit = core.last_stats()
+            s_q = dict(s_fit, total_ms=0.0, hash_ms=0.0, lookup_ms=0.0, launches=0)
+        else:
+            index = core_fit(core, spec, X)
+            s_fit = core.last_stats()
+            cand = core_query(core, spec, Q, index, batch)
+            s_q = core.last_stats()
+            if world > 1:  # each rank receives the merged lists of its slice of the queries
+                cand, _ = sharded.exchange_by_query(cand, row_base=rank * n,
+                                                    row_bases=[r * n for r in range(world)])
+        return s_fit, s_q, (read_back(cand) if host_out else 0)
 
     for _ in range(args.warmup):
         step(Xd, Qd, False)
@@ -239,16 +369,18 @@ def run_ours(args):
     t_dev = max_over_ranks(torch, time.perf_counter() - t0, world, device)
     clocks = sampler.stop()
 
-    # end to end: pinned host arrays in, CSR read back
-    d2h = 0
+    # end to end: pinned host arrays in, CSR read back to the host
+    d2h, h2d = 0, 0
     t_e2e = float("nan")
     if not args.skip_e2e:
-        for _ in range(min(args.warmup, 2)):
-            step(Xh_np, Qh_np, True)
+        Xh, Qh = to_pinned_host(torch, Xd), to_pinned_host(torch, Qd)
+        h2d = nbytes_of(Xh) + nbytes_of(Qh)
+        for _ in range(2):
+            step(Xh, Qh, True)
         barrier(torch, world)
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            _, _, b = step(Xh_np, Qh_np, True)
+            _, _, b = step(Xh, Qh, True)
             d2h = max(d2h, b)
         barrier(torch, world)
         t_e2e = max_over_ranks(torch, time.perf_counter() - t0, world, device)
@@ -256,58 +388,70 @@ def run_ours(args):
     if rank != 0:
         return
     peaks = load_peaks()
-    ms_step = t_dev / args.steps * 1e3
-    total_rows = N_ROWS * world
-    fit_ms = statistics.mean(s["total_ms"] for s in stage["fit"])
-    hash_ms = statistics.mean(s["hash_ms"] for s in stage["fit"])
-    scatter_ms = statistics.mean(s["scatter_ms"] for s in stage["fit"])
-    q_ms = statistics.mean(s["total_ms"] for s in stage["query"])
-    gather_ms = statistics.mean(s["gather_ms"] for s in stage["query"])
+    mean = lambda key, which: statistics.mean(s[key] for s in stage[which])  # noqa: E731
+    total_rows = n * world
+    fit_ms, hash_ms, scatter_ms = mean("total_ms", "fit"), mean("hash_ms", "fit"), mean("scatter_ms", "fit")
+    q_ms, gather_ms = mean("total_ms", "query"), mean("gather_ms", "query")
     sf, sq = stage["fit"][-1], stage["query"][-1]
     passes = max(1, sf["sort_passes"])
-    items = sf["n_items"]
-    kb = 4 * sf["key_words"]
-    tf32 = measure_tf32_peak(torch, device) if not args.skip_cpu else 690.0
-    flops = 2.0 * N_ROWS * N_FEATURES * N_TABLES * N_HASHES
-    proj = {"bound": "tensor", "achieved": flops / (hash_ms * 1e-3) / 1e12,
-            "peak": tf32 / 3.0, "unit": "TFLOP/s",
-            "kernel": "project_tc_kernel" if sf["hash_path"] == 1 else "project_simt_kernel",
-            "note": "fp32-equivalent flop 2*n*d*H over the CUDA-event time of the projection launch; "
-                    "peak = TF32 dense matmul measured in this run (8192^3) / 3 (3xTF32)",
-            "tf32_tflops_measured": tf32, "traffic": None}
-    proj["frac"] = proj["achieved"] / proj["peak"]
-    sort_bytes = items * (kb + 4) * 2.0
-    sort = {"bound": "hbm", "achieved": sort_bytes / (scatter_ms * 1e-3) / 1e9,
-            "peak": peaks["hbm_gbs"], "unit": "GB/s", "kernel": "radix_scatter_kernel",
-            "note": f"(key {kb} B + row id 4 B) read + written per item, one launch (the scatter of the "
-                    f"last of {passes} passes) timed with CUDA events; peak {peaks['source']}", "traffic": None}
-    sort["frac"] = sort["achieved"] / sort["peak"]
-    gat_bytes = 4.0 * (sq["raw_candidates"] + 3 * sq["unique_candidates"])
-    gather = {"bound": "hbm", "achieved": gat_bytes / (gather_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
-              "unit": "GB/s", "kernel": "dedupe_bitmap_kernel+compact",
-              "note": "4*raw read + 4*uniq written to scratch + 4*uniq read + 4*uniq written"}
-    gather["frac"] = gather["achieved"] / gather["peak"]
-    dominant = proj if hash_ms >= scatter_ms else sort
+    items, kb = sf["n_items"], 4 * sf["key_words"]
+    roof = {}
+    if spec["family"] == "minhash":
+        nnz = int(Xd[0].numel())
+        evals = float(nnz) * spec["L"] * spec["k"]
+        hbytes = 4.0 * nnz + 4.0 * (n + 1) + 4.0 * n * spec["L"] * sf["key_words"]
+        roof["hash"] = {"bound": "hbm", "achieved": hbytes / (hash_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                        "unit": "GB/s", "kernel": "minhash_kernel", "traffic": None,
+                        "note": "integer-issue bound by nature: 4*nnz + 4*(n+1) + 4*n*L*NW bytes over the event "
+                                "time; hash evaluations/s in hash_evals_per_s",
+                        "hash_evals_per_s": evals / (hash_ms * 1e-3)}
+    else:
+        tf32 = measure_tf32_peak(torch, device) if not args.skip_cpu else 700.0
+        flops = 2.0 * n * spec["d"] * spec["L"] * spec["k"]
+        roof["hash"] = {"bound": "tensor", "achieved": flops / (hash_ms * 1e-3) / 1e12, "peak": tf32 / 3.0,
+                        "unit": "TFLOP/s", "traffic": None,
+                        "kernel": "project_tc_kernel" if sf["hash_path"] == 1 else "project_simt_kernel",
+                        "note": "fp32-equivalent flop 2*n*d*H over the CUDA-event time of the projection "
+                                "launch; peak = TF32 dense matmul measured in this run (8192^3) / 3 (3xTF32; "
+                                "tiles whose low part is zero issue 2 of the 3 MMAs)",
+                        "tf32_tflops_measured": tf32}
+    roof["sort"] = {"bound": "hbm", "achieved": items * (kb + 4) * 2.0 / (scatter_ms * 1e-3) / 1e9,
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "kernel": "radix_scatter_kernel", "traffic": None,
+                    "note": f"(key {kb} B + row id 4 B) read + written per item, one launch (the scatter of the "
+                            f"last of {passes} passes) timed with CUDA events; peak {peaks['source']}"}
+    if gather_ms > 0:
+        roof["gather"] = {"bound": "hbm", "peak": peaks["hbm_gbs"], "unit": "GB/s", "traffic": None,
+                          "achieved": 4.0 * (sq["raw_candidates"] + 3 * sq["unique_candidates"]) / (gather_ms * 1e-3) / 1e9,
+                          "kernel": "dedupe kernels + compaction",
+                          "note": "4*raw read + 4*uniq written to scratch + 4*uniq read + 4*uniq written, over the "
+                                  "event time from lookup end to CSR complete (includes two host round trips)"}
+    for r in roof.values():
+        r["frac"] = r["achieved"] / r["peak"]
+    dominant = roof["hash"] if hash_ms >= scatter_ms * passes else roof["sort"]
+    in_bytes = nbytes_of(Xd)
     line = {
-        "metric": "RPLSH 1Mx128 32x16: fit + 10k-query rows/s",
+        "metric": METRICS[wl],
         "value": total_rows / (t_dev / args.steps), "unit": "rows/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD, "rows_per_gpu": N_ROWS, "queries": N_QUERIES,
-                   "l2": "inputs (512 MB per step) larger than L2, no flush", "seed": SEED,
-                   "parallelism": f"row-sharded x{world}" if world > 1 else "single GPU"},
-        "fit_rows_per_s": N_ROWS * world / (fit_ms * 1e-3), "query_qps": N_QUERIES / (q_ms * 1e-3),
-        "stage_ms": {"fit_total": fit_ms, "hash": hash_ms, "sort": statistics.mean(s["sort_ms"] for s in stage["fit"]),
-                     "sort_scatter": scatter_ms, "build": statistics.mean(s["build_ms"] for s in stage["fit"]),
-                     "query_total": q_ms, "query_hash": statistics.mean(s["hash_ms"] for s in stage["query"]),
-                     "lookup": statistics.mean(s["lookup_ms"] for s in stage["query"]), "gather": gather_ms},
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_dev / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u32" if spec["family"] == "minhash" else "f32", "data": "synthetic",
+        "config": {"workload": spec["name"], "id": wl, "rows_per_gpu": n, "queries": nq, "seed": spec["seed"],
+                   "l2": (f"inputs ({in_bytes >> 20} MB per step) larger than L2, no flush" if in_bytes > (130 << 20)
+                          else f"inputs ({in_bytes >> 10} KB) fit L2: small configuration, no flush"),
+                   "parallelism": f"row-sharded x{world}, all-to-all candidate exchange" if world > 1 else "single GPU"},
+        "fit_rows_per_s": total_rows / (fit_ms * 1e-3),
+        "query_qps": (nq / (q_ms * 1e-3)) if q_ms > 0 else None,
+        "stage_ms": {"fit_total": fit_ms, "hash": hash_ms, "sort": mean("sort_ms", "fit"),
+                     "sort_scatter_last_pass": scatter_ms, "build": mean("build_ms", "fit"),
+                     "query_total": q_ms, "query_hash": mean("hash_ms", "query"),
+                     "lookup": mean("lookup_ms", "query"), "gather": gather_ms},
         "shape": {"buckets": sf["n_buckets"], "raw_candidates": sq["raw_candidates"],
-                  "unique_candidates": sq["unique_candidates"]},
-        "roofline": dominant, "roofline_all": {"projection": proj, "sort": sort, "gather": gather},
+                  "unique_candidates": sq["unique_candidates"], "key_words": sf["key_words"],
+                  "elem_bytes": sf["elem_bytes"], "sort_passes": passes},
+        "roofline": dominant, "roofline_all": roof,
         "e2e": {"value": total_rows / (t_e2e / args.steps), "unit": "rows/s",
                 "ms_per_step": t_e2e / args.steps * 1e3,
-                "h2d_bytes_per_step": int(Xh_np.nbytes + Qh_np.nbytes), "d2h_bytes_per_step": int(d2h)},
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": launches, "clocks": clocks,
     }
     if world == 1 and not args.skip_cpu:
@@ -330,7 +474,7 @@ def load_reference_module():
         return None
 
 
-def run_reference(args):
+def run_reference(args, wl, spec):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -341,10 +485,12 @@ def run_reference(args):
         have_gpu = torch.cuda.is_available()
     except Exception:
         have_gpu = False
-    base = {"metric": "RPLSH 1Mx128 32x16: fit + 10k-query rows/s", "unit": "rows/s", "impl": "reference",
+    n, nq = spec["n"], spec["nq"]
+    base = {"metric": METRICS[wl], "unit": "rows/s", "impl": "reference",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "rows_per_gpu": N_ROWS, "queries": N_QUERIES, "seed": SEED}}
+            "scaling": "weak", "vs_baseline": None, "dtype": "u32" if spec["family"] == "minhash" else "f32",
+            "data": "synthetic",
+            "config": {"workload": spec["name"], "id": wl, "rows_per_gpu": n, "queries": nq, "seed": spec["seed"]}}
     if ref is None or not have_gpu:
         cb = cpu_baseline()
         base.update({"value": cb["value"], "ms_per_step": None, "cpu_baseline": cb,
@@ -356,86 +502,100 @@ def run_reference(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device(f"cuda:{local}")
-    Xd, Qd = make_inputs(torch, device, 0)
-    Xh = torch.empty(Xd.shape, dtype=torch.float32, pin_memory=True).copy_(Xd)
-    Qh = torch.empty(Qd.shape, dtype=torch.float32, pin_memory=True).copy_(Qd)
+    Xd, Qd = make_inputs(torch, device, 0, wl, spec)
     torch.cuda.synchronize()
-    core = ref.RPLSHCore(N_TABLES, N_HASHES, SEED)
+    core = make_core(ref, spec)
+    batch = nq if wl == "c2" else (100_000 if wl == "c5" else None)
 
-    def step(host):
+    def to_dev(h):
+        if h is None:
+            return None
+        if isinstance(h, tuple):
+            return tuple(to_dev(x) for x in h)
+        return torch.from_numpy(h).to(device, non_blocking=True)
+
+    def step(X, Q, host):
         if host:
-            X = Xh.to(device, non_blocking=True)
-            Q = Qh.to(device, non_blocking=True)
+            X, Q = to_dev(X), to_dev(Q)
             torch.cuda.synchronize()
-        else:
-            X, Q = Xd, Qd
         t0 = time.perf_counter()
-        ix = core.fit_float(X, N_ROWS, N_FEATURES)
-        t1 = time.perf_counter()
-        cand = core.query_float(Q, N_QUERIES, ix, N_QUERIES)
+        if spec["mode"] == "fit_query":
+            # upstream's Python layer turns fit_query(batch_size=b) into fit + batched query
+            # (python/culsh/rp_lsh.py:145-147); the unbatched call needs ~46 GB of projection scratch
+            ix = core.fit_float(X, n, spec["d"])
+            t1 = time.perf_counter()
+            cand = core.query_float(X, n, ix, batch)
+        else:
+            ix = core_fit(core, spec, X)
+            t1 = time.perf_counter()
+            cand = core_query(core, spec, Q, ix, batch)
         t2 = time.perf_counter()
-        d2h = 0
-        if host:
-            a, b, c = cand.get_offsets(), cand.get_counts(), cand.get_indices()
-            d2h = a.nbytes + b.nbytes + c.nbytes
-        return t1 - t0, t2 - t1, d2h
+        return t1 - t0, t2 - t1, (read_back(cand) if host else 0)
 
     for _ in range(args.warmup):
-        step(False)
+        step(Xd, Qd, False)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     fits, queries = [], []
     for _ in range(args.steps):
-        f, q, _ = step(False)
+        f, q, _ = step(Xd, Qd, False)
         fits.append(f)
         queries.append(q)
     torch.cuda.synchronize()
     t_dev = time.perf_counter() - t0
-    step(True)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    d2h = 0
-    for _ in range(args.steps):
-        _, _, d2h = step(True)
-    torch.cuda.synchronize()
-    t_e2e = time.perf_counter() - t0
+    e2e = {"value": None, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    if not args.skip_e2e:
+        Xh, Qh = to_pinned_host(torch, Xd), to_pinned_host(torch, Qd)
+        step(Xh, Qh, True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        d2h = 0
+        for _ in range(args.steps):
+            _, _, d2h = step(Xh, Qh, True)
+        torch.cuda.synchronize()
+        t_e2e = time.perf_counter() - t0
+        e2e = {"value": n / (t_e2e / args.steps), "unit": "rows/s", "ms_per_step": t_e2e / args.steps * 1e3,
+               "h2d_bytes_per_step": int(nbytes_of(Xh) + nbytes_of(Qh)), "d2h_bytes_per_step": int(d2h)}
     base.update({
-        "value": N_ROWS / (t_dev / args.steps), "ms_per_step": t_dev / args.steps * 1e3,
-        "fit_rows_per_s": N_ROWS / statistics.mean(fits), "query_qps": N_QUERIES / statistics.mean(queries),
+        "value": n / (t_dev / args.steps), "ms_per_step": t_dev / args.steps * 1e3,
+        "fit_rows_per_s": n / statistics.mean(fits),
+        "query_qps": (nq or n) / statistics.mean(queries),
         "stage_ms": {"fit_total": statistics.mean(fits) * 1e3, "query_total": statistics.mean(queries) * 1e3},
-        "cpu_baseline": {"value": N_ROWS / (t_dev / args.steps), "unit": "rows/s", "cores": 0, "kind": "reference",
+        "cpu_baseline": {"value": n / (t_dev / args.steps), "unit": "rows/s", "cores": 0, "kind": "reference",
                          "sample": "full workload; upstream cuLSH CUDA build (its cuBLAS/CUB kernels compiled for "
                                    "sm_100) on one B200 - upstream has no CPU implementation of this path"},
-        "e2e": {"value": N_ROWS / (t_e2e / args.steps), "unit": "rows/s", "ms_per_step": t_e2e / args.steps * 1e3,
-                "h2d_bytes_per_step": int(Xh.numel() * 4 + Qh.numel() * 4), "d2h_bytes_per_step": int(d2h)},
-        "reference_device": "B200 (upstream CUDA build)",
+        "e2e": e2e, "reference_device": "B200 (upstream CUDA build)",
     })
     if world > 1:
-        base["config"]["note"] = "upstream is single-GPU: rank 0 runs one 1M-row shard"
+        base["config"]["note"] = "upstream is single-GPU: rank 0 runs one shard"
     print(json.dumps(base))
 
 
 def main():
-    global N_ROWS, N_QUERIES
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--rows", type=int, default=N_ROWS, help="rows per GPU (default: the 1M-row workload)")
-    ap.add_argument("--queries", type=int, default=N_QUERIES)
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c2")
+    ap.add_argument("--rows", type=int, default=None, help="rows per GPU (default: the workload's)")
+    ap.add_argument("--queries", type=int, default=None)
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: no host-input leg")
-    ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: no CPU baseline leg")
+    ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: no CPU baseline / TF32 peak leg")
     ap.add_argument("--reference-cpu", action="store_true",
                     help="reference arm: time the NumPy restatement on the host cores instead of "
                          "upstream's CUDA build")
     args = ap.parse_args()
-    N_ROWS, N_QUERIES = args.rows, args.queries
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    spec = dict(WORKLOADS[args.workload])
+    if args.rows:
+        spec["n"] = args.rows
+    if args.queries is not None and spec["nq"]:
+        spec["nq"] = args.queries
     if args.impl == "reference":
-        run_reference(args)
+        run_reference(args, args.workload, spec)
     else:
-        run_ours(args)
+        args.warmup = max(args.warmup, 3)
+        run_ours(args, args.workload, spec)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         import torch.distributed as dist
         if dist.is_initialized():

@@ -13,6 +13,7 @@
 #include <memory>
 #include <stdexcept>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "../../include/culsh_b200.h"
@@ -123,7 +124,8 @@ struct ParamKey {
     int family, H, d, window, is_double;
     uint64_t seed;
     bool operator<(const ParamKey& o) const {
-        return std::memcmp(this, &o, sizeof(ParamKey)) < 0;
+        return std::tie(family, H, d, window, is_double, seed) <
+               std::tie(o.family, o.H, o.d, o.window, o.is_double, o.seed);
     }
 };
 
@@ -139,6 +141,9 @@ enum ScratchSlot {
 
 struct Ctx {
     int device = 0;
+    // hash parameters already generated on this handle (they depend only on the key): the
+    // cuRAND generator set-up costs more than a tenth of a 1M-row fit
+    std::map<ParamKey, std::shared_ptr<void>> param_cache;
     void* slot_ptr[SL_COUNT] = {};
     size_t slot_cap[SL_COUNT] = {};
     cudaStream_t stream = nullptr;

@@ -20,6 +20,14 @@ struct culsh_handle {
     CtxPtr ctx;
 };
 
+// Hash parameters of an index; immutable once generated, so indexes built on one handle with
+// the same (family, shape, window, dtype, seed) share one set.
+struct ParamSet {
+    DevBuf<uint8_t> p0;       // projection (float/double [H][d]) | hash A (uint32 [H])
+    DevBuf<uint8_t> p1;       // bias (float/double [H])          | hash B (uint32 [H])
+    DevBuf<uint8_t> p_split;  // tensor-core path: hi/lo split of the projection
+};
+
 struct culsh_index {
     CtxPtr ctx;
     KeySpec ks;
@@ -30,9 +38,7 @@ struct culsh_index {
     DevBuf<uint32_t> bucket_keys;    // [B][NW] packed signatures, sorted inside a table
     DevBuf<int32_t> bucket_offsets;  // [B+1]
     DevBuf<int32_t> table_offsets;   // [L+1]
-    DevBuf<uint8_t> p0;              // projection (float/double [H][d]) | hash A (uint32 [H])
-    DevBuf<uint8_t> p1;              // bias (float/double [H])          | hash B (uint32 [H])
-    DevBuf<uint8_t> p_split;         // tensor-core path: hi/lo split of the projection
+    std::shared_ptr<ParamSet> params = std::make_shared<ParamSet>();  // may be shared between indexes
 };
 
 struct culsh_candidates {
@@ -176,17 +182,33 @@ struct CurandGen {
     }
 };
 
+void generate_params_uncached(culsh_index& ix);
+
 void generate_params(culsh_index& ix) {
     const CtxPtr& c = ix.ctx;
+    ParamKey key{ix.family, ix.L * ix.k, ix.family == CULSH_MINHASH ? 0 : ix.d, ix.window, ix.is_double, ix.seed};
+    auto it = c->param_cache.find(key);
+    if (it != c->param_cache.end()) {
+        ix.params = std::static_pointer_cast<ParamSet>(it->second);
+        return;
+    }
+    generate_params_uncached(ix);
+    if (c->param_cache.size() >= 16) c->param_cache.clear();
+    c->param_cache[key] = ix.params;
+}
+
+void generate_params_uncached(culsh_index& ix) {
+    const CtxPtr& c = ix.ctx;
     const int H = ix.L * ix.k;
+    ix.params = std::make_shared<ParamSet>();
     CurandGen gen(c->stream, ix.seed);
     if (ix.family == CULSH_MINHASH) {
-        ix.p0.alloc(c, sizeof(uint32_t) * H);
-        ix.p1.alloc(c, sizeof(uint32_t) * H);
-        CURAND_CHECK(curandGenerate(gen.g, reinterpret_cast<uint32_t*>(ix.p0.p), H));
-        CURAND_CHECK(curandGenerate(gen.g, reinterpret_cast<uint32_t*>(ix.p1.p), H));
+        ix.params->p0.alloc(c, sizeof(uint32_t) * H);
+        ix.params->p1.alloc(c, sizeof(uint32_t) * H);
+        CURAND_CHECK(curandGenerate(gen.g, reinterpret_cast<uint32_t*>(ix.params->p0.p), H));
+        CURAND_CHECK(curandGenerate(gen.g, reinterpret_cast<uint32_t*>(ix.params->p1.p), H));
         minhash_normalize_kernel<<<(unsigned)ceil_div(H, 256), 256, 0, c->stream>>>(
-            reinterpret_cast<uint32_t*>(ix.p0.p), reinterpret_cast<uint32_t*>(ix.p1.p), H);
+            reinterpret_cast<uint32_t*>(ix.params->p0.p), reinterpret_cast<uint32_t*>(ix.params->p1.p), H);
         KERNEL_CHECK();
         return;
     }
@@ -195,21 +217,21 @@ void generate_params(culsh_index& ix) {
         fail(CULSH_ERR_INVALID,
              "n_hash_tables*n_hashes*n_features = %zu must be even (cuRAND normal generation)", pn);
     const size_t esz = ix.is_double ? 8 : 4;
-    ix.p0.alloc(c, esz * pn);
+    ix.params->p0.alloc(c, esz * pn);
     if (ix.is_double)
-        CURAND_CHECK(curandGenerateNormalDouble(gen.g, reinterpret_cast<double*>(ix.p0.p), pn, 0.0, 1.0));
+        CURAND_CHECK(curandGenerateNormalDouble(gen.g, reinterpret_cast<double*>(ix.params->p0.p), pn, 0.0, 1.0));
     else
-        CURAND_CHECK(curandGenerateNormal(gen.g, reinterpret_cast<float*>(ix.p0.p), pn, 0.0f, 1.0f));
+        CURAND_CHECK(curandGenerateNormal(gen.g, reinterpret_cast<float*>(ix.params->p0.p), pn, 0.0f, 1.0f));
     if (ix.family == CULSH_PSLSH) {
-        ix.p1.alloc(c, esz * H);
+        ix.params->p1.alloc(c, esz * H);
         if (ix.is_double) {
-            CURAND_CHECK(curandGenerateUniformDouble(gen.g, reinterpret_cast<double*>(ix.p1.p), H));
+            CURAND_CHECK(curandGenerateUniformDouble(gen.g, reinterpret_cast<double*>(ix.params->p1.p), H));
             scale_by_int_kernel<double><<<(unsigned)ceil_div(pn, 256), 256, 0, c->stream>>>(
-                reinterpret_cast<double*>(ix.p0.p), pn, ix.window);
+                reinterpret_cast<double*>(ix.params->p0.p), pn, ix.window);
         } else {
-            CURAND_CHECK(curandGenerateUniform(gen.g, reinterpret_cast<float*>(ix.p1.p), H));
+            CURAND_CHECK(curandGenerateUniform(gen.g, reinterpret_cast<float*>(ix.params->p1.p), H));
             scale_by_int_kernel<float><<<(unsigned)ceil_div(pn, 256), 256, 0, c->stream>>>(
-                reinterpret_cast<float*>(ix.p0.p), pn, ix.window);
+                reinterpret_cast<float*>(ix.params->p0.p), pn, ix.window);
         }
         KERNEL_CHECK();
     }
@@ -226,13 +248,13 @@ void hash_dense(const culsh_index& ix, const KeySpec& ks, const T* X, int n, uin
                 uint8_t* ovf_rows, int n_total, int row_offset, bool allow_fallback = false) {
     const CtxPtr& c = ix.ctx;
     if (n == 0) return;
-    const T* P = reinterpret_cast<const T*>(ix.p0.p);
-    const T* bias = reinterpret_cast<const T*>(ix.p1.p);
+    const T* P = reinterpret_cast<const T*>(ix.params->p0.p);
+    const T* bias = reinterpret_cast<const T*>(ix.params->p1.p);
     auto launch = [&](cudaStream_t s, const T* Xd, int rows, int off) {
         bool tc = false;
         if (std::is_same<T, float>::value && c->projection_path != 1)
             tc = launch_project_tc(c, s, ix.family, reinterpret_cast<const float*>(Xd),
-                                   reinterpret_cast<const float*>(P), ix.p_split.p,
+                                   reinterpret_cast<const float*>(P), ix.params->p_split.p,
                                    reinterpret_cast<const float*>(bias), rows, ix.d, ix.L, ix.k, ks,
                                    keys, ovf_rows, off, n_total);
         if (!tc) {
@@ -299,8 +321,8 @@ void hash_csr(const culsh_index& ix, const KeySpec& ks, const int32_t* indices, 
                                      cudaMemcpyHostToDevice, c->stream));
         ii = d_indices.p;
     }
-    launch_minhash(c, c->stream, ii, ip, reinterpret_cast<const uint32_t*>(ix.p0.p),
-                   reinterpret_cast<const uint32_t*>(ix.p1.p), n, ix.L, ix.k, ks, keys, n_total,
+    launch_minhash(c, c->stream, ii, ip, reinterpret_cast<const uint32_t*>(ix.params->p0.p),
+                   reinterpret_cast<const uint32_t*>(ix.params->p1.p), n, ix.L, ix.k, ks, keys, n_total,
                    row_offset);
     // staging buffers are released in stream order after the kernel
 }
@@ -437,7 +459,8 @@ int bitmap_window_bits(const CtxPtr& c, int n_rows) {
     // a multiple of 4096 bits: the emission walks the window in 128-word groups
     size_t max_bits = ((c->smem_optin > fixed ? c->smem_optin - fixed : 0) * 8) / 4096 * 4096;
     size_t want = ((size_t)n_rows + 4095) / 4096 * 4096;
-    size_t cap = std::min<size_t>(max_bits, (size_t)1 << 20);
+    static const size_t cap_bits = [] { const char* e = getenv("CULSH_BITMAP_BITS"); return e ? (size_t)atol(e) : ((size_t)1 << 20); }();
+    size_t cap = std::min<size_t>(max_bits, cap_bits);
     return (int)std::min(want, cap);
 }
 
@@ -606,8 +629,8 @@ void empty_result(const CtxPtr& c, culsh_candidates& out) {
 // Family front ends
 // -----------------------------------------------------------------------------------------
 void prepare_tc_split(culsh_index& ix) {
-    if (ix.family == CULSH_MINHASH || ix.is_double) return;
-    prepare_project_tc(ix.ctx, reinterpret_cast<const float*>(ix.p0.p), ix.L * ix.k, ix.d, ix.L, ix.k, ix.p_split);
+    if (ix.family == CULSH_MINHASH || ix.is_double || ix.params->p_split.p) return;
+    prepare_project_tc(ix.ctx, reinterpret_cast<const float*>(ix.params->p0.p), ix.L * ix.k, ix.d, ix.L, ix.k, ix.params->p_split);
 }
 
 template <typename T>
@@ -761,7 +784,10 @@ int culsh_create(int device, culsh_handle** out) {
 }
 
 int culsh_destroy(culsh_handle* h) {
-    return guarded([&] { delete h; });
+    return guarded([&] {
+        if (h) h->ctx->param_cache.clear();  // the cached sets hold references to the context
+        delete h;
+    });
 }
 
 int culsh_get_stats(const culsh_handle* h, culsh_stats* out) {
@@ -970,7 +996,7 @@ int culsh_index_get_meta(const culsh_index* ix, culsh_index_meta* m) {
         // minhash/index.cuh size_bytes), in upstream's layout
         uint64_t sz = ((uint64_t)ix->n_buckets + 1) * 4 + ((uint64_t)ix->L + 1) * 4 +
                       (uint64_t)ix->n_buckets * ix->ks.sig_nbytes + (uint64_t)ix->n * ix->L * 4;
-        sz += ix->p0.bytes() + ix->p1.bytes();
+        sz += ix->params->p0.bytes() + ix->params->p1.bytes();
         m->size_bytes = sz;
     });
 }
@@ -1008,7 +1034,7 @@ int culsh_index_get_projection(const culsh_index* ix, void* dst) {
         if (!ix) fail(CULSH_ERR_INVALID, "null index");
         if (ix->family == CULSH_MINHASH) fail(CULSH_ERR_INVALID, "MinHash index has no projection");
         DeviceGuard g(ix->ctx->device);
-        copy_out(ix->ctx, dst, ix->p0.p, ix->p0.bytes());
+        copy_out(ix->ctx, dst, ix->params->p0.p, ix->params->p0.bytes());
     });
 }
 int culsh_index_get_bias(const culsh_index* ix, void* dst) {
@@ -1016,7 +1042,7 @@ int culsh_index_get_bias(const culsh_index* ix, void* dst) {
         if (!ix) fail(CULSH_ERR_INVALID, "null index");
         if (ix->family != CULSH_PSLSH) fail(CULSH_ERR_INVALID, "only a p-stable index has a bias");
         DeviceGuard g(ix->ctx->device);
-        copy_out(ix->ctx, dst, ix->p1.p, ix->p1.bytes());
+        copy_out(ix->ctx, dst, ix->params->p1.p, ix->params->p1.bytes());
     });
 }
 int culsh_index_get_hash_a(const culsh_index* ix, uint32_t* dst) {
@@ -1024,7 +1050,7 @@ int culsh_index_get_hash_a(const culsh_index* ix, uint32_t* dst) {
         if (!ix) fail(CULSH_ERR_INVALID, "null index");
         if (ix->family != CULSH_MINHASH) fail(CULSH_ERR_INVALID, "not a MinHash index");
         DeviceGuard g(ix->ctx->device);
-        copy_out(ix->ctx, dst, ix->p0.p, ix->p0.bytes());
+        copy_out(ix->ctx, dst, ix->params->p0.p, ix->params->p0.bytes());
     });
 }
 int culsh_index_get_hash_b(const culsh_index* ix, uint32_t* dst) {
@@ -1032,7 +1058,7 @@ int culsh_index_get_hash_b(const culsh_index* ix, uint32_t* dst) {
         if (!ix) fail(CULSH_ERR_INVALID, "null index");
         if (ix->family != CULSH_MINHASH) fail(CULSH_ERR_INVALID, "not a MinHash index");
         DeviceGuard g(ix->ctx->device);
-        copy_out(ix->ctx, dst, ix->p1.p, ix->p1.bytes());
+        copy_out(ix->ctx, dst, ix->params->p1.p, ix->params->p1.bytes());
     });
 }
 
@@ -1077,15 +1103,15 @@ int culsh_index_load(culsh_handle* h, int family, int is_double, const int32_t* 
         CU_CHECK(cudaMemcpyAsync(ix->table_offsets.p, table_bucket_offsets, ix->table_offsets.bytes(), cudaMemcpyDefault, s));
         const int H = L * k;
         if (family == CULSH_MINHASH) {
-            ix->p0.alloc(c, sizeof(uint32_t) * H);
-            ix->p1.alloc(c, sizeof(uint32_t) * H);
+            ix->params->p0.alloc(c, sizeof(uint32_t) * H);
+            ix->params->p1.alloc(c, sizeof(uint32_t) * H);
         } else {
             const size_t esz = ix->is_double ? 8 : 4;
-            ix->p0.alloc(c, esz * H * n_features);
-            if (family == CULSH_PSLSH) ix->p1.alloc(c, esz * H);
+            ix->params->p0.alloc(c, esz * H * n_features);
+            if (family == CULSH_PSLSH) ix->params->p1.alloc(c, esz * H);
         }
-        CU_CHECK(cudaMemcpyAsync(ix->p0.p, param0, ix->p0.bytes(), cudaMemcpyDefault, s));
-        if (ix->p1.n) CU_CHECK(cudaMemcpyAsync(ix->p1.p, param1, ix->p1.bytes(), cudaMemcpyDefault, s));
+        CU_CHECK(cudaMemcpyAsync(ix->params->p0.p, param0, ix->params->p0.bytes(), cudaMemcpyDefault, s));
+        if (ix->params->p1.n) CU_CHECK(cudaMemcpyAsync(ix->params->p1.p, param1, ix->params->p1.bytes(), cudaMemcpyDefault, s));
         // raw signatures -> packed keys (p-stable: narrowest element width that holds them)
         Scratch<uint8_t> raw(c, SL_MISC0, B * sig_nbytes);
         CU_CHECK(cudaMemcpyAsync(raw.p, bucket_signatures, raw.bytes(), cudaMemcpyDefault, s));

@@ -350,11 +350,32 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
                 cleared = true;
                 __syncthreads();
             }
-            // mark: warps take lists round-robin, lanes stride a list
-            for (int t = warp; t < Lg; t += BM_WARPS) {
-                const int lo = s_lo[t], we = s_we[t];
-                for (int i = lo + lane; i < we; i += 32) {
-                    uint32_t id = (uint32_t)(cand[i] - win_lo);
+            // mark.  The whole CTA strides every list; eight lists are in flight at a time so
+            // that their global loads overlap (most lists are shorter than one CTA stride).
+            for (int t0 = 0; t0 < Lg; t0 += 8) {
+                int32_t v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int t = t0 + j;
+                    v[j] = -1;
+                    if (t < Lg) {
+                        const int i = s_lo[t] + tid;
+                        if (i < s_we[t]) v[j] = cand[i];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (v[j] >= 0) {
+                        const uint32_t id = (uint32_t)(v[j] - win_lo);
+                        atomicOr(&bitmap[id >> 5], 1u << (id & 31));
+                    }
+                }
+            }
+            for (int t = 0; t < Lg; ++t) {  // the tails of lists longer than one CTA stride
+                const int we = s_we[t];
+#pragma unroll 4
+                for (int i = s_lo[t] + BM_THREADS + tid; i < we; i += BM_THREADS) {
+                    const uint32_t id = (uint32_t)(cand[i] - win_lo);
                     atomicOr(&bitmap[id >> 5], 1u << (id & 31));
                 }
             }
