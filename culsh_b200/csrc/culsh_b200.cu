@@ -504,9 +504,14 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
         CU_CHECK(cudaStreamSynchronize(s));
         return;
     }
-    Scratch<int32_t> tmp(c, SL_TMP, raw_total);
+    // Single pass (ids emitted at their final position, no compaction) when the index fits one
+    // bitmap window and most queries have large candidate sets; otherwise scratch + compaction.
+    const bool chained = (size_t)ix.n <= (size_t)wbits && (size_t)nb * 2 >= (size_t)n_q;
+    const uint32_t n_other = (uint32_t)n_q - nb - nm;  // queries on the warp path (incl. empty ones)
+    Scratch<int32_t> tmp;
+    tmp.reserve(c, SL_TMP, raw_total);
     tr.lap("alloc tmp");
-    {
+    if (n_other) {
         size_t blocks = std::min<size_t>(ceil_div(n_q, SM_WARPS), (size_t)c->sm_count * 16);
         dedupe_small_kernel<<<(unsigned)blocks, SM_THREADS, 0, s>>>(
             matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, raw_off.p, n_q, L, tmp.p, out.counts.p);
@@ -521,36 +526,76 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
                                                        raw_cnt.p, raw_off.p, L, id_bytes, tmp.p, out.counts.p);
         KERNEL_CHECK();
     }
-    if (nb) {
+    if (chained) {
+        out.indices.alloc(c, raw_total);  // capacity: the unique total is not known yet
+        Scratch<unsigned long long> status(c, SL_CHAIN, (size_t)n_q + 1);
+        uint32_t* ticket = reinterpret_cast<uint32_t*>(status.p + n_q);
+        CU_CHECK(cudaMemsetAsync(status.p, 0, sizeof(unsigned long long) * ((size_t)n_q + 1), s));
         size_t smem = bitmap_smem_bytes(wbits);
-        CU_CHECK(cudaFuncSetAttribute(dedupe_bitmap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        dedupe_bitmap_kernel<<<nb, BM_THREADS, smem, s>>>(big_list.p, matched, ix.bucket_offsets.p,
-                                                          ix.cand.p, raw_off.p, L, ix.n, wbits, tmp.p,
-                                                          out.counts.p);
+        CU_CHECK(cudaFuncSetAttribute(dedupe_chained_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        unsigned long long* phase = nullptr;
+        Scratch<unsigned long long> phase_buf;
+        if (tr.on) {  // CULSH_TRACE: per-phase cycle counts of the kernel (thread 0 of every CTA)
+            phase_buf.reserve(c, SL_MISC0, 16);
+            phase = phase_buf.p;
+            CU_CHECK(cudaMemsetAsync(phase, 0, 16 * sizeof(unsigned long long), s));
+        }
+        dedupe_chained_kernel<<<(unsigned)n_q, BM_THREADS, smem, s>>>(
+            matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, raw_off.p, n_q, L, wbits, mid_max, tmp.p, tmp.p,
+            status.p, ticket, out.indices.p, out.counts.p, out.offsets.p, c->d_error, phase);
         KERNEL_CHECK();
-    }
-    exclusive_scan<uint64_t, uint64_t>(s, out.counts.p, n_q, out.offsets.p, scratch.p);
-    uint64_t total = 0;
-    read_words(c, out.offsets.p + n_q, sizeof(uint64_t), &total);
-    tr.lap("dedupe+scan+sync");
-    out.total = total;
-    c->stats.unique_candidates += total;
-    if (total) {
-        out.indices.alloc(c, total);
-        tr.lap("alloc indices");
-        size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
-        compact_small_kernel<<<(unsigned)blocks, 256, 0, s>>>(tmp.p, raw_cnt.p, raw_off.p, out.counts.p,
-                                                             out.offsets.p, n_q, out.indices.p);
-        KERNEL_CHECK();
+        if (phase) {
+            unsigned long long hc[16];
+            read_words(c, phase, sizeof(hc), hc);
+            fprintf(stderr, "[culsh trace] mark detail cycles/query: prefix %.0f search+load %.0f (+atomics %.0f) tail-sync %.0f\n",
+                    (double)hc[8] / n_q, (double)hc[9] / n_q, (double)hc[10] / n_q, (double)hc[11] / n_q);
+            fprintf(stderr, "[culsh trace] chained kernel cycles/query: setup %.0f clear+mark %.0f count %.0f chain %.0f emit %.0f\n",
+                    (double)hc[0] / n_q, (double)hc[1] / n_q, (double)hc[2] / n_q, (double)hc[3] / n_q, (double)hc[4] / n_q);
+        }
+        uint64_t total = 0;
+        read_words(c, out.offsets.p + n_q, sizeof(uint64_t), &total);
+        tr.lap("chained dedupe+sync");
+        out.total = total;
+        c->stats.unique_candidates += total;
+        if (total == 0) {
+            out.indices.release();
+        } else if (total * 4 < raw_total * 3) {  // much smaller than the capacity: keep an exact copy
+            DevBuf<int32_t> exact(c, total);
+            CU_CHECK(cudaMemcpyAsync(exact.p, out.indices.p, sizeof(int32_t) * total, cudaMemcpyDeviceToDevice, s));
+            out.indices = std::move(exact);
+        }
+    } else {
         if (nb) {
-            compact_big_kernel<<<nb, 256, 0, s>>>(big_list.p, tmp.p, raw_off.p, out.counts.p,
-                                                  out.offsets.p, out.indices.p);
+            size_t smem = bitmap_smem_bytes(wbits);
+            CU_CHECK(cudaFuncSetAttribute(dedupe_bitmap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            dedupe_bitmap_kernel<<<nb, BM_THREADS, smem, s>>>(big_list.p, matched, ix.bucket_offsets.p,
+                                                              ix.cand.p, raw_off.p, L, ix.n, wbits, tmp.p,
+                                                              out.counts.p);
             KERNEL_CHECK();
         }
-        if (nm) {
-            compact_big_kernel<<<nm, 256, 0, s>>>(mid_list, tmp.p, raw_off.p, out.counts.p,
-                                                  out.offsets.p, out.indices.p);
+        exclusive_scan<uint64_t, uint64_t>(s, out.counts.p, n_q, out.offsets.p, scratch.p);
+        uint64_t total = 0;
+        read_words(c, out.offsets.p + n_q, sizeof(uint64_t), &total);
+        tr.lap("dedupe+scan+sync");
+        out.total = total;
+        c->stats.unique_candidates += total;
+        if (total) {
+            out.indices.alloc(c, total);
+            tr.lap("alloc indices");
+            size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
+            compact_small_kernel<<<(unsigned)blocks, 256, 0, s>>>(tmp.p, raw_cnt.p, raw_off.p, out.counts.p,
+                                                                 out.offsets.p, n_q, out.indices.p);
             KERNEL_CHECK();
+            if (nb) {
+                compact_big_kernel<<<nb, 256, 0, s>>>(big_list.p, tmp.p, raw_off.p, out.counts.p,
+                                                      out.offsets.p, out.indices.p);
+                KERNEL_CHECK();
+            }
+            if (nm) {
+                compact_big_kernel<<<nm, 256, 0, s>>>(mid_list, tmp.p, raw_off.p, out.counts.p,
+                                                      out.offsets.p, out.indices.p);
+                KERNEL_CHECK();
+            }
         }
     }
     tm.mark();

@@ -295,6 +295,77 @@ inline size_t bitmap_smem_bytes(int window_bits) {
     return (size_t)window_bits / 8 + 3 * BM_MAX_L * sizeof(int) + (size_t)BM_WARPS * BM_STAGE * sizeof(int32_t);
 }
 
+
+// Marks the ids of Lg ascending lists [s_lo[t], s_we[t]) of `cand` in the bitmap.  The lists are
+// laid end to end (s_pre = exclusive prefix of their lengths) and that flat sequence is cut
+// into equal stretches, one per warp, so the work is balanced however uneven the lists are.
+// Must be called by all BM_THREADS threads; s_lo / s_we must be visible (barrier before).
+__device__ __forceinline__ void mark_lists_flat(uint32_t* __restrict__ bitmap, const int32_t* __restrict__ cand,
+                                                const int* __restrict__ s_lo, const int* __restrict__ s_we,
+                                                int* __restrict__ s_pre, uint32_t* __restrict__ s_wtot, int Lg,
+                                                int win_lo, long long* dbg = nullptr) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    long long t0 = dbg ? clock64() : 0;
+    const int len = tid < Lg ? s_we[tid] - s_lo[tid] : 0;
+    int inc = len;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += x;
+    }
+    if (lane == 31) s_wtot[warp] = (uint32_t)inc;
+    __syncthreads();
+    int base = 0, total = 0;
+    for (int w = 0; w < BM_WARPS; ++w) {
+        const int x = (int)s_wtot[w];
+        if (w < warp) base += x;
+        total += x;
+    }
+    if (tid < Lg) s_pre[tid] = base + inc - len;
+    __syncthreads();
+    if (dbg && tid == 0) { dbg[0] += clock64() - t0; t0 = clock64(); }
+    // Each warp takes a contiguous stretch of the flat sequence; a lane's list index only moves
+    // forward (one binary search per warp, then cheap advances), loads stay coalesced and MK of
+    // them are in flight per lane.
+    constexpr int MK = 20;
+    const int per_warp = (((total + BM_WARPS - 1) / BM_WARPS) + 31) & ~31;
+    const int w_begin = warp * per_warp, w_end = min(total, w_begin + per_warp);
+    if (w_begin < w_end) {
+        int t = 0;
+        {
+            int a = 0, b = Lg - 1;
+            while (a < b) {  // largest t with s_pre[t] <= w_begin
+                const int mid = (a + b + 1) >> 1;
+                if (s_pre[mid] <= w_begin) a = mid; else b = mid - 1;
+            }
+            t = a;
+        }
+        for (int e0 = w_begin + lane; e0 - lane < w_end; e0 += 32 * MK) {
+            int32_t v[MK];
+#pragma unroll
+            for (int j = 0; j < MK; ++j) {
+                const int e = e0 + 32 * j;
+                v[j] = -1;
+                if (e < w_end) {
+                    while (t + 1 < Lg && s_pre[t + 1] <= e) ++t;
+                    v[j] = cand[s_lo[t] + (e - s_pre[t])];
+                }
+            }
+            if (dbg && tid == 0) dbg[1] += clock64() - t0;
+#pragma unroll
+            for (int j = 0; j < MK; ++j) {
+                if (v[j] >= 0) {
+                    const uint32_t id = (uint32_t)(v[j] - win_lo);
+                    atomicOr(&bitmap[id >> 5], 1u << (id & 31));
+                }
+            }
+            if (dbg && tid == 0) { dbg[2] += clock64() - t0; t0 = clock64(); }
+        }
+    }
+    __syncthreads();
+    if (dbg && tid == 0) dbg[3] += clock64() - t0;
+}
+
 __global__ void __launch_bounds__(BM_THREADS)
 dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __restrict__ matched,
                      const int32_t* __restrict__ bucket_offsets, const int32_t* __restrict__ cand,
@@ -350,36 +421,7 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
                 cleared = true;
                 __syncthreads();
             }
-            // mark.  The whole CTA strides every list; eight lists are in flight at a time so
-            // that their global loads overlap (most lists are shorter than one CTA stride).
-            for (int t0 = 0; t0 < Lg; t0 += 8) {
-                int32_t v[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int t = t0 + j;
-                    v[j] = -1;
-                    if (t < Lg) {
-                        const int i = s_lo[t] + tid;
-                        if (i < s_we[t]) v[j] = cand[i];
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (v[j] >= 0) {
-                        const uint32_t id = (uint32_t)(v[j] - win_lo);
-                        atomicOr(&bitmap[id >> 5], 1u << (id & 31));
-                    }
-                }
-            }
-            for (int t = 0; t < Lg; ++t) {  // the tails of lists longer than one CTA stride
-                const int we = s_we[t];
-#pragma unroll 4
-                for (int i = s_lo[t] + BM_THREADS + tid; i < we; i += BM_THREADS) {
-                    const uint32_t id = (uint32_t)(cand[i] - win_lo);
-                    atomicOr(&bitmap[id >> 5], 1u << (id & 31));
-                }
-            }
-            __syncthreads();
+            mark_lists_flat(bitmap, cand, s_lo, s_we, s_hi, s_wtot, Lg, win_lo);
         }
         if (!cleared) continue;  // uniform: nothing in this window
         // ---- pop-count scan.  The window is cut into groups of 128 words (one uint4 per lane);
@@ -446,6 +488,265 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
         __syncthreads();
     }
     if (tid == 0) uniq_cnt[q] = (uint64_t)written;
+}
+
+// ---------------------------------------------------------------------------------------
+// Single-pass form of the block path for indexes that fit one bitmap window and query sets
+// dominated by large candidate sets: one CTA per query IN QUERY ORDER (tickets from an atomic
+// counter, so a CTA only ever waits on CTAs that started before it).  After counting its
+// unique ids a CTA publishes the count, obtains the sum over all earlier queries from a
+// chained look-back over `status` (a warp reads 32 predecessors per round), and emits its
+// sorted ids straight at their final CSR position - no scratch copy, no compaction pass.
+// Queries that took the warp / sort paths have their count and ids in `tmp` already; their
+// CTA joins the chain with that count and copies the ids.
+// status word: bits 62-63 flag (0 empty, 1 own count, 2 inclusive prefix), low 62 bits value.
+// Every wait is bounded; on expiry DEV_ERR_LOOKBACK_TIMEOUT is recorded and the CTA goes on.
+// ---------------------------------------------------------------------------------------
+constexpr unsigned long long CH_FLAG_AGG = 1ull << 62;
+constexpr unsigned long long CH_FLAG_INC = 2ull << 62;
+constexpr unsigned long long CH_VAL_MASK = (1ull << 62) - 1;
+constexpr int CH_SPIN_LIMIT = 1 << 22;
+
+__device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long* p) {
+    return *reinterpret_cast<const volatile unsigned long long*>(p);
+}
+
+// Executed by warp 0 of the CTA that owns ticket q; returns the exclusive prefix.
+// `publish` stores this query's own count first (done once); with `blocking` false the walk
+// gives up (returns false, nothing published) as soon as a needed predecessor is missing.
+__device__ __forceinline__ bool chain_exclusive_prefix(unsigned long long* status, int q,
+                                                       unsigned long long own, int lane, int* d_error,
+                                                       bool publish, bool blocking, unsigned long long& excl_out) {
+    unsigned long long* mine = status + q;
+    excl_out = 0ull;
+    if (q == 0) {
+        if (lane == 0) *reinterpret_cast<volatile unsigned long long*>(mine) = CH_FLAG_INC | own;
+        return true;
+    }
+    if (publish && lane == 0) *reinterpret_cast<volatile unsigned long long*>(mine) = CH_FLAG_AGG | own;
+    unsigned long long excl = 0;
+    int j = q - 1;
+    bool done = false;
+    while (!done) {
+        const int idx = j - lane;
+        unsigned long long s = idx >= 0 ? ld_volatile_u64(status + idx) : CH_FLAG_INC;  // before query 0: prefix 0
+        int spins = 0;
+        while (__any_sync(0xFFFFFFFFu, (s >> 62) == 0)) {  // someone in the window has not published yet
+            if (!blocking) {
+                // usable only if a prefix sits nearer than the first missing entry
+                const uint32_t miss = __ballot_sync(0xFFFFFFFFu, (s >> 62) == 0);
+                const uint32_t inc = __ballot_sync(0xFFFFFFFFu, (s >> 62) == 2);
+                if (inc && (__ffs(inc) < __ffs(miss))) break;
+                return false;
+            }
+            if (++spins > CH_SPIN_LIMIT) {
+                if (lane == 0) atomicOr(d_error, DEV_ERR_LOOKBACK_TIMEOUT);
+                s |= CH_FLAG_INC;  // give up: treat as a prefix so that the walk ends
+                break;
+            }
+            if (spins > 16) __nanosleep(64);
+            if ((s >> 62) == 0) s = ld_volatile_u64(status + idx);
+        }
+        const uint32_t inc_mask = __ballot_sync(0xFFFFFFFFu, (s >> 62) == 2);
+        const int stop = inc_mask ? __ffs(inc_mask) - 1 : 32;  // nearest predecessor holding a prefix
+        unsigned long long v = lane <= stop ? (s & CH_VAL_MASK) : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        excl += v;
+        done = inc_mask != 0;
+        j -= 32;
+    }
+    if (lane == 0) *reinterpret_cast<volatile unsigned long long*>(mine) = CH_FLAG_INC | ((excl + own) & CH_VAL_MASK);
+    excl_out = excl;
+    return true;
+}
+
+__global__ void __launch_bounds__(BM_THREADS)
+dedupe_chained_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
+                      const int32_t* __restrict__ cand, const uint64_t* __restrict__ raw_cnt,
+                      const uint64_t* __restrict__ raw_off, int n_q, int L, int window_bits, int mid_max,
+                      int32_t* scratch /* same buffer as tmp; big queries write and re-read it */,
+                      const int32_t* __restrict__ tmp, unsigned long long* __restrict__ status,
+                      uint32_t* __restrict__ ticket, int32_t* __restrict__ out_indices,
+                      uint64_t* __restrict__ counts, uint64_t* __restrict__ offsets, int* __restrict__ d_error,
+                      unsigned long long* __restrict__ phase_cycles /* optional: 12 accumulators */) {
+    extern __shared__ __align__(16) uint32_t s_dyn[];
+    long long t_phase = phase_cycles ? clock64() : 0;
+    long long dbg_local[4] = {0, 0, 0, 0};
+    auto lap = [&](int k) {
+        if (phase_cycles && threadIdx.x == 0) {
+            long long now = clock64();
+            atomicAdd(&phase_cycles[k], (unsigned long long)(now - t_phase));
+            t_phase = now;
+        }
+    };
+    uint32_t* bitmap = s_dyn;                                       // [window_bits / 32]
+    int* s_lo = reinterpret_cast<int*>(bitmap + window_bits / 32);  // [Lc] list start (global position)
+    int* s_hi = s_lo + BM_MAX_L;
+    int* s_we = s_hi + BM_MAX_L;                                    // [Lc] list end
+    int32_t* s_stage = reinterpret_cast<int32_t*>(s_we + BM_MAX_L); // [BM_WARPS][BM_STAGE]
+    __shared__ uint32_t s_wtot[BM_WARPS];
+    __shared__ unsigned long long s_excl;
+    __shared__ int s_q;
+    __shared__ int s_resolved;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) s_q = (int)atomicAdd(ticket, 1u);
+    __syncthreads();
+    const int q = s_q;
+    if (q >= n_q) return;
+    const uint64_t raw = raw_cnt[q];
+    const bool big = raw > (uint64_t)SMALL_MAX && raw > (uint64_t)mid_max;
+    lap(0);
+    const int words = window_bits / 32;
+    int32_t* stage = s_stage + warp * BM_STAGE;
+
+    if (!big) {  // count and ids are in tmp already: join the chain, then copy
+        const unsigned long long c = counts[q];
+        if (warp == 0) {
+            unsigned long long e;
+            chain_exclusive_prefix(status, q, c, lane, d_error, true, true, e);
+            if (lane == 0) s_excl = e;
+        }
+        __syncthreads();
+        const unsigned long long excl = s_excl;
+        const int32_t* src = tmp + raw_off[q];
+        for (unsigned long long i = tid; i < c; i += BM_THREADS) out_indices[excl + i] = src[i];
+        if (tid == 0) {
+            offsets[q] = excl;
+            if (q == n_q - 1) offsets[n_q] = excl + c;
+        }
+        return;
+    }
+
+    // ---- clear + mark (single window covers every row id) ----
+    {
+        uint4* b4 = reinterpret_cast<uint4*>(bitmap);
+        for (int w = tid; w < words / 4; w += BM_THREADS) b4[w] = make_uint4(0, 0, 0, 0);
+    }
+    for (int g0 = 0; g0 < L; g0 += BM_MAX_L) {
+        const int Lg = min(BM_MAX_L, L - g0);
+        __syncthreads();  // bitmap cleared / previous group's lists consumed
+        for (int t = tid; t < Lg; t += BM_THREADS) {
+            const int b = matched[(size_t)q * L + g0 + t];
+            int lo = 0, we = 0;
+            if (b >= 0) { lo = bucket_offsets[b]; we = bucket_offsets[b + 1]; }
+            s_lo[t] = lo; s_we[t] = we;
+        }
+        __syncthreads();
+        mark_lists_flat(bitmap, cand, s_lo, s_we, s_hi, s_wtot, Lg, 0, phase_cycles ? dbg_local : nullptr);
+    }
+    __syncthreads();
+    lap(1);
+    if (phase_cycles && threadIdx.x == 0)
+        for (int i = 0; i < 4; ++i) atomicAdd(&phase_cycles[8 + i], (unsigned long long)dbg_local[i]);
+
+    // ---- count ----
+    const uint4* b4 = reinterpret_cast<const uint4*>(bitmap);
+    const int groups = words / 128;
+    const int gpw = (groups + BM_WARPS - 1) / BM_WARPS;
+    const int g_begin = warp * gpw, g_end = min(groups, g_begin + gpw);
+    uint32_t wsum = 0;
+    for (int g = g_begin; g < g_end; ++g) {
+        const uint4 v = b4[g * 32 + lane];
+        wsum += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xFFFFFFFFu, wsum, o);
+    if (lane == 0) s_wtot[warp] = wsum;
+    __syncthreads();
+    uint32_t wbase = 0, wtotal = 0;
+    for (int i = 0; i < BM_WARPS; ++i) {
+        const uint32_t x = s_wtot[i];
+        if (i < warp) wbase += x;
+        wtotal += x;
+    }
+    lap(2);
+    // One look at the chain without waiting: if the prefix is already known the ids go straight
+    // to their final place; otherwise they go to the scratch slot of this query first, the chain
+    // is resolved after the emission (by then the predecessors have usually published) and the
+    // CTA moves its ids, still hot in L2, to the final place itself.
+    if (warp == 0) {
+        unsigned long long e;
+        const bool ok = chain_exclusive_prefix(status, q, (unsigned long long)wtotal, lane, d_error, true, false, e);
+        if (lane == 0) { s_excl = e; s_resolved = ok ? 1 : 0; }
+    }
+    __syncthreads();
+    lap(3);
+    const bool direct = s_resolved != 0;
+    unsigned long long excl = s_excl;
+    int32_t* out = direct ? out_indices + excl : scratch + raw_off[q];
+    uint32_t out_pos = wbase;
+    uint32_t fill = 0;
+    for (int g = g_begin; g < g_end; ++g) {
+        const uint4 v = b4[g * 32 + lane];
+        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+        const uint32_t c = __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
+        uint32_t inc = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= o) inc += x;
+        }
+        const uint32_t tot = __shfl_sync(0xFFFFFFFFu, inc, 31);
+        if (tot == 0) continue;
+        const int32_t id0 = (g * 128 + lane * 4) * 32;
+        if (tot > BM_STAGE || fill + tot > BM_STAGE) {
+            __syncwarp();
+            for (uint32_t i = lane; i < fill; i += 32) out[out_pos + i] = stage[i];
+            out_pos += fill;
+            fill = 0;
+            __syncwarp();
+        }
+        if (tot > BM_STAGE) {
+            int32_t* dst = out + out_pos + (inc - c);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t bits = wv[j];
+                while (bits) {
+                    const int b = __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    *dst++ = id0 + j * 32 + b;
+                }
+            }
+            out_pos += tot;
+        } else {
+            int32_t* dst = stage + fill + (inc - c);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t bits = wv[j];
+                while (bits) {
+                    const int b = __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    *dst++ = id0 + j * 32 + b;
+                }
+            }
+            fill += tot;
+        }
+    }
+    __syncwarp();
+    for (uint32_t i = lane; i < fill; i += 32) out[out_pos + i] = stage[i];
+    if (!direct) {
+        __syncthreads();  // all ids of this query are in its scratch slot
+        if (warp == 0) {
+            unsigned long long e;
+            chain_exclusive_prefix(status, q, (unsigned long long)wtotal, lane, d_error, false, true, e);
+            if (lane == 0) s_excl = e;
+        }
+        __syncthreads();
+        excl = s_excl;
+        const int32_t* src = scratch + raw_off[q];
+        for (uint32_t i = tid; i < wtotal; i += BM_THREADS) out_indices[excl + i] = src[i];
+    }
+    if (tid == 0) {
+        counts[q] = wtotal;
+        offsets[q] = excl;
+        if (q == n_q - 1) offsets[n_q] = excl + wtotal;
+    }
+    if (phase_cycles) {
+        __syncthreads();
+        lap(4);
+    }
 }
 
 // ---------------------------------------------------------------------------------------
