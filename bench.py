@@ -19,9 +19,10 @@ Other workloads (same JSON line, for the remaining benchmark configurations):
   c5  RPLSH fit_query self-join, 10,000,000 x 256 unit-sphere rows, 48 x 24, seed 3 (1 GPU)
 
 At N > 1 (torchrun, one rank per GPU) each rank holds its own shard (weak scaling), the
-queries are the same on every rank, and the per-shard candidates are exchanged over NCCL (one
-all-to-all) so that rank j holds the merged CSR, with global row ids, of the j-th slice of the
-queries.
+queries are the same on every rank, and rank j ends up with the merged CSR, with global row
+ids, of the j-th slice of the queries: every rank publishes its per-shard CSR in peer-mapped
+device memory and each rank's merge kernel reads the lists it needs straight from its peers
+over NVLink (NCCL carries only two one-word all-reduces per step as barriers).
 
 `--impl reference` times upstream cuLSH's own CUDA build (oracle/_ref, compiled from the
 upstream sources by oracle/Makefile) on the same workload when that module loads, else the
@@ -72,7 +73,7 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms while the timed region runs."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -86,7 +87,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200", "-i", str(self.gpu)],
+                 "-lms", "50", "-i", str(self.gpu)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -337,6 +338,7 @@ def run_ours(args, wl, spec):
     core.set_profiling(True)
     batch = nq if wl == "c2" else None
     stage = {"fit": [], "query": []}
+    exchange = sharded.PeerExchange(device=local) if world > 1 else None
 
     def step(X, Q, host_out):
         if spec["mode"] == "fit_query":
@@ -348,9 +350,8 @@ def run_ours(args, wl, spec):
             s_fit = core.last_stats()
             cand = core_query(core, spec, Q, index, batch)
             s_q = core.last_stats()
-            if world > 1:  # each rank receives the merged lists of its slice of the queries
-                cand, _ = sharded.exchange_by_query(cand, row_base=rank * n,
-                                                    row_bases=[r * n for r in range(world)])
+            if world > 1:  # each rank pulls the lists of its slice of the queries from its peers
+                cand, _ = exchange.exchange(cand, [r * n for r in range(world)])
         return s_fit, s_q, (read_back(cand) if host_out else 0)
 
     for _ in range(args.warmup):
@@ -438,7 +439,7 @@ def run_ours(args, wl, spec):
         "config": {"workload": spec["name"], "id": wl, "rows_per_gpu": n, "queries": nq, "seed": spec["seed"],
                    "l2": (f"inputs ({in_bytes >> 20} MB per step) larger than L2, no flush" if in_bytes > (130 << 20)
                           else f"inputs ({in_bytes >> 10} KB) fit L2: small configuration, no flush"),
-                   "parallelism": f"row-sharded x{world}, all-to-all candidate exchange" if world > 1 else "single GPU"},
+                   "parallelism": f"row-sharded x{world}, peer-memory candidate exchange fused with the merge" if world > 1 else "single GPU"},
         "fit_rows_per_s": total_rows / (fit_ms * 1e-3),
         "query_qps": (nq / (q_ms * 1e-3)) if q_ms > 0 else None,
         "stage_ms": {"fit_total": fit_ms, "hash": hash_ms, "sort": mean("sort_ms", "fit"),
@@ -574,7 +575,7 @@ def run_reference(args, wl, spec):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c2")

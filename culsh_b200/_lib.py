@@ -79,6 +79,11 @@ SIGNATURES = {
     "culsh_candidates_get_counts": [VP, VP],
     "culsh_candidates_get_offsets": [VP, VP],
     "culsh_candidates_device_ptrs": [VP, PP, PP, PP],
+    "culsh_peer_alloc": [VP, C.c_size_t, PP, C.c_char_p],
+    "culsh_peer_free": [VP, VP],
+    "culsh_peer_open": [VP, C.c_char_p, PP],
+    "culsh_peer_close": [VP, VP],
+    "culsh_device_copy": [VP, VP, VP, C.c_size_t],
     "culsh_host_alloc": [C.c_size_t, PP],
     "culsh_host_free": [VP],
     "culsh_merge_shard_candidates": [VP, I, I, PP, PP, C.POINTER(C.c_int64), PP],

@@ -1262,6 +1262,69 @@ int culsh_host_free(void* p) {
     });
 }
 
+// ---- peer memory ------------------------------------------------------------------------
+int culsh_peer_alloc(culsh_handle* h, size_t bytes, void** dptr, unsigned char handle[64]) {
+    return guarded([&] {
+        if (!h || !dptr || !handle || bytes == 0) fail(CULSH_ERR_INVALID, "bad argument");
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+        DeviceGuard g(h->ctx->device);
+        void* p = nullptr;
+        cudaError_t e = cudaMalloc(&p, bytes);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            fail(CULSH_ERR_ALLOC, "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+        }
+        cudaIpcMemHandle_t ih;
+        e = cudaIpcGetMemHandle(&ih, p);
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            cudaGetLastError();
+            fail(CULSH_ERR_CUDA, "cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+        }
+        std::memcpy(handle, &ih, 64);
+        *dptr = p;
+    });
+}
+
+int culsh_peer_free(culsh_handle* h, void* dptr) {
+    return guarded([&] {
+        if (!h) fail(CULSH_ERR_INVALID, "null handle");
+        DeviceGuard g(h->ctx->device);
+        if (dptr) CU_CHECK(cudaFree(dptr));
+    });
+}
+
+int culsh_peer_open(culsh_handle* h, const unsigned char handle[64], void** dptr) {
+    return guarded([&] {
+        if (!h || !handle || !dptr) fail(CULSH_ERR_INVALID, "bad argument");
+        DeviceGuard g(h->ctx->device);
+        cudaIpcMemHandle_t ih;
+        std::memcpy(&ih, handle, 64);
+        void* p = nullptr;
+        CU_CHECK(cudaIpcOpenMemHandle(&p, ih, cudaIpcMemLazyEnablePeerAccess));
+        *dptr = p;
+    });
+}
+
+int culsh_peer_close(culsh_handle* h, void* dptr) {
+    return guarded([&] {
+        if (!h) fail(CULSH_ERR_INVALID, "null handle");
+        DeviceGuard g(h->ctx->device);
+        if (dptr) CU_CHECK(cudaIpcCloseMemHandle(dptr));
+    });
+}
+
+int culsh_device_copy(culsh_handle* h, void* dst, const void* src, size_t bytes) {
+    return guarded([&] {
+        if (!h) fail(CULSH_ERR_INVALID, "null handle");
+        if (bytes == 0) return;
+        if (!dst || !src) fail(CULSH_ERR_INVALID, "null pointer");
+        DeviceGuard g(h->ctx->device);
+        CU_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, h->ctx->stream));
+        CU_CHECK(cudaStreamSynchronize(h->ctx->stream));
+    });
+}
+
 // ---- shard merge ------------------------------------------------------------------------
 int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
                                  const int32_t* const* shard_indices,
@@ -1299,9 +1362,15 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
         res->total = total;
         if (total) {
             res->indices.alloc(c, total);
-            size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
-            shard_interleave_kernel<<<(unsigned)blocks, 256, 0, s>>>(d_idx.p, d_off.p, d_base.p, n_shards,
-                                                                    n_q, res->offsets.p, res->indices.p);
+            if (total / (uint64_t)n_q >= 512) {  // long lists: a CTA per query
+                size_t blocks = std::min<size_t>((size_t)n_q, (size_t)c->sm_count * 16);
+                shard_interleave_kernel<<<(unsigned)blocks, 256, 0, s>>>(d_idx.p, d_off.p, d_base.p, n_shards,
+                                                                        n_q, res->offsets.p, res->indices.p);
+            } else {
+                size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
+                shard_interleave_small_kernel<<<(unsigned)blocks, 256, 0, s>>>(
+                    d_idx.p, d_off.p, d_base.p, n_shards, n_q, res->offsets.p, res->indices.p);
+            }
             KERNEL_CHECK();
         }
         CU_CHECK(cudaStreamSynchronize(s));
@@ -1377,8 +1446,8 @@ int culsh_merge_shard_candidates_noalloc(culsh_handle* h, int n_shards, int n_q,
         if (total) {
             if (!out_indices) fail(CULSH_ERR_INVALID, "out_indices is null");
             size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
-            shard_interleave_kernel<<<(unsigned)blocks, 256, 0, s>>>(d_idx, d_off, d_base, n_shards, n_q,
-                                                                    out_offsets, out_indices);
+            shard_interleave_small_kernel<<<(unsigned)blocks, 256, 0, s>>>(d_idx, d_off, d_base, n_shards, n_q,
+                                                                          out_offsets, out_indices);
             KERNEL_CHECK();
         }
         CU_CHECK(cudaStreamSynchronize(s));

@@ -801,12 +801,31 @@ __global__ void shard_counts_kernel(const uint64_t* const* __restrict__ shard_of
     counts[q] = c;
 }
 
-// one warp per query: copy each shard's list (shifted to global ids) in shard order
+// one CTA per query (grid-stride): copy each shard's list (shifted to global ids) in shard order
 __global__ void __launch_bounds__(256)
 shard_interleave_kernel(const int32_t* const* __restrict__ shard_indices,
                         const uint64_t* const* __restrict__ shard_offsets,
                         const int64_t* __restrict__ row_base, int n_shards, int n_q,
                         const uint64_t* __restrict__ offsets, int32_t* __restrict__ out) {
+    for (size_t q = blockIdx.x; q < (size_t)n_q; q += gridDim.x) {
+        uint64_t o = offsets[q];
+        for (int r = 0; r < n_shards; ++r) {
+            const uint64_t s = shard_offsets[r][q], e = shard_offsets[r][q + 1];
+            const int32_t* src = shard_indices[r] + s;
+            const int32_t base = (int32_t)row_base[r];
+#pragma unroll 4
+            for (uint64_t i = threadIdx.x; i < e - s; i += blockDim.x) out[o + i] = src[i] + base;
+            o += e - s;
+        }
+    }
+}
+
+// one warp per query, for results with short lists
+__global__ void __launch_bounds__(256)
+shard_interleave_small_kernel(const int32_t* const* __restrict__ shard_indices,
+                              const uint64_t* const* __restrict__ shard_offsets,
+                              const int64_t* __restrict__ row_base, int n_shards, int n_q,
+                              const uint64_t* __restrict__ offsets, int32_t* __restrict__ out) {
     const int lane = threadIdx.x & 31;
     const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const size_t n_warps = ((size_t)gridDim.x * blockDim.x) >> 5;

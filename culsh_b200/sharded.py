@@ -133,19 +133,18 @@ def exchange_by_query(cand, row_base: int, group=None, row_bases: Optional[List[
         bs = [torch.zeros_like(b) for _ in range(world)]
         dist.all_gather(bs, b, group=group)
         row_bases = [int(x.item()) for x in bs]
-    sc = torch.tensor(send_counts, dtype=torch.int64, device=dev)
-    rc = torch.empty_like(sc)
-    dist.all_to_all_single(rc, sc, group=group)
-    recv_counts = [int(x) for x in rc.tolist()]
-    recv_idx = torch.empty(max(1, sum(recv_counts)), dtype=torch.int32, device=dev)
-    dist.all_to_all_single(recv_idx[:sum(recv_counts)], idx, output_split_sizes=recv_counts,
-                           input_split_sizes=send_counts, group=group)
+    # offsets first (small): the last entry of each received slice is that shard's id count for
+    # my queries, so no separate exchange of sizes is needed
     send_off = torch.cat([off[lo:hi + 1] - off[lo] for lo, hi in bounds])
     lo_r, hi_r = bounds[rank]
     my_len = hi_r - lo_r + 1
     recv_off = torch.empty(world * my_len, dtype=torch.int64, device=dev)
     dist.all_to_all_single(recv_off, send_off, output_split_sizes=[my_len] * world,
                            input_split_sizes=[hi - lo + 1 for lo, hi in bounds], group=group)
+    recv_counts = [int(x) for x in recv_off[my_len - 1::my_len].tolist()]
+    recv_idx = torch.empty(max(1, sum(recv_counts)), dtype=torch.int32, device=dev)
+    dist.all_to_all_single(recv_idx[:sum(recv_counts)], idx, output_split_sizes=recv_counts,
+                           input_split_sizes=send_counts, group=group)
     torch.cuda.synchronize()
     idx_ptrs, off_ptrs, start = [], [], 0
     for s in range(world):
@@ -155,3 +154,97 @@ def exchange_by_query(cand, row_base: int, group=None, row_bases: Optional[List[
     merged = _culsh_core.merge_shard_candidates(idx_ptrs, off_ptrs, row_bases, my_len - 1,
                                                 device=dev.index)
     return merged, (lo_r, hi_r)
+
+
+class PeerExchange:
+    """Shard exchange over peer memory: every rank publishes its per-shard CSR in a device buffer
+    that the other processes of the box have mapped (CUDA IPC), and the merge kernel of each
+    rank pulls the lists of ITS query slice straight out of the peers' buffers over NVLink
+    while it interleaves them - transfer and merge are one kernel, there is no staging copy
+    and no collective on the data path.  The process group (any backend) only carries the
+    64-byte handles, two barriers per exchange and the capacity agreement.
+
+    Buffer layout per rank: [n_queries + 1 int64 offsets | padding to 256 B | int32 indices].
+    """
+
+    def __init__(self, group=None, device: Optional[int] = None):
+        import torch.distributed as dist
+        from . import _culsh_core
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.h = _culsh_core.get_handle(device)
+        self.capacity = 0
+        self.local = None      # device address of my buffer
+        self.peers = []        # device addresses of every rank's buffer as mapped here
+
+    def _close(self):
+        import ctypes as C
+        from . import _lib
+        for r, p in enumerate(self.peers):
+            if r != self.rank and p:
+                _lib.check(self.h.lib.culsh_peer_close(self.h.ptr, C.c_void_p(p)))
+        if self.local:
+            _lib.check(self.h.lib.culsh_peer_free(self.h.ptr, C.c_void_p(self.local)))
+        self.peers, self.local, self.capacity = [], None, 0
+
+    def close(self):
+        import torch.distributed as dist
+        dist.barrier(self.group)
+        self._close()
+
+    def _sync_max(self, value: int) -> int:
+        """All-reduce(max) of one integer; doubles as a barrier over the group."""
+        import torch
+        import torch.distributed as dist
+        on_gpu = dist.get_backend(self.group) == "nccl"
+        t = torch.tensor([int(value)], dtype=torch.int64,
+                         device=f"cuda:{self.h.device}" if on_gpu else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return int(t.item())
+
+    def _grow(self, need: int):
+        """Collective (every rank calls it with the same `need`): allocate, export, map."""
+        import ctypes as C
+        import torch.distributed as dist
+        from . import _lib
+        self._close()
+        cap = (int(need * 1.25) + (1 << 21)) >> 21 << 21
+        ptr = C.c_void_p()
+        hbuf = C.create_string_buffer(64)
+        _lib.check(self.h.lib.culsh_peer_alloc(self.h.ptr, cap, C.byref(ptr), hbuf))
+        self.local, self.capacity = ptr.value, cap
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(hbuf.raw), group=self.group)
+        self.peers = []
+        for r, hb in enumerate(handles):
+            if r == self.rank:
+                self.peers.append(self.local)
+            else:
+                q = C.c_void_p()
+                _lib.check(self.h.lib.culsh_peer_open(self.h.ptr, hb, C.byref(q)))
+                self.peers.append(q.value)
+
+    def exchange(self, cand, row_bases: List[int]):
+        """Returns (Candidates of my query slice with global row ids, (q_lo, q_hi))."""
+        import ctypes as C
+        import torch.distributed as dist
+        from . import _culsh_core, _lib
+        nq = cand.n_queries
+        off_bytes = ((nq + 1) * 8 + 255) // 256 * 256
+        # all ranks are past their previous merge once this returns, so the buffers may be reused
+        need = self._sync_max(off_bytes + 4 * cand.n_total_candidates)
+        if need > self.capacity:
+            self._grow(need)
+        ip, _, op = cand.device_pointers()
+        lib, hp = self.h.lib, self.h.ptr
+        _lib.check(lib.culsh_device_copy(hp, C.c_void_p(self.local), C.c_void_p(op), (nq + 1) * 8))
+        if cand.n_total_candidates:
+            _lib.check(lib.culsh_device_copy(hp, C.c_void_p(self.local + off_bytes), C.c_void_p(ip),
+                                             4 * cand.n_total_candidates))
+        self._sync_max(0)             # every rank's buffer is complete
+        lo, hi = shard_bounds(nq, self.world, self.rank)
+        merged = _culsh_core.merge_shard_candidates(
+            [p + off_bytes for p in self.peers], [p + 8 * lo for p in self.peers], row_bases, hi - lo,
+            device=self.h.device)
+        return merged, (lo, hi)

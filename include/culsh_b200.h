@@ -202,6 +202,18 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_queries,
                                  const uint64_t* const* shard_offsets, const int64_t* row_base,
                                  culsh_candidates** out);
 
+/* Peer-memory plumbing for the row-sharded exchange (no upstream counterpart).  A rank exports
+ * a plain device allocation to the other processes of the box; peers map it and the merge
+ * kernel of culsh_merge_shard_candidates then reads their per-shard CSR arrays directly over
+ * NVLink with ordinary loads (no staging copy, no collective library on the data path).
+ * `handle` is the 64-byte cudaIpcMemHandle_t. */
+int culsh_peer_alloc(culsh_handle* h, size_t bytes, void** dptr, unsigned char handle[64]);
+int culsh_peer_free(culsh_handle* h, void* dptr);
+int culsh_peer_open(culsh_handle* h, const unsigned char handle[64], void** dptr);
+int culsh_peer_close(culsh_handle* h, void* dptr);
+/* dst (device, this handle's device) <- src (device) on the handle's stream, then wait. */
+int culsh_device_copy(culsh_handle* h, void* dst, const void* src, size_t bytes);
+
 /* Same merge for callers that must not allocate (no counterpart in the reference).
  *
  * Some hosts of this library cannot call cudaMalloc at the point where shard results are

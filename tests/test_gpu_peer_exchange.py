@@ -1,0 +1,69 @@
+"""Peer-memory shard exchange: two processes share ONE GPU (CUDA IPC works between processes on
+the same device), gloo carries the handles and barriers, and each rank's merge kernel reads
+the other rank's per-shard CSR through the mapped pointer.  The union over both query slices
+must equal the unsharded result."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.cuda.set_device(0)
+        import culsh_b200
+        from culsh_b200 import sharded
+        rng = np.random.RandomState(77)
+        n, d, L, k, nq = 6000, 16, 6, 6, 201
+        X = rng.randn(n, d).astype(np.float32)
+        Q = X[rng.randint(0, n, nq)] + 0.01 * rng.randn(nq, d).astype(np.float32)
+        ex = sharded.PeerExchange(device=0)
+        bases = [sharded.shard_bounds(n, world, r)[0] for r in range(world)]
+        lo, hi = sharded.shard_bounds(n, world, rank)
+        model = culsh_b200.RPLSH(L, k, seed=13).fit(X[lo:hi])
+        for rep, nqq in enumerate((nq, 57)):  # second call reuses the mapped buffers
+            cand = model.query(Q[:nqq])
+            merged, (q_lo, q_hi) = ex.exchange(cand, bases)
+            np.savez(os.path.join(out_dir, f"r{rank}_{rep}.npz"), idx=merged.get_indices(),
+                     off=merged.get_offsets(), q_lo=q_lo, q_hi=q_hi)
+        if rank == 0:
+            whole = culsh_b200.RPLSH(L, k, seed=13).fit(X)
+            for rep, nqq in enumerate((nq, 57)):
+                w = whole.query(Q[:nqq])
+                np.savez(os.path.join(out_dir, f"whole_{rep}.npz"), idx=w.get_indices(), off=w.get_offsets())
+        ex.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_peer_exchange_two_processes_one_gpu(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for rep in range(2):
+        w = np.load(tmp_path / f"whole_{rep}.npz")
+        woff = w["off"].astype(np.int64)
+        for r in range(world):
+            g = np.load(tmp_path / f"r{r}_{rep}.npz")
+            q_lo, q_hi = int(g["q_lo"]), int(g["q_hi"])
+            off = g["off"].astype(np.int64)
+            assert len(off) == q_hi - q_lo + 1
+            assert np.array_equal(off, woff[q_lo:q_hi + 1] - woff[q_lo])
+            assert np.array_equal(g["idx"], w["idx"][woff[q_lo]:woff[q_hi]])
