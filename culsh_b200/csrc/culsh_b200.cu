@@ -464,6 +464,26 @@ int bitmap_window_bits(const CtxPtr& c, int n_rows) {
     return (int)std::min(want, cap);
 }
 
+// Tuning knobs of the chained kernel, read from the environment at every call (tests vary them):
+//   CULSH_CHAIN_BITS    rows per window (default 253,952: bitmap, prefix and stage of three CTAs
+//                       fit one SM); the row range is cut into the fewest such windows, each a
+//                       multiple of 4096 rows
+//   CULSH_CHAIN_STAGE   ids staged in shared memory per copy-out chunk (default 5632)
+//   CULSH_CHAIN_THREADS threads per CTA: 256, 384 (default) or 512
+//   CULSH_CHAIN_SLICES  0 = CTAs search their list slices themselves (default 1: precomputed)
+constexpr int CHAIN_MAX_WINDOWS = 8;
+inline long env_long(const char* name, long dflt) {
+    const char* e = getenv(name);
+    return e && *e ? atol(e) : dflt;
+}
+int chain_window_bits(int n_rows, int* n_win) {
+    const size_t cap_bits = std::max<size_t>(4096, (size_t)env_long("CULSH_CHAIN_BITS", 253952) / 4096 * 4096);
+    const size_t n = (size_t)std::max(n_rows, 1);
+    const size_t wins = ceil_div(n, cap_bits);
+    *n_win = (int)std::min<size_t>(wins, 1u << 20);
+    return (int)(ceil_div(ceil_div(n, wins), (size_t)4096) * 4096);
+}
+
 void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, culsh_candidates& out,
                         StageTimer& tm) {
     const CtxPtr& c = ix.ctx;
@@ -504,9 +524,14 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
         CU_CHECK(cudaStreamSynchronize(s));
         return;
     }
-    // Single pass (ids emitted at their final position, no compaction) when the index fits one
-    // bitmap window and most queries have large candidate sets; otherwise scratch + compaction.
-    const bool chained = (size_t)ix.n <= (size_t)wbits && (size_t)nb * 2 >= (size_t)n_q;
+    // Single pass (ids emitted at their final CSR position, no compaction) when most queries have
+    // large candidate sets and the row range is a few chain windows; otherwise scratch + compaction.
+    int n_win = 1;
+    const int cbits = chain_window_bits(ix.n, &n_win);
+    const int stage_ids = (int)std::min<long>(40960, std::max<long>(256, env_long("CULSH_CHAIN_STAGE", 5632)));
+    const bool chained = n_win <= CHAIN_MAX_WINDOWS && L <= CW_MAX_L && (size_t)nb * 2 >= (size_t)n_q &&
+                         (uint64_t)n_q * (uint64_t)n_win < (1ull << 31) &&
+                         chain_window_smem_bytes(cbits, stage_ids) + 1024 <= c->smem_optin;
     const uint32_t n_other = (uint32_t)n_q - nb - nm;  // queries on the warp path (incl. empty ones)
     Scratch<int32_t> tmp;
     tmp.reserve(c, SL_TMP, raw_total);
@@ -528,29 +553,35 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     }
     if (chained) {
         out.indices.alloc(c, raw_total);  // capacity: the unique total is not known yet
-        Scratch<unsigned long long> status(c, SL_CHAIN, (size_t)n_q + 1);
-        uint32_t* ticket = reinterpret_cast<uint32_t*>(status.p + n_q);
-        CU_CHECK(cudaMemsetAsync(status.p, 0, sizeof(unsigned long long) * ((size_t)n_q + 1), s));
-        size_t smem = bitmap_smem_bytes(wbits);
-        CU_CHECK(cudaFuncSetAttribute(dedupe_chained_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        unsigned long long* phase = nullptr;
-        Scratch<unsigned long long> phase_buf;
-        if (tr.on) {  // CULSH_TRACE: per-phase cycle counts of the kernel (thread 0 of every CTA)
-            phase_buf.reserve(c, SL_MISC0, 16);
-            phase = phase_buf.p;
-            CU_CHECK(cudaMemsetAsync(phase, 0, 16 * sizeof(unsigned long long), s));
+        const size_t n_tk = (size_t)n_q * n_win;
+        Scratch<unsigned long long> status(c, SL_CHAIN, n_tk + 1);
+        uint32_t* ticket = reinterpret_cast<uint32_t*>(status.p + n_tk);
+        CU_CHECK(cudaMemsetAsync(status.p, 0, sizeof(unsigned long long) * (n_tk + 1), s));
+        // list slices per window, precomputed when the table is small enough (<= 256 MB)
+        Scratch<int2> slices;
+        if (env_long("CULSH_CHAIN_SLICES", 1) && n_win > 1 && n_tk * (size_t)L <= ((size_t)32 << 20)) {
+            slices.reserve(c, SL_SLICES, n_tk * (size_t)L);
+            slice_lists_kernel<<<(unsigned)ceil_div((size_t)n_q * L, 256), 256, 0, s>>>(
+                matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, n_q, L, cbits, n_win, mid_max, slices.p);
+            KERNEL_CHECK();
         }
-        dedupe_chained_kernel<<<(unsigned)n_q, BM_THREADS, smem, s>>>(
-            matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, raw_off.p, n_q, L, wbits, mid_max, tmp.p, tmp.p,
-            status.p, ticket, out.indices.p, out.counts.p, out.offsets.p, c->d_error, phase);
+        auto launch = [&](auto nt_tag) {
+            constexpr int NT = decltype(nt_tag)::value;
+            const size_t smem = chain_window_smem_bytes(cbits, stage_ids);
+            CU_CHECK(cudaFuncSetAttribute(dedupe_chained_rank_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CU_CHECK(cudaFuncSetAttribute(dedupe_chained_rank_kernel<NT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+            dedupe_chained_rank_kernel<NT><<<(unsigned)n_tk, NT, smem, s>>>(
+                matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, raw_off.p, n_q, L, ix.n, cbits, n_win, stage_ids,
+                mid_max, slices.p, tmp.p, status.p, ticket, out.indices.p, out.counts.p, out.offsets.p, c->d_error);
+        };
+        const long cw_threads = env_long("CULSH_CHAIN_THREADS", 384);
+        if (cw_threads == 512) launch(std::integral_constant<int, 512>{});
+        else if (cw_threads == 256) launch(std::integral_constant<int, 256>{});
+        else launch(std::integral_constant<int, 384>{});
         KERNEL_CHECK();
-        if (phase) {
-            unsigned long long hc[16];
-            read_words(c, phase, sizeof(hc), hc);
-            fprintf(stderr, "[culsh trace] mark detail cycles/query: prefix %.0f search+load %.0f (+atomics %.0f) tail-sync %.0f\n",
-                    (double)hc[8] / n_q, (double)hc[9] / n_q, (double)hc[10] / n_q, (double)hc[11] / n_q);
-            fprintf(stderr, "[culsh trace] chained kernel cycles/query: setup %.0f clear+mark %.0f count %.0f chain %.0f emit %.0f\n",
-                    (double)hc[0] / n_q, (double)hc[1] / n_q, (double)hc[2] / n_q, (double)hc[3] / n_q, (double)hc[4] / n_q);
+        if (n_win > 1) {
+            counts_from_offsets_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(out.offsets.p, n_q, out.counts.p);
+            KERNEL_CHECK();
         }
         uint64_t total = 0;
         read_words(c, out.offsets.p + n_q, sizeof(uint64_t), &total);

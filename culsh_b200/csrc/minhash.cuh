@@ -16,15 +16,31 @@ constexpr uint32_t MINHASH_PRIME = 4294967291u;  // minhash/hash.cuh:17
 constexpr int MH_THREADS = 256;
 constexpr int MH_MAX_PER_LANE = 8;               // hashes per lane per sweep (H <= 256 in one sweep)
 
-__device__ __forceinline__ uint32_t mod_prime_u64(uint64_t x) {
-    // x = hi*2^32 + lo == hi*5 + lo (mod p); two folds bring it below 2p.
-    uint64_t y = (x >> 32) * 5ull + (x & 0xFFFFFFFFull);        // < 6 * 2^32
-    uint64_t z = (y >> 32) * 5ull + (y & 0xFFFFFFFFull);        // < 2^32 + 25
-    if (z >= MINHASH_PRIME) z -= MINHASH_PRIME;
-    return (uint32_t)z;
+__device__ __forceinline__ uint64_t mad_wide_u32(uint32_t a, uint32_t b, uint64_t c) {
+    uint64_t d;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
+    return d;
+}
+
+// (a*c + b) mod p with p = 2^32 - 5, i.e. 2^32 == 5 (mod p), for a, b < p and c < 2^31.
+// x = a*c + b < 2^63; y = 5*x_hi + x_lo < 3.5 * 2^32 is congruent to x; s = 5*y_hi + y_lo
+// < 2^32 + 15 is congruent too and lies below 2p, so the result is s or s - p.  s >= p exactly
+// when s + 5 carries out of 32 bits, and then (s + 5) mod 2^32 = s - p: one add with a carry
+// test replaces the compare-and-subtract.  b64 is b zero-extended (the caller keeps it in
+// registers across the row).
+__device__ __forceinline__ uint32_t hash_mod_prime(uint32_t a, uint32_t c, uint64_t b64) {
+    const uint64_t x = mad_wide_u32(a, c, b64);
+    const uint64_t y = mad_wide_u32((uint32_t)(x >> 32), 5u, (uint64_t)(uint32_t)x);
+    const uint32_t u = 5u * (uint32_t)(y >> 32) + 5u;   // <= 20
+    const uint32_t t = (uint32_t)y + u;                 // (s + 5) mod 2^32
+    return t < u ? t : t - 5u;                          // carried: s - p; else s
 }
 
 // keys: [L][n_total][NW] with NW = round_key_words(4k); word j (right-aligned) = bswap32(min).
+// PL = hash functions per lane per sweep; a sweep covers 32*PL consecutive hash functions and
+// H > 256 takes several sweeps.  Slots past H hold a = b = 0, evaluate to 0 and are never stored,
+// so the inner loop carries no predicate.
+template <int PL>
 __global__ void __launch_bounds__(MH_THREADS)
 minhash_kernel(const int32_t* __restrict__ indices, const int32_t* __restrict__ indptr,
                const uint32_t* __restrict__ A, const uint32_t* __restrict__ B, int n_rows,
@@ -37,32 +53,28 @@ minhash_kernel(const int32_t* __restrict__ indices, const int32_t* __restrict__ 
 
     for (int row = warp; row < n_rows; row += n_warps) {
         const int start = indptr[row], end = indptr[row + 1];
-        for (int h0 = 0; h0 < H; h0 += 32 * MH_MAX_PER_LANE) {
-            uint32_t a[MH_MAX_PER_LANE], b[MH_MAX_PER_LANE], m[MH_MAX_PER_LANE];
+        for (int h0 = 0; h0 < H; h0 += 32 * PL) {
+            uint32_t a[PL], m[PL];
+            uint64_t b[PL];
 #pragma unroll
-            for (int i = 0; i < MH_MAX_PER_LANE; ++i) {
+            for (int i = 0; i < PL; ++i) {
                 int h = h0 + i * 32 + lane;
                 a[i] = h < H ? A[h] : 0u;
-                b[i] = h < H ? B[h] : 0u;
+                b[i] = h < H ? (uint64_t)B[h] : 0ull;
                 m[i] = 0xFFFFFFFFu;
             }
-            const int n_live = min(MH_MAX_PER_LANE, (H - h0 + 31) / 32);
             for (int base = start; base < end; base += 32) {
-                int mine = base + lane < end ? indices[base + lane] : 0;
-                int cnt = min(32, end - base);
+                const int mine = base + lane < end ? indices[base + lane] : 0;
+                const int cnt = min(32, end - base);
+#pragma unroll 4
                 for (int s = 0; s < cnt; ++s) {
-                    uint32_t c = (uint32_t)__shfl_sync(0xFFFFFFFFu, mine, s);
+                    const uint32_t c = (uint32_t)__shfl_sync(0xFFFFFFFFu, mine, s);
 #pragma unroll
-                    for (int i = 0; i < MH_MAX_PER_LANE; ++i) {
-                        if (i < n_live) {
-                            uint32_t hv = mod_prime_u64((uint64_t)a[i] * c + (uint64_t)b[i]);
-                            m[i] = min(m[i], hv);
-                        }
-                    }
+                    for (int i = 0; i < PL; ++i) m[i] = min(m[i], hash_mod_prime(a[i], c, b[i]));
                 }
             }
 #pragma unroll
-            for (int i = 0; i < MH_MAX_PER_LANE; ++i) {
+            for (int i = 0; i < PL; ++i) {
                 int h = h0 + i * 32 + lane;
                 if (h < H) {
                     int t = h / k, j = h - t * k;
@@ -90,9 +102,20 @@ inline void launch_minhash(const CtxPtr& c, cudaStream_t stream, const int32_t* 
     size_t blocks = ceil_div((size_t)n_rows, warps_per_block);
     size_t cap = (size_t)c->sm_count * 32;
     if (blocks > cap) blocks = cap;
-    minhash_kernel<<<(unsigned)blocks, MH_THREADS, 0, stream>>>(indices, indptr, A, B, n_rows, L, k,
-                                                               ks.key_words, keys, n_total,
-                                                               row_offset);
+    const int H = L * k;
+    const int sweeps = (int)ceil_div(H, 32 * MH_MAX_PER_LANE);
+    const int per_lane = (int)ceil_div(H, 32 * sweeps);  // 1..MH_MAX_PER_LANE
+#define CULSH_MH_CASE(PLV)                                                                      \
+    case PLV:                                                                                   \
+        minhash_kernel<PLV><<<(unsigned)blocks, MH_THREADS, 0, stream>>>(                       \
+            indices, indptr, A, B, n_rows, L, k, ks.key_words, keys, n_total, row_offset);      \
+        break;
+    switch (per_lane) {
+        CULSH_MH_CASE(1) CULSH_MH_CASE(2) CULSH_MH_CASE(3) CULSH_MH_CASE(4)
+        CULSH_MH_CASE(5) CULSH_MH_CASE(6) CULSH_MH_CASE(7) CULSH_MH_CASE(8)
+        default: fail(CULSH_ERR_INTERNAL, "minhash: hashes per lane out of range");
+    }
+#undef CULSH_MH_CASE
     KERNEL_CHECK();
 }
 

@@ -300,12 +300,13 @@ inline size_t bitmap_smem_bytes(int window_bits) {
 // laid end to end (s_pre = exclusive prefix of their lengths) and that flat sequence is cut
 // into equal stretches, one per warp, so the work is balanced however uneven the lists are.
 // Must be called by all BM_THREADS threads; s_lo / s_we must be visible (barrier before).
+template <int NT = BM_THREADS>
 __device__ __forceinline__ void mark_lists_flat(uint32_t* __restrict__ bitmap, const int32_t* __restrict__ cand,
                                                 const int* __restrict__ s_lo, const int* __restrict__ s_we,
                                                 int* __restrict__ s_pre, uint32_t* __restrict__ s_wtot, int Lg,
-                                                int win_lo, long long* dbg = nullptr) {
+                                                int win_lo) {
+    constexpr int NWARP = NT / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    long long t0 = dbg ? clock64() : 0;
     const int len = tid < Lg ? s_we[tid] - s_lo[tid] : 0;
     int inc = len;
 #pragma unroll
@@ -316,19 +317,18 @@ __device__ __forceinline__ void mark_lists_flat(uint32_t* __restrict__ bitmap, c
     if (lane == 31) s_wtot[warp] = (uint32_t)inc;
     __syncthreads();
     int base = 0, total = 0;
-    for (int w = 0; w < BM_WARPS; ++w) {
+    for (int w = 0; w < NWARP; ++w) {
         const int x = (int)s_wtot[w];
         if (w < warp) base += x;
         total += x;
     }
     if (tid < Lg) s_pre[tid] = base + inc - len;
     __syncthreads();
-    if (dbg && tid == 0) { dbg[0] += clock64() - t0; t0 = clock64(); }
     // Each warp takes a contiguous stretch of the flat sequence; a lane's list index only moves
     // forward (one binary search per warp, then cheap advances), loads stay coalesced and MK of
     // them are in flight per lane.
     constexpr int MK = 20;
-    const int per_warp = (((total + BM_WARPS - 1) / BM_WARPS) + 31) & ~31;
+    const int per_warp = (((total + NWARP - 1) / NWARP) + 31) & ~31;
     const int w_begin = warp * per_warp, w_end = min(total, w_begin + per_warp);
     if (w_begin < w_end) {
         int t = 0;
@@ -351,7 +351,6 @@ __device__ __forceinline__ void mark_lists_flat(uint32_t* __restrict__ bitmap, c
                     v[j] = cand[s_lo[t] + (e - s_pre[t])];
                 }
             }
-            if (dbg && tid == 0) dbg[1] += clock64() - t0;
 #pragma unroll
             for (int j = 0; j < MK; ++j) {
                 if (v[j] >= 0) {
@@ -359,11 +358,9 @@ __device__ __forceinline__ void mark_lists_flat(uint32_t* __restrict__ bitmap, c
                     atomicOr(&bitmap[id >> 5], 1u << (id & 31));
                 }
             }
-            if (dbg && tid == 0) { dbg[2] += clock64() - t0; t0 = clock64(); }
         }
     }
     __syncthreads();
-    if (dbg && tid == 0) dbg[3] += clock64() - t0;
 }
 
 __global__ void __launch_bounds__(BM_THREADS)
@@ -491,14 +488,14 @@ dedupe_bitmap_kernel(const uint32_t* __restrict__ big_list, const int32_t* __res
 }
 
 // ---------------------------------------------------------------------------------------
-// Single-pass form of the block path for indexes that fit one bitmap window and query sets
-// dominated by large candidate sets: one CTA per query IN QUERY ORDER (tickets from an atomic
-// counter, so a CTA only ever waits on CTAs that started before it).  After counting its
-// unique ids a CTA publishes the count, obtains the sum over all earlier queries from a
-// chained look-back over `status` (a warp reads 32 predecessors per round), and emits its
-// sorted ids straight at their final CSR position - no scratch copy, no compaction pass.
-// Queries that took the warp / sort paths have their count and ids in `tmp` already; their
-// CTA joins the chain with that count and copies the ids.
+// Chained single-pass dedupe for query sets dominated by large candidate sets: CTAs take
+// (query, window) tickets from an atomic counter IN CSR ORDER, so a CTA only ever waits on CTAs
+// that started before it.  After counting its unique ids a CTA publishes the count, obtains the
+// sum over all earlier tickets from a chained look-back over `status` (a warp reads 32
+// predecessors per round), and writes its sorted ids straight at their final CSR position - no
+// scratch copy, no compaction pass.  Queries that took the warp / sort paths have their count
+// and ids in `tmp` already; their first ticket joins the chain with that count and copies the
+// ids, their other tickets publish zero.
 // status word: bits 62-63 flag (0 empty, 1 own count, 2 inclusive prefix), low 62 bits value.
 // Every wait is bounded; on expiry DEV_ERR_LOOKBACK_TIMEOUT is recorded and the CTA goes on.
 // ---------------------------------------------------------------------------------------
@@ -561,192 +558,296 @@ __device__ __forceinline__ bool chain_exclusive_prefix(unsigned long long* statu
     return true;
 }
 
-__global__ void __launch_bounds__(BM_THREADS)
-dedupe_chained_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
-                      const int32_t* __restrict__ cand, const uint64_t* __restrict__ raw_cnt,
-                      const uint64_t* __restrict__ raw_off, int n_q, int L, int window_bits, int mid_max,
-                      int32_t* scratch /* same buffer as tmp; big queries write and re-read it */,
-                      const int32_t* __restrict__ tmp, unsigned long long* __restrict__ status,
-                      uint32_t* __restrict__ ticket, int32_t* __restrict__ out_indices,
-                      uint64_t* __restrict__ counts, uint64_t* __restrict__ offsets, int* __restrict__ d_error,
-                      unsigned long long* __restrict__ phase_cycles /* optional: 12 accumulators */) {
-    extern __shared__ __align__(16) uint32_t s_dyn[];
-    long long t_phase = phase_cycles ? clock64() : 0;
-    long long dbg_local[4] = {0, 0, 0, 0};
-    auto lap = [&](int k) {
-        if (phase_cycles && threadIdx.x == 0) {
-            long long now = clock64();
-            atomicAdd(&phase_cycles[k], (unsigned long long)(now - t_phase));
-            t_phase = now;
+// ---------------------------------------------------------------------------------------
+// Rank form of the chained kernel.  The row range is cut into n_win windows of window_bits rows
+// and one CTA handles one (query, window) pair, tickets in (query, window) order - the order of
+// the ids in the CSR.  A CTA
+//   1. narrows every bucket list (ascending row ids) to its window with a 32-way warp search,
+//   2. marks the ids of those slices in a shared-memory bitmap,
+//   3. scans the bitmap once: pop-count prefix per 64-bit word and the number of unique ids,
+//      which it publishes to the chain,
+//   4. walks the slices a second time (L2 hits): the rank of an id among the unique ids of the
+//      window is prefix[word] + popc(bits below it), so the id is dropped at stage[rank] in
+//      shared memory - duplicates write the same value to the same slot,
+//   5. resolves its exclusive prefix from the chain and copies the staged ids, now sorted and
+//      unique, to their final CSR position with coalesced stores.
+// Work is proportional to the candidates (two walks) plus one pass over the window, there is no
+// per-bit emission loop and no scratch copy; windows of 32 KB let several CTAs share an SM so the
+// dependent loads of one overlap the work of the others.  A window with more unique ids than the
+// stage holds repeats steps 4-5 per stage-sized chunk of ranks.
+// ---------------------------------------------------------------------------------------
+constexpr int CW_MAX_L = 256;    // lists per query kept in shared memory (<= threads per CTA)
+
+inline size_t chain_window_smem_bytes(int window_bits, int stage_ids) {
+    return (size_t)window_bits / 8 + (size_t)window_bits / 16 + (size_t)stage_ids * sizeof(int32_t) +
+           (3 * CW_MAX_L + 1) * sizeof(int);
+}
+
+// First position p in [lo, hi) with a[p] >= target (hi if there is none).  Called by a full warp.
+__device__ __forceinline__ int warp_lower_bound(const int32_t* __restrict__ a, int lo, int hi, int32_t target,
+                                                int lane) {
+    while (hi - lo > 32) {
+        const int len = hi - lo;
+        const int p = lo + (int)(((long long)(lane + 1) * len) / 33);  // 32 distinct probes inside (lo, hi)
+        const uint32_t below = __ballot_sync(0xFFFFFFFFu, a[p] < target);  // lanes 0..c-1
+        const int c = __popc(below);
+        const int p_prev = __shfl_sync(0xFFFFFFFFu, p, max(c - 1, 0));
+        const int p_next = __shfl_sync(0xFFFFFFFFu, p, min(c, 31));
+        if (c > 0) lo = p_prev + 1;
+        if (c < 32) hi = p_next;
+    }
+    const bool below = lo + lane < hi && a[lo + lane] < target;
+    return lo + __popc(__ballot_sync(0xFFFFFFFFu, below));
+}
+
+// Calls f(id) for every element of the Lg lists [s_lo[t], s_lo[t] + len_t) laid end to end
+// (s_pre[t] = exclusive prefix of the lengths, s_pre[Lg] = total).  The flat sequence is cut into
+// equal stretches, one per warp; lanes read consecutive elements (coalesced), MK loads in flight.
+template <int NT, typename F>
+__device__ __forceinline__ void walk_lists(const int32_t* __restrict__ cand, const int* __restrict__ s_lo,
+                                           const int* __restrict__ s_pre, int Lg, F&& f) {
+    constexpr int NWARP = NT / 32;
+    constexpr int MK = 16;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int total = s_pre[Lg];
+    const int per_warp = (((total + NWARP - 1) / NWARP) + 31) & ~31;
+    const int w_begin = warp * per_warp, w_end = min(total, w_begin + per_warp);
+    if (w_begin >= w_end) return;
+    int t;
+    {
+        int a = 0, b = Lg - 1;
+        while (a < b) {  // largest t with s_pre[t] <= w_begin
+            const int mid = (a + b + 1) >> 1;
+            if (s_pre[mid] <= w_begin) a = mid; else b = mid - 1;
         }
-    };
-    uint32_t* bitmap = s_dyn;                                       // [window_bits / 32]
-    int* s_lo = reinterpret_cast<int*>(bitmap + window_bits / 32);  // [Lc] list start (global position)
-    int* s_hi = s_lo + BM_MAX_L;
-    int* s_we = s_hi + BM_MAX_L;                                    // [Lc] list end
-    int32_t* s_stage = reinterpret_cast<int32_t*>(s_we + BM_MAX_L); // [BM_WARPS][BM_STAGE]
-    __shared__ uint32_t s_wtot[BM_WARPS];
+        t = a;
+    }
+    int next = s_pre[t + 1];            // first flat position past list t
+    int base = s_lo[t] - s_pre[t];      // flat position -> position in cand
+    for (int e0 = w_begin + lane; e0 - lane < w_end; e0 += 32 * MK) {
+        int32_t v[MK];
+#pragma unroll
+        for (int j = 0; j < MK; ++j) {
+            const int e = e0 + 32 * j;
+            v[j] = -1;
+            if (e < w_end) {
+                while (e >= next) {  // e < total, so t stays below Lg
+                    ++t;
+                    next = s_pre[t + 1];
+                    base = s_lo[t] - s_pre[t];
+                }
+                v[j] = cand[base + e];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < MK; ++j)
+            if (v[j] >= 0) f(v[j]);
+    }
+}
+
+// Slice of every bucket list that falls into every window: slices[(q * n_win + w) * L + t] =
+// [a, b) in cand.  One thread per (query, list) walks the windows in order, so each boundary is
+// one binary search from the previous boundary on; with millions of threads in flight the
+// dependent loads cost nothing, whereas inside the chained kernel they would sit on the critical
+// path of every CTA.
+__global__ void __launch_bounds__(256)
+slice_lists_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
+                   const int32_t* __restrict__ cand, const uint64_t* __restrict__ raw_cnt, int n_q, int L,
+                   int window_bits, int n_win, int mid_max, int2* __restrict__ slices) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_q * L) return;
+    const int q = (int)(idx / L), t = (int)(idx - (size_t)q * L);
+    const uint64_t raw = raw_cnt[q];
+    if (!(raw > (uint64_t)SMALL_MAX && raw > (uint64_t)mid_max)) return;  // not a bitmap-path query
+    const int b = matched[idx];
+    int lo = 0, we = 0;
+    if (b >= 0) { lo = bucket_offsets[b]; we = bucket_offsets[b + 1]; }
+    int a = lo;
+    for (int w = 0; w < n_win; ++w) {
+        int e = we;
+        if (w < n_win - 1 && a < we) {
+            const long long bound = (long long)(w + 1) * window_bits;
+            e = bound > 0x7FFFFFFFll ? we : lower_bound_i32(cand, a, we, (int32_t)bound);
+        }
+        slices[((size_t)q * n_win + w) * L + t] = make_int2(a, e);
+        a = e;
+    }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(NT)
+dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
+                           const int32_t* __restrict__ cand, const uint64_t* __restrict__ raw_cnt,
+                           const uint64_t* __restrict__ raw_off, int n_q, int L, int n_rows, int window_bits,
+                           int n_win, int stage_ids, int mid_max, const int2* __restrict__ slices /* or null */,
+                           const int32_t* __restrict__ tmp,
+                           unsigned long long* __restrict__ status, uint32_t* __restrict__ ticket,
+                           int32_t* __restrict__ out_indices, uint64_t* __restrict__ counts,
+                           uint64_t* __restrict__ offsets, int* __restrict__ d_error) {
+    constexpr int NWARP = NT / 32;
+    extern __shared__ __align__(16) uint32_t s_dyn[];
+    const int n64 = window_bits / 64;
+    unsigned long long* bm64 = reinterpret_cast<unsigned long long*>(s_dyn);   // [n64]
+    uint32_t* bm32 = s_dyn;
+    uint32_t* prefix = s_dyn + 2 * n64;                                        // [n64]
+    int32_t* stage = reinterpret_cast<int32_t*>(prefix + n64);                // [stage_ids]
+    int* s_lo = reinterpret_cast<int*>(stage + stage_ids);                    // [L] slice start in cand
+    int* s_we = s_lo + CW_MAX_L;                                               // [L] slice end
+    int* s_pre = s_we + CW_MAX_L;                                              // [L + 1] prefix of slice lengths
+    __shared__ uint32_t s_wtot[NWARP];
     __shared__ unsigned long long s_excl;
-    __shared__ int s_q;
-    __shared__ int s_resolved;
+    __shared__ int s_tk;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) s_q = (int)atomicAdd(ticket, 1u);
+    if (tid == 0) s_tk = (int)atomicAdd(ticket, 1u);
     __syncthreads();
-    const int q = s_q;
-    if (q >= n_q) return;
+    const int tk = s_tk;
+    const long long n_tk = (long long)n_q * n_win;
+    if (tk >= n_tk) return;
+    const int q = tk / n_win, w = tk - q * n_win;
+    const bool last_ticket = tk == n_tk - 1;
     const uint64_t raw = raw_cnt[q];
     const bool big = raw > (uint64_t)SMALL_MAX && raw > (uint64_t)mid_max;
-    lap(0);
-    const int words = window_bits / 32;
-    int32_t* stage = s_stage + warp * BM_STAGE;
 
-    if (!big) {  // count and ids are in tmp already: join the chain, then copy
-        const unsigned long long c = counts[q];
+    if (!big) {  // count and ids are in tmp already: window 0 joins the chain with them and copies
+        if (w > 0 && !last_ticket) {
+            if (tid == 0) *reinterpret_cast<volatile unsigned long long*>(status + tk) = CH_FLAG_AGG;
+            return;
+        }
+        const unsigned long long c = w == 0 ? counts[q] : 0ull;
         if (warp == 0) {
             unsigned long long e;
-            chain_exclusive_prefix(status, q, c, lane, d_error, true, true, e);
+            chain_exclusive_prefix(status, tk, c, lane, d_error, true, true, e);
             if (lane == 0) s_excl = e;
         }
         __syncthreads();
         const unsigned long long excl = s_excl;
         const int32_t* src = tmp + raw_off[q];
-        for (unsigned long long i = tid; i < c; i += BM_THREADS) out_indices[excl + i] = src[i];
+        for (unsigned long long i = tid; i < c; i += NT) out_indices[excl + i] = src[i];
         if (tid == 0) {
-            offsets[q] = excl;
-            if (q == n_q - 1) offsets[n_q] = excl + c;
+            if (w == 0) offsets[q] = excl;
+            if (last_ticket) offsets[n_q] = excl + c;
         }
         return;
     }
 
-    // ---- clear + mark (single window covers every row id) ----
+    const int win_lo = w * window_bits;
+    const int win_hi = min(n_rows, win_lo + window_bits);
+    // ---- 1. clear, list bounds, slices ----
     {
-        uint4* b4 = reinterpret_cast<uint4*>(bitmap);
-        for (int w = tid; w < words / 4; w += BM_THREADS) b4[w] = make_uint4(0, 0, 0, 0);
+        uint4* b4 = reinterpret_cast<uint4*>(s_dyn);
+        for (int i = tid; i < n64 / 2; i += NT) b4[i] = make_uint4(0, 0, 0, 0);
     }
-    for (int g0 = 0; g0 < L; g0 += BM_MAX_L) {
-        const int Lg = min(BM_MAX_L, L - g0);
-        __syncthreads();  // bitmap cleared / previous group's lists consumed
-        for (int t = tid; t < Lg; t += BM_THREADS) {
-            const int b = matched[(size_t)q * L + g0 + t];
+    if (slices) {
+        if (tid < L) {
+            const int2 sl = slices[(size_t)tk * L + tid];
+            s_lo[tid] = sl.x; s_we[tid] = sl.y;
+        }
+    } else {
+        if (tid < L) {
+            const int b = matched[(size_t)q * L + tid];
             int lo = 0, we = 0;
             if (b >= 0) { lo = bucket_offsets[b]; we = bucket_offsets[b + 1]; }
-            s_lo[t] = lo; s_we[t] = we;
+            s_lo[tid] = lo; s_we[tid] = we;
         }
-        __syncthreads();
-        mark_lists_flat(bitmap, cand, s_lo, s_we, s_hi, s_wtot, Lg, 0, phase_cycles ? dbg_local : nullptr);
+        if (n_win > 1) {
+            __syncthreads();
+            for (int t = warp; t < L; t += NWARP) {
+                const int lo = s_lo[t], we = s_we[t];
+                if (lo >= we) continue;
+                int a = lo, b = we;
+                if (w > 0) a = warp_lower_bound(cand, lo, we, win_lo, lane);
+                if (w < n_win - 1) b = warp_lower_bound(cand, a, we, win_hi, lane);
+                if (lane == 0) { s_lo[t] = a; s_we[t] = b; }
+            }
+        }
     }
     __syncthreads();
-    lap(1);
-    if (phase_cycles && threadIdx.x == 0)
-        for (int i = 0; i < 4; ++i) atomicAdd(&phase_cycles[8 + i], (unsigned long long)dbg_local[i]);
-
-    // ---- count ----
-    const uint4* b4 = reinterpret_cast<const uint4*>(bitmap);
-    const int groups = words / 128;
-    const int gpw = (groups + BM_WARPS - 1) / BM_WARPS;
-    const int g_begin = warp * gpw, g_end = min(groups, g_begin + gpw);
-    uint32_t wsum = 0;
-    for (int g = g_begin; g < g_end; ++g) {
-        const uint4 v = b4[g * 32 + lane];
-        wsum += __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xFFFFFFFFu, wsum, o);
-    if (lane == 0) s_wtot[warp] = wsum;
-    __syncthreads();
-    uint32_t wbase = 0, wtotal = 0;
-    for (int i = 0; i < BM_WARPS; ++i) {
-        const uint32_t x = s_wtot[i];
-        if (i < warp) wbase += x;
-        wtotal += x;
-    }
-    lap(2);
-    // One look at the chain without waiting: if the prefix is already known the ids go straight
-    // to their final place; otherwise they go to the scratch slot of this query first, the chain
-    // is resolved after the emission (by then the predecessors have usually published) and the
-    // CTA moves its ids, still hot in L2, to the final place itself.
-    if (warp == 0) {
-        unsigned long long e;
-        const bool ok = chain_exclusive_prefix(status, q, (unsigned long long)wtotal, lane, d_error, true, false, e);
-        if (lane == 0) { s_excl = e; s_resolved = ok ? 1 : 0; }
-    }
-    __syncthreads();
-    lap(3);
-    const bool direct = s_resolved != 0;
-    unsigned long long excl = s_excl;
-    int32_t* out = direct ? out_indices + excl : scratch + raw_off[q];
-    uint32_t out_pos = wbase;
-    uint32_t fill = 0;
-    for (int g = g_begin; g < g_end; ++g) {
-        const uint4 v = b4[g * 32 + lane];
-        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-        const uint32_t c = __popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w);
-        uint32_t inc = c;
+    {   // exclusive prefix of the slice lengths (L <= NT)
+        const int len = tid < L ? s_we[tid] - s_lo[tid] : 0;
+        int inc = len;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            const int x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
             if (lane >= o) inc += x;
         }
-        const uint32_t tot = __shfl_sync(0xFFFFFFFFu, inc, 31);
-        if (tot == 0) continue;
-        const int32_t id0 = (g * 128 + lane * 4) * 32;
-        if (tot > BM_STAGE || fill + tot > BM_STAGE) {
-            __syncwarp();
-            for (uint32_t i = lane; i < fill; i += 32) out[out_pos + i] = stage[i];
-            out_pos += fill;
-            fill = 0;
-            __syncwarp();
-        }
-        if (tot > BM_STAGE) {
-            int32_t* dst = out + out_pos + (inc - c);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t bits = wv[j];
-                while (bits) {
-                    const int b = __ffs(bits) - 1;
-                    bits &= bits - 1;
-                    *dst++ = id0 + j * 32 + b;
-                }
-            }
-            out_pos += tot;
-        } else {
-            int32_t* dst = stage + fill + (inc - c);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t bits = wv[j];
-                while (bits) {
-                    const int b = __ffs(bits) - 1;
-                    bits &= bits - 1;
-                    *dst++ = id0 + j * 32 + b;
-                }
-            }
-            fill += tot;
-        }
+        if (lane == 31) s_wtot[warp] = (uint32_t)inc;
+        __syncthreads();
+        int base = 0;
+        for (int i = 0; i < warp; ++i) base += (int)s_wtot[i];
+        if (tid < L) s_pre[tid] = base + inc - len;
+        if (tid == L - 1) s_pre[L] = base + inc;
     }
-    __syncwarp();
-    for (uint32_t i = lane; i < fill; i += 32) out[out_pos + i] = stage[i];
-    if (!direct) {
-        __syncthreads();  // all ids of this query are in its scratch slot
-        if (warp == 0) {
-            unsigned long long e;
-            chain_exclusive_prefix(status, q, (unsigned long long)wtotal, lane, d_error, false, true, e);
-            if (lane == 0) s_excl = e;
+    __syncthreads();
+    // ---- 2. mark ----
+    walk_lists<NT>(cand, s_lo, s_pre, L, [&](int32_t v) {
+        const uint32_t id = (uint32_t)(v - win_lo);
+        atomicOr(&bm32[id >> 5], 1u << (id & 31));
+    });
+    __syncthreads();
+    // ---- 3. pop-count prefix per 64-bit word; a thread owns a contiguous run of words ----
+    const int per_thread = ((n64 + NT - 1) / NT) | 1;  // odd stride: 64-bit loads of a warp spread over all banks
+    const int i_begin = min(n64, tid * per_thread), i_end = min(n64, i_begin + per_thread);
+    uint32_t mine = 0;
+    for (int i = i_begin; i < i_end; ++i) mine += __popcll(bm64[i]);
+    uint32_t inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += x;
+    }
+    if (lane == 31) s_wtot[warp] = inc;  // safe: every thread passed the barrier after its last read
+    __syncthreads();
+    uint32_t run = inc - mine, wtotal = 0;
+    for (int i = 0; i < NWARP; ++i) {
+        const uint32_t x = s_wtot[i];
+        if (i < warp) run += x;
+        wtotal += x;
+    }
+    for (int i = i_begin; i < i_end; ++i) {
+        prefix[i] = run;
+        run += __popcll(bm64[i]);
+    }
+    // publish the count now; the prefix is resolved after the first chunk has been ranked
+    if (tid == 0 && tk > 0) *reinterpret_cast<volatile unsigned long long*>(status + tk) = CH_FLAG_AGG | wtotal;
+    __syncthreads();
+    // ---- 4 + 5. rank, stage, copy out ----
+    unsigned long long excl = 0;
+    for (uint32_t chunk_lo = 0; chunk_lo == 0 || chunk_lo < wtotal; chunk_lo += (uint32_t)stage_ids) {
+        if (wtotal > 0) {
+            walk_lists<NT>(cand, s_lo, s_pre, L, [&](int32_t v) {
+                const uint32_t id = (uint32_t)(v - win_lo);
+                const unsigned long long below = bm64[id >> 6] & ((1ull << (id & 63)) - 1ull);
+                const uint32_t r = prefix[id >> 6] + (uint32_t)__popcll(below) - chunk_lo;
+                if (r < (uint32_t)stage_ids) stage[r] = v;
+            });
+        }
+        if (chunk_lo == 0) {
+            if (warp == 0) {
+                unsigned long long e;
+                chain_exclusive_prefix(status, tk, (unsigned long long)wtotal, lane, d_error, false, true, e);
+                if (lane == 0) s_excl = e;
+            }
         }
         __syncthreads();
         excl = s_excl;
-        const int32_t* src = scratch + raw_off[q];
-        for (uint32_t i = tid; i < wtotal; i += BM_THREADS) out_indices[excl + i] = src[i];
+        const uint32_t n_chunk = min((uint32_t)stage_ids, wtotal - chunk_lo);
+        int32_t* dst = out_indices + excl + chunk_lo;
+        for (uint32_t i = tid; i < n_chunk; i += NT) dst[i] = stage[i];
+        if (chunk_lo + (uint32_t)stage_ids < wtotal) __syncthreads();  // stage is reused by the next chunk
     }
     if (tid == 0) {
-        counts[q] = wtotal;
-        offsets[q] = excl;
-        if (q == n_q - 1) offsets[n_q] = excl + wtotal;
+        if (w == 0) offsets[q] = excl;
+        if (n_win == 1) counts[q] = wtotal;
+        if (last_ticket) offsets[n_q] = excl + wtotal;
     }
-    if (phase_cycles) {
-        __syncthreads();
-        lap(4);
-    }
+}
+
+// counts[q] = offsets[q + 1] - offsets[q]
+__global__ void counts_from_offsets_kernel(const uint64_t* __restrict__ offsets, int n_q,
+                                           uint64_t* __restrict__ counts) {
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q < n_q) counts[q] = offsets[q + 1] - offsets[q];
 }
 
 // ---------------------------------------------------------------------------------------

@@ -14,6 +14,9 @@
 namespace culsh_b200 {
 
 constexpr int RS_THREADS = 256;
+#ifndef RS_MIN_BLOCKS
+#define RS_MIN_BLOCKS 3
+#endif
 constexpr int RS_WARPS = RS_THREADS / 32;
 
 template <int NW>
@@ -156,7 +159,7 @@ radix_tile_scan_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table) {
 // Pass step 3: stable scatter of one tile on byte `p`.
 // ---------------------------------------------------------------------------------------
 template <int NW, bool FIRST>
-__global__ void __launch_bounds__(RS_THREADS)
+__global__ void __launch_bounds__(RS_THREADS, RS_MIN_BLOCKS)
 radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int n,
                      int tiles_per_table, int p, const uint32_t* __restrict__ tile_off) {

@@ -282,6 +282,40 @@ def test_sort_path_for_mid_sized_sets_on_a_large_index(eng):
     _assert_candidates_equal(m2.query(X[sel[:3]]), oracle.query_index(oracle.fit_index(sig2, 2, 3), sig2[sel[:3]]))
 
 
+@pytest.mark.parametrize("bits,stage,threads,slices", [
+    (None, None, None, None),        # defaults: two windows at this size
+    (8192, 256, 256, 1),             # many windows (falls back to the windowed bitmap kernel)
+    (65536, 256, 256, 1),            # 5 windows, many copy-out chunks, precomputed slices
+    (65536, 300, 512, 0),            # the CTAs search their slices themselves
+    (131072, 40960, 384, 0),         # 3 windows, one chunk
+    (1 << 20, 5632, 384, 1),         # one window
+])
+def test_chained_dedupe_windows_chunks_and_slices(eng, monkeypatch, bits, stage, threads, slices):
+    """Query sets dominated by large candidate sets take the chained single-pass kernel; its window
+    size, stage size, CTA size and slice source must not change the result."""
+    culsh, core_mod = eng
+    for name, v in (("CULSH_CHAIN_BITS", bits), ("CULSH_CHAIN_STAGE", stage), ("CULSH_CHAIN_THREADS", threads),
+                    ("CULSH_CHAIN_SLICES", slices)):
+        if v is None:
+            monkeypatch.delenv(name, raising=False)
+        else:
+            monkeypatch.setenv(name, str(v))
+    rng = np.random.RandomState(33)
+    n, d, L, k = 300_000, 8, 6, 5
+    X = rng.randn(n, d).astype(np.float32)
+    model = culsh.RPLSH(L, k, seed=12).fit(X)
+    core = core_mod.RPLSHCore(L, k, 12)
+    sig = _sig_matrix(core.hash(X, model.index))
+    oidx = oracle.fit_index(sig, L, k)
+    sel = np.concatenate([rng.randint(0, n, 40), [0, n - 1]])
+    Q = X[sel].copy()
+    Q[5] = 1e6 * np.sign(rng.randn(d)).astype(np.float32)  # most likely a rare signature
+    sigq = _sig_matrix(core.hash(Q, model.index))
+    want = oracle.query_index(oidx, sigq)
+    assert (want[2].astype(np.int64) > 20000).mean() > 0.8  # large sets: ~n/32 rows per table
+    _assert_candidates_equal(model.query(Q), want)
+
+
 def test_no_match_and_zero_queries(eng):
     culsh, _ = eng
     rng = np.random.RandomState(3)
