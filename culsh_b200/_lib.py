@@ -27,7 +27,7 @@ class Stats(C.Structure):
     _fields_ = [
         ("hash_ms", C.c_float), ("sort_ms", C.c_float), ("build_ms", C.c_float),
         ("lookup_ms", C.c_float), ("gather_ms", C.c_float), ("total_ms", C.c_float),
-        ("scatter_ms", C.c_float), ("reserved0", C.c_float),
+        ("scatter_ms", C.c_float), ("dedupe_ms", C.c_float),
         ("n_items", C.c_uint64), ("n_buckets", C.c_uint64), ("raw_candidates", C.c_uint64),
         ("unique_candidates", C.c_uint64),
         ("sort_passes", C.c_int32), ("key_words", C.c_int32), ("elem_bytes", C.c_int32),

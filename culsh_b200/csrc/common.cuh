@@ -150,6 +150,7 @@ struct Ctx {
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t ev[8] = {};
     cudaEvent_t ev_pass[2] = {};      // around the scatter launch of the last radix pass
+    cudaEvent_t ev_dedupe[2] = {};    // around the chained / bitmap dedupe launch of the last query batch
     cudaEvent_t copy_done[2] = {};
     cudaEvent_t chunk_free[2] = {};
     uint64_t* pinned = nullptr;       // 64 x u64 words of pinned host memory
@@ -165,6 +166,7 @@ struct Ctx {
         if (stream) cudaStreamSynchronize(stream);
         for (auto& e : ev) if (e) cudaEventDestroy(e);
         for (auto& e : ev_pass) if (e) cudaEventDestroy(e);
+        for (auto& e : ev_dedupe) if (e) cudaEventDestroy(e);
         for (auto& e : copy_done) if (e) cudaEventDestroy(e);
         for (auto& e : chunk_free) if (e) cudaEventDestroy(e);
         if (copy_stream) cudaStreamSynchronize(copy_stream);

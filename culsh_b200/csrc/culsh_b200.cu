@@ -490,6 +490,7 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     cudaStream_t s = c->stream;
     const int L = ix.L;
     HostTrace tr;
+    bool dedupe_timed = false;
     out.ctx = c;
     out.n_queries = n_q;
     out.counts.alloc(c, (size_t)n_q);
@@ -561,7 +562,7 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
         Scratch<int2> slices;
         if (env_long("CULSH_CHAIN_SLICES", 1) && n_win > 1 && n_tk * (size_t)L <= ((size_t)32 << 20)) {
             slices.reserve(c, SL_SLICES, n_tk * (size_t)L);
-            slice_lists_kernel<<<(unsigned)ceil_div((size_t)n_q * L, 256), 256, 0, s>>>(
+            slice_lists_kernel<<<(unsigned)ceil_div(n_tk * (size_t)L, 256), 256, 0, s>>>(
                 matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, n_q, L, cbits, n_win, mid_max, slices.p);
             KERNEL_CHECK();
         }
@@ -575,10 +576,12 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
                 mid_max, slices.p, tmp.p, status.p, ticket, out.indices.p, out.counts.p, out.offsets.p, c->d_error);
         };
         const long cw_threads = env_long("CULSH_CHAIN_THREADS", 384);
+        if (c->profiling) cudaEventRecord(c->ev_dedupe[0], s);
         if (cw_threads == 512) launch(std::integral_constant<int, 512>{});
         else if (cw_threads == 256) launch(std::integral_constant<int, 256>{});
         else launch(std::integral_constant<int, 384>{});
         KERNEL_CHECK();
+        if (c->profiling) { cudaEventRecord(c->ev_dedupe[1], s); dedupe_timed = true; }
         if (n_win > 1) {
             counts_from_offsets_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(out.offsets.p, n_q, out.counts.p);
             KERNEL_CHECK();
@@ -599,10 +602,12 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
         if (nb) {
             size_t smem = bitmap_smem_bytes(wbits);
             CU_CHECK(cudaFuncSetAttribute(dedupe_bitmap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (c->profiling) cudaEventRecord(c->ev_dedupe[0], s);
             dedupe_bitmap_kernel<<<nb, BM_THREADS, smem, s>>>(big_list.p, matched, ix.bucket_offsets.p,
                                                               ix.cand.p, raw_off.p, L, ix.n, wbits, tmp.p,
                                                               out.counts.p);
             KERNEL_CHECK();
+            if (c->profiling) { cudaEventRecord(c->ev_dedupe[1], s); dedupe_timed = true; }
         }
         exclusive_scan<uint64_t, uint64_t>(s, out.counts.p, n_q, out.offsets.p, scratch.p);
         uint64_t total = 0;
@@ -631,6 +636,11 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     }
     tm.mark();
     CU_CHECK(cudaStreamSynchronize(s));
+    if (dedupe_timed) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, c->ev_dedupe[0], c->ev_dedupe[1]);
+        c->stats.dedupe_ms += ms;
+    }
     tr.lap("compact+sync");
 }
 
@@ -839,6 +849,7 @@ int culsh_create(int device, culsh_handle** out) {
         CU_CHECK(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
         for (auto& e : c->ev) CU_CHECK(cudaEventCreate(&e));
         for (auto& e : c->ev_pass) CU_CHECK(cudaEventCreate(&e));
+        for (auto& e : c->ev_dedupe) CU_CHECK(cudaEventCreate(&e));
         for (auto& e : c->copy_done) CU_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         for (auto& e : c->chunk_free) CU_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         CU_CHECK(cudaMallocHost(&c->pinned, 64 * sizeof(uint64_t)));
@@ -1368,6 +1379,7 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
         DeviceGuard g(h->ctx->device);
         const CtxPtr& c = h->ctx;
         cudaStream_t s = c->stream;
+        HostTrace tr;
         auto res = std::make_unique<culsh_candidates>();
         if (n_q == 0) {
             empty_result(c, *res);
@@ -1390,11 +1402,13 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
         exclusive_scan<uint64_t, uint64_t>(s, res->counts.p, n_q, res->offsets.p, scratch.p);
         uint64_t total = 0;
         read_words(c, res->offsets.p + n_q, sizeof(uint64_t), &total);
+        tr.lap("merge: tables+counts+scan+sync");
         res->total = total;
         if (total) {
             res->indices.alloc(c, total);
+            tr.lap("merge: alloc indices");
             if (total / (uint64_t)n_q >= 512) {  // long lists: a CTA per query
-                size_t blocks = std::min<size_t>((size_t)n_q, (size_t)c->sm_count * 16);
+                size_t blocks = std::min<size_t>((size_t)n_q, (size_t)c->sm_count * 8);
                 shard_interleave_kernel<<<(unsigned)blocks, 256, 0, s>>>(d_idx.p, d_off.p, d_base.p, n_shards,
                                                                         n_q, res->offsets.p, res->indices.p);
             } else {
@@ -1405,6 +1419,7 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
             KERNEL_CHECK();
         }
         CU_CHECK(cudaStreamSynchronize(s));
+        tr.lap("merge: interleave+sync");
         *out = res.release();
     });
 }

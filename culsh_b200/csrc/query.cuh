@@ -646,32 +646,34 @@ __device__ __forceinline__ void walk_lists(const int32_t* __restrict__ cand, con
 }
 
 // Slice of every bucket list that falls into every window: slices[(q * n_win + w) * L + t] =
-// [a, b) in cand.  One thread per (query, list) walks the windows in order, so each boundary is
-// one binary search from the previous boundary on; with millions of threads in flight the
-// dependent loads cost nothing, whereas inside the chained kernel they would sit on the critical
-// path of every CTA.
+// [a, b) in cand.  One thread per (query, list, window) finds the window's lower boundary with a
+// binary search and writes it as the start of its own slice and the end of the previous one;
+// with a million independent searches in flight the dependent loads cost nothing, whereas
+// inside the chained kernel they would sit on the critical path of every CTA.
 __global__ void __launch_bounds__(256)
 slice_lists_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
                    const int32_t* __restrict__ cand, const uint64_t* __restrict__ raw_cnt, int n_q, int L,
                    int window_bits, int n_win, int mid_max, int2* __restrict__ slices) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)n_q * L) return;
-    const int q = (int)(idx / L), t = (int)(idx - (size_t)q * L);
+    if (idx >= (size_t)n_q * L * n_win) return;
+    const int w = (int)(idx % n_win);
+    const size_t pair = idx / n_win;  // q * L + t
+    const int q = (int)(pair / L), t = (int)(pair - (size_t)q * L);
     const uint64_t raw = raw_cnt[q];
     if (!(raw > (uint64_t)SMALL_MAX && raw > (uint64_t)mid_max)) return;  // not a bitmap-path query
-    const int b = matched[idx];
+    const int b = matched[pair];
     int lo = 0, we = 0;
     if (b >= 0) { lo = bucket_offsets[b]; we = bucket_offsets[b + 1]; }
+    int* flat = reinterpret_cast<int*>(slices);
+    const size_t mine = (((size_t)q * n_win + w) * L + t) * 2;
     int a = lo;
-    for (int w = 0; w < n_win; ++w) {
-        int e = we;
-        if (w < n_win - 1 && a < we) {
-            const long long bound = (long long)(w + 1) * window_bits;
-            e = bound > 0x7FFFFFFFll ? we : lower_bound_i32(cand, a, we, (int32_t)bound);
-        }
-        slices[((size_t)q * n_win + w) * L + t] = make_int2(a, e);
-        a = e;
+    if (w > 0) {
+        const long long bound = (long long)w * window_bits;
+        a = bound > 0x7FFFFFFFll ? we : lower_bound_i32(cand, lo, we, (int32_t)bound);
+        flat[mine - (size_t)L * 2 + 1] = a;  // end of the previous window's slice
     }
+    flat[mine] = a;
+    if (w == n_win - 1) flat[mine + 1] = we;
 }
 
 template <int NT>
@@ -902,21 +904,68 @@ __global__ void shard_counts_kernel(const uint64_t* const* __restrict__ shard_of
     counts[q] = c;
 }
 
-// one CTA per query (grid-stride): copy each shard's list (shifted to global ids) in shard order
+// One CTA per query (grid-stride): the shards' lists, shifted to global ids, in shard order.  The
+// shard buffers may be peer memory, so the per-shard offsets of a query are fetched by one thread
+// each (one round trip instead of one per shard), and the lists are copied as one flat sequence
+// with eight independent loads in flight per thread to cover the link latency.
+constexpr int SI_GROUP = 64;   // shards handled per sweep
+constexpr int SI_UNROLL = 8;
 __global__ void __launch_bounds__(256)
 shard_interleave_kernel(const int32_t* const* __restrict__ shard_indices,
                         const uint64_t* const* __restrict__ shard_offsets,
                         const int64_t* __restrict__ row_base, int n_shards, int n_q,
                         const uint64_t* __restrict__ offsets, int32_t* __restrict__ out) {
+    __shared__ const int32_t* s_src[SI_GROUP];   // shard list of this query, already at its start
+    __shared__ uint64_t s_pre[SI_GROUP + 1];     // exclusive prefix of the list lengths
+    __shared__ int32_t s_base[SI_GROUP];
+    const int tid = threadIdx.x;
     for (size_t q = blockIdx.x; q < (size_t)n_q; q += gridDim.x) {
         uint64_t o = offsets[q];
-        for (int r = 0; r < n_shards; ++r) {
-            const uint64_t s = shard_offsets[r][q], e = shard_offsets[r][q + 1];
-            const int32_t* src = shard_indices[r] + s;
-            const int32_t base = (int32_t)row_base[r];
-#pragma unroll 4
-            for (uint64_t i = threadIdx.x; i < e - s; i += blockDim.x) out[o + i] = src[i] + base;
-            o += e - s;
+        for (int g0 = 0; g0 < n_shards; g0 += SI_GROUP) {
+            const int G = min(SI_GROUP, n_shards - g0);
+            __syncthreads();  // the previous sweep is done with the tables
+            if (tid < G) {
+                const uint64_t* po = shard_offsets[g0 + tid];
+                const uint64_t s = po[q], e = po[q + 1];
+                s_src[tid] = shard_indices[g0 + tid] + s;
+                s_pre[tid + 1] = e - s;  // length for now
+                s_base[tid] = (int32_t)row_base[g0 + tid];
+            }
+            __syncthreads();
+            if (tid == 0) {
+                uint64_t run = 0;
+                for (int r = 0; r < G; ++r) {
+                    const uint64_t len = s_pre[r + 1];
+                    s_pre[r] = run;
+                    run += len;
+                }
+                s_pre[G] = run;
+            }
+            __syncthreads();
+            const uint64_t total = s_pre[G];
+            int r = 0;
+            for (uint64_t i0 = tid; i0 < total; i0 += 256 * SI_UNROLL) {
+                // the loaded value is not touched before all loads are issued: an add right after
+                // the load would make every load wait for the one before it
+                int32_t v[SI_UNROLL], shift[SI_UNROLL];
+#pragma unroll
+                for (int j = 0; j < SI_UNROLL; ++j) {
+                    const uint64_t i = i0 + 256 * j;
+                    v[j] = 0;
+                    shift[j] = 0;
+                    if (i < total) {
+                        while (i >= s_pre[r + 1]) ++r;  // i < total keeps r below G
+                        shift[j] = s_base[r];
+                        v[j] = s_src[r][i - s_pre[r]];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < SI_UNROLL; ++j) {
+                    const uint64_t i = i0 + 256 * j;
+                    if (i < total) out[o + i] = v[j] + shift[j];
+                }
+            }
+            o += total;
         }
     }
 }

@@ -159,7 +159,7 @@ radix_tile_scan_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table) {
 // Pass step 3: stable scatter of one tile on byte `p`.
 // ---------------------------------------------------------------------------------------
 template <int NW, bool FIRST>
-__global__ void __launch_bounds__(RS_THREADS, RS_MIN_BLOCKS)
+__global__ void __launch_bounds__(RS_THREADS, (NW == 1 ? 4 : RS_MIN_BLOCKS))
 radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int n,
                      int tiles_per_table, int p, const uint32_t* __restrict__ tile_off) {
@@ -209,7 +209,22 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
         const int li = warp * (32 * IPT) + i * 32 + lane;
         const bool valid = li < count;
         const uint32_t d = valid ? key_digit<NW>(key[i], p) : 0x100u;
-        const uint32_t peers = __match_any_sync(0xFFFFFFFFu, d);
+        // lanes with the same digit.  For one-word keys the kernel is bound by the latency of the
+        // shared-memory / match pipeline, and nine ballots (digit bits + validity) are cheaper
+        // than match.any; wider keys are bandwidth-bound and take the shorter instruction.
+        uint32_t peers;
+        if constexpr (NW == 1) {
+            peers = count == TILE ? 0xFFFFFFFFu : __ballot_sync(0xFFFFFFFFu, valid);
+            if (!valid) peers = ~peers;
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                const bool bit = (d >> b) & 1u;
+                const uint32_t m = __ballot_sync(0xFFFFFFFFu, bit);
+                peers &= bit ? m : ~m;
+            }
+        } else {
+            peers = __match_any_sync(0xFFFFFFFFu, d);
+        }
         const int leader = __ffs(peers) - 1;
         const uint32_t below = __popc(peers & ((1u << lane) - 1));
         uint32_t old = 0;

@@ -162,10 +162,15 @@ class PeerExchange:
     rank pulls the lists of ITS query slice straight out of the peers' buffers over NVLink
     while it interleaves them - transfer and merge are one kernel, there is no staging copy
     and no collective on the data path.  The process group (any backend) only carries the
-    64-byte handles, two barriers per exchange and the capacity agreement.
+    64-byte handles and one one-word all-reduce per exchange (barrier + capacity agreement).
 
-    Buffer layout per rank: [n_queries + 1 int64 offsets | padding to 256 B | int32 indices].
+    Every rank's buffer has two halves used alternately, so a rank may publish its next result
+    while a slower peer is still reading the previous one; a peer has always finished reading a
+    half before it joins the barrier of the following exchange, after which that half is free.
+    Layout of a half: [n_queries + 1 int64 offsets | padding to 256 B | int32 indices].
     """
+
+    GROW_ALIGN = 1 << 21   # buffer halves grow to 1.25x the need, rounded up to this many bytes
 
     def __init__(self, group=None, device: Optional[int] = None):
         import torch.distributed as dist
@@ -174,8 +179,9 @@ class PeerExchange:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.h = _culsh_core.get_handle(device)
-        self.capacity = 0
-        self.local = None      # device address of my buffer
+        self.capacity = 0      # bytes per half
+        self.phase = 0         # half used by the next exchange
+        self.local = None      # device address of my buffer (two halves)
         self.peers = []        # device addresses of every rank's buffer as mapped here
 
     def _close(self):
@@ -209,10 +215,11 @@ class PeerExchange:
         import torch.distributed as dist
         from . import _lib
         self._close()
-        cap = (int(need * 1.25) + (1 << 21)) >> 21 << 21
+        a = self.GROW_ALIGN
+        cap = (int(need * 1.25) + a) // a * a
         ptr = C.c_void_p()
         hbuf = C.create_string_buffer(64)
-        _lib.check(self.h.lib.culsh_peer_alloc(self.h.ptr, cap, C.byref(ptr), hbuf))
+        _lib.check(self.h.lib.culsh_peer_alloc(self.h.ptr, 2 * cap, C.byref(ptr), hbuf))
         self.local, self.capacity = ptr.value, cap
         handles = [None] * self.world
         dist.all_gather_object(handles, bytes(hbuf.raw), group=self.group)
@@ -232,19 +239,28 @@ class PeerExchange:
         from . import _culsh_core, _lib
         nq = cand.n_queries
         off_bytes = ((nq + 1) * 8 + 255) // 256 * 256
-        # all ranks are past their previous merge once this returns, so the buffers may be reused
-        need = self._sync_max(off_bytes + 4 * cand.n_total_candidates)
-        if need > self.capacity:
-            self._grow(need)
         ip, _, op = cand.device_pointers()
         lib, hp = self.h.lib, self.h.ptr
-        _lib.check(lib.culsh_device_copy(hp, C.c_void_p(self.local), C.c_void_p(op), (nq + 1) * 8))
-        if cand.n_total_candidates:
-            _lib.check(lib.culsh_device_copy(hp, C.c_void_p(self.local + off_bytes), C.c_void_p(ip),
-                                             4 * cand.n_total_candidates))
-        self._sync_max(0)             # every rank's buffer is complete
+
+        def publish():
+            base = self.local + self.phase * self.capacity
+            _lib.check(lib.culsh_device_copy(hp, C.c_void_p(base), C.c_void_p(op), (nq + 1) * 8))
+            if cand.n_total_candidates:
+                _lib.check(lib.culsh_device_copy(hp, C.c_void_p(base + off_bytes), C.c_void_p(ip),
+                                                 4 * cand.n_total_candidates))
+
+        mine = off_bytes + 4 * cand.n_total_candidates
+        if mine <= self.capacity:
+            publish()
+        need = self._sync_max(mine)   # barrier: if nobody has to grow, every rank's half is complete
+        if need > self.capacity:      # same decision on every rank
+            self._grow(need)
+            publish()
+            self._sync_max(0)
+        shift = self.phase * self.capacity
         lo, hi = shard_bounds(nq, self.world, self.rank)
         merged = _culsh_core.merge_shard_candidates(
-            [p + off_bytes for p in self.peers], [p + 8 * lo for p in self.peers], row_bases, hi - lo,
-            device=self.h.device)
+            [p + shift + off_bytes for p in self.peers], [p + shift + 8 * lo for p in self.peers], row_bases,
+            hi - lo, device=self.h.device)
+        self.phase ^= 1
         return merged, (lo, hi)

@@ -73,7 +73,7 @@ typedef struct culsh_index_meta {
 typedef struct culsh_stats {
     float hash_ms, sort_ms, build_ms, lookup_ms, gather_ms, total_ms;
     float scatter_ms; /* the scatter launch of the last radix pass alone */
-    float reserved0;
+    float dedupe_ms;  /* the dedupe launch (chained or bitmap kernel) of the query batches alone */
     uint64_t n_items, n_buckets, raw_candidates, unique_candidates;
     int32_t sort_passes, key_words, elem_bytes, hash_path; /* hash_path: 0 SIMT, 1 tcgen05 */
     int32_t launches;  /* kernels of this library launched by the call */

@@ -31,20 +31,22 @@ def _worker(rank, world, port, out_dir):
         from culsh_b200 import sharded
         rng = np.random.RandomState(77)
         n, d, L, k, nq = 6000, 16, 6, 6, 201
+        reps = (57, nq, 33, nq)  # both halves of the buffer are reused; the second call has to grow it
         X = rng.randn(n, d).astype(np.float32)
         Q = X[rng.randint(0, n, nq)] + 0.01 * rng.randn(nq, d).astype(np.float32)
+        sharded.PeerExchange.GROW_ALIGN = 256  # small results must still outgrow the first buffer
         ex = sharded.PeerExchange(device=0)
         bases = [sharded.shard_bounds(n, world, r)[0] for r in range(world)]
         lo, hi = sharded.shard_bounds(n, world, rank)
         model = culsh_b200.RPLSH(L, k, seed=13).fit(X[lo:hi])
-        for rep, nqq in enumerate((nq, 57)):  # second call reuses the mapped buffers
+        for rep, nqq in enumerate(reps):
             cand = model.query(Q[:nqq])
             merged, (q_lo, q_hi) = ex.exchange(cand, bases)
             np.savez(os.path.join(out_dir, f"r{rank}_{rep}.npz"), idx=merged.get_indices(),
                      off=merged.get_offsets(), q_lo=q_lo, q_hi=q_hi)
         if rank == 0:
             whole = culsh_b200.RPLSH(L, k, seed=13).fit(X)
-            for rep, nqq in enumerate((nq, 57)):
+            for rep, nqq in enumerate(reps):
                 w = whole.query(Q[:nqq])
                 np.savez(os.path.join(out_dir, f"whole_{rep}.npz"), idx=w.get_indices(), off=w.get_offsets())
         ex.close()
@@ -57,7 +59,7 @@ def test_peer_exchange_two_processes_one_gpu(tmp_path):
     import torch.multiprocessing as mp
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    for rep in range(2):
+    for rep in range(4):
         w = np.load(tmp_path / f"whole_{rep}.npz")
         woff = w["off"].astype(np.int64)
         for r in range(world):
