@@ -264,3 +264,54 @@ class PeerExchange:
             hi - lo, device=self.h.device)
         self.phase ^= 1
         return merged, (lo, hi)
+
+
+def all_gather_rows(X, group=None):
+    """Every rank's row block, concatenated in rank order, on every rank.
+
+    NumPy arrays travel as objects (any backend); torch tensors are padded to the longest block
+    and gathered with one all_gather_into_tensor on their own device (NCCL for CUDA tensors).
+    Returns (X_all, rows_per_rank).
+    """
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    if isinstance(X, np.ndarray):
+        parts = [None] * world
+        dist.all_gather_object(parts, X, group=group)
+        return np.concatenate(parts, axis=0), [int(p.shape[0]) for p in parts]
+    rows = [None] * world
+    dist.all_gather_object(rows, int(X.shape[0]), group=group)
+    longest = max(rows)
+    block = X if X.shape[0] == longest else torch.cat(
+        [X, X.new_zeros((longest - X.shape[0],) + tuple(X.shape[1:]))])
+    out = X.new_empty((world * longest,) + tuple(X.shape[1:]))
+    dist.all_gather_into_tensor(out, block.contiguous(), group=group)
+    if all(r == longest for r in rows):
+        return out, rows
+    return torch.cat([out[j * longest:j * longest + r] for j, r in enumerate(rows)]), rows
+
+
+def fit_query_sharded(estimator, X_local, exchange: "PeerExchange", batch_size: Optional[int] = None,
+                      group=None):
+    """Self-join over a row-sharded data set (upstream: single-GPU fit_query, core/fit_query.cuh:30-55).
+
+    `estimator` is an unfitted RPLSH / PStableLSH object built with the same arguments (seed
+    included) on every rank; `X_local` is this rank's row block (blocks in rank order form the
+    data set, every block as long as the first except possibly the last ones, as shard_bounds
+    cuts them).  Every rank fits its block, all blocks are gathered so that every rank can ask
+    its shard for the neighbours of EVERY row, and the peer exchange hands each rank the merged
+    candidate lists of its own rows with global row ids.  Returns (Candidates, (row_lo, row_hi)).
+    """
+    model = estimator.fit(X_local)
+    X_all, rows = all_gather_rows(X_local, group)
+    bases = [0]
+    for r in rows[:-1]:
+        bases.append(bases[-1] + r)
+    cand = model.query(X_all, batch_size=batch_size)
+    merged, (lo, hi) = exchange.exchange(cand, bases)
+    me = exchange.rank
+    if (lo, hi) != (bases[me], bases[me] + rows[me]):
+        raise ValueError("row blocks must be cut as shard_bounds(n_rows, world, rank) cuts them")
+    return merged, (lo, hi)

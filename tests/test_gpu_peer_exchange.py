@@ -49,6 +49,14 @@ def _worker(rank, world, port, out_dir):
             for rep, nqq in enumerate(reps):
                 w = whole.query(Q[:nqq])
                 np.savez(os.path.join(out_dir, f"whole_{rep}.npz"), idx=w.get_indices(), off=w.get_offsets())
+        # sharded self-join: every rank ends with the fit_query lists of its own rows
+        est = culsh_b200.PStableLSH(5, 3, window_size=2, seed=4)
+        fq, (r_lo, r_hi) = sharded.fit_query_sharded(est, X[lo:hi], ex, batch_size=1500)
+        np.savez(os.path.join(out_dir, f"fq{rank}.npz"), idx=fq.get_indices(), off=fq.get_offsets(),
+                 r_lo=r_lo, r_hi=r_hi)
+        if rank == 0:
+            w = culsh_b200.PStableLSH(5, 3, window_size=2, seed=4).fit_query(X)
+            np.savez(os.path.join(out_dir, "fq_whole.npz"), idx=w.get_indices(), off=w.get_offsets())
         ex.close()
     finally:
         dist.destroy_process_group()
@@ -69,3 +77,14 @@ def test_peer_exchange_two_processes_one_gpu(tmp_path):
             assert len(off) == q_hi - q_lo + 1
             assert np.array_equal(off, woff[q_lo:q_hi + 1] - woff[q_lo])
             assert np.array_equal(g["idx"], w["idx"][woff[q_lo]:woff[q_hi]])
+    w = np.load(tmp_path / "fq_whole.npz")
+    woff = w["off"].astype(np.int64)
+    covered = 0
+    for r in range(world):
+        g = np.load(tmp_path / f"fq{r}.npz")
+        r_lo, r_hi = int(g["r_lo"]), int(g["r_hi"])
+        assert r_lo == covered
+        covered = r_hi
+        assert np.array_equal(g["off"].astype(np.int64), woff[r_lo:r_hi + 1] - woff[r_lo])
+        assert np.array_equal(g["idx"], w["idx"][woff[r_lo]:woff[r_hi]])
+    assert covered == len(woff) - 1

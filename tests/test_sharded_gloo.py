@@ -64,3 +64,27 @@ def test_two_rank_exchange_and_union(tmp_path):
     out = str(tmp_path / "result.txt")
     mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     assert open(out).read() == "ok"
+
+
+def _gather_worker(rank, world, port, out_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n, d = 11, 3  # ragged: 6 rows on rank 0, 5 on rank 1
+        X = np.arange(n * d, dtype=np.float32).reshape(n, d)
+        lo, hi = sharded.shard_bounds(n, world, rank)
+        a, rows_a = sharded.all_gather_rows(X[lo:hi])
+        b, rows_b = sharded.all_gather_rows(torch.from_numpy(X[lo:hi].copy()))
+        ok = (np.array_equal(a, X) and np.array_equal(b.numpy(), X) and rows_a == rows_b == [6, 5])
+        with open(f"{out_path}.{rank}", "w") as f:
+            f.write("ok" if ok else "mismatch")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_all_gather_rows_numpy_and_tensor_ragged(tmp_path):
+    out = str(tmp_path / "gather")
+    mp.spawn(_gather_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert open(out + ".0").read() == "ok" and open(out + ".1").read() == "ok"
