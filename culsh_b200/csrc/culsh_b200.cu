@@ -380,12 +380,20 @@ int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_buck
     ix.bucket_keys.alloc(c, (size_t)B * NW);
     ix.bucket_offsets.alloc(c, (size_t)B + 1);
     ix.table_offsets.alloc(c, (size_t)L + 1);
-    if (item_to_bucket) item_to_bucket->reserve(c, SL_I2B, (size_t)n * L);
+    Scratch<int32_t> i2b_tm;  // (table, row) -> bucket, transposed to (row, table) below
+    if (item_to_bucket) {
+        item_to_bucket->reserve(c, SL_I2B, (size_t)n * L);
+        i2b_tm.reserve(c, SL_I2B_TM, (size_t)n * L);
+    }
     tr.lap("alloc bucket arrays");
     CULSH_DISPATCH_NW(NW, launch_bucket_write<NW>(c->stream, kp[cur], vp[cur], n, L, tile_base.p,
                                                   ix.bucket_keys.p, ix.bucket_offsets.p,
-                                                  ix.table_offsets.p,
-                                                  item_to_bucket ? item_to_bucket->p : nullptr));
+                                                  ix.table_offsets.p, i2b_tm.p));
+    if (item_to_bucket) {
+        dim3 grid((unsigned)ceil_div(n, 32), (unsigned)ceil_div(L, 32));
+        transpose_table_major_kernel<<<grid, 256, 0, c->stream>>>(i2b_tm.p, n, L, item_to_bucket->p);
+        KERNEL_CHECK();
+    }
     // the sorted row ids are the candidate array: adopt the buffer
     static_assert(sizeof(int32_t) == sizeof(uint32_t), "");
     if (cur != sb.final_buf) fail(CULSH_ERR_INTERNAL, "radix sort ended in the scratch buffer");

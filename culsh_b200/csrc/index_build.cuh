@@ -53,7 +53,7 @@ bucket_count_kernel(const uint32_t* __restrict__ keys, int n, int tiles_per_tabl
 // Items are visited in warp-coalesced order twice: the first sweep records the head flags of
 // the tile as one ballot word per 32 consecutive items, a prefix over those words then gives
 // every item its bucket id, and the second sweep writes bucket keys / offsets (consecutive
-// heads -> consecutive addresses) and the optional (row, table) -> bucket map.
+// heads -> consecutive addresses) and the optional (table, row) -> bucket map [L][n].
 template <int NW>
 __global__ void __launch_bounds__(IB_THREADS)
 bucket_write_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ rows, int n,
@@ -117,7 +117,9 @@ bucket_write_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restric
             store_key<NW>(bucket_keys + (size_t)bid * NW, kk);
             bucket_offsets[bid] = (int32_t)(tbase + li);
         }
-        if (item_to_bucket) item_to_bucket[(size_t)rows[tbase + li] * L + t] = (int32_t)bid;
+        // table-major: the writes of one table stay inside its n*4-byte strip, which the L2 merges
+        // into full lines (row-major would touch a separate sector per item)
+        if (item_to_bucket) item_to_bucket[tbase + rows[tbase + li]] = (int32_t)bid;
     }
 }
 
@@ -140,6 +142,28 @@ inline void launch_bucket_write(cudaStream_t s, const uint32_t* keys, const uint
                                                           bucket_keys, bucket_offsets, table_offsets,
                                                           item_to_bucket);
     KERNEL_CHECK();
+}
+
+// [L][n] -> [n][L]: 32 x 32 tiles through shared memory, coalesced on both sides.
+__global__ void __launch_bounds__(256)
+transpose_table_major_kernel(const int32_t* __restrict__ src, int n, int L, int32_t* __restrict__ dst) {
+    __shared__ int32_t tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const size_t row0 = (size_t)blockIdx.x * 32;
+    const int t0 = blockIdx.y * 32;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+        const int t = t0 + j;
+        const size_t row = row0 + tx;
+        if (t < L && row < (size_t)n) tile[j][tx] = src[(size_t)t * n + row];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+        const size_t row = row0 + j;
+        const int t = t0 + tx;
+        if (row < (size_t)n && t < L) dst[row * L + t] = tile[tx][j];
+    }
 }
 
 #define CULSH_DISPATCH_NW(NWVAL, ...)                                         \

@@ -100,14 +100,39 @@ dedupe_small_kernel(const int32_t* __restrict__ matched, const int32_t* __restri
         }
         int m = 32;
         while (m < r) m <<= 1;
-        // gather the bucket lists one after another
+        // gather the bucket lists: 32 tables at a time, one lane per table, so the dependent loads
+        // (bucket id -> list bounds -> ids) of all tables overlap.  A lane copies up to four ids
+        // of its own list with independent loads; longer lists are copied by the whole warp.
         int fill = 0;
-        for (int t = 0; t < L; ++t) {
-            int b = matched[(size_t)q * L + t];
-            if (b < 0) continue;
-            int s = bucket_offsets[b], e = bucket_offsets[b + 1];
-            for (int i = s + lane; i < e; i += 32) buf[fill + (i - s)] = cand[i];
-            fill += e - s;
+        for (int t0 = 0; t0 < L; t0 += 32) {
+            const int t = t0 + lane;
+            const int b = t < L ? matched[(size_t)q * L + t] : -1;
+            int s = 0, e = 0;
+            if (b >= 0) { s = bucket_offsets[b]; e = bucket_offsets[b + 1]; }
+            const int len = e - s;
+            int inc = len;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+                if (lane >= o) inc += x;
+            }
+            const int dst0 = fill + inc - len;
+            int32_t v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = i < len ? cand[s + i] : 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (i < len) buf[dst0 + i] = v[i];
+            uint32_t longer = __ballot_sync(0xFFFFFFFFu, len > 4);
+            while (longer) {
+                const int src = __ffs(longer) - 1;
+                longer &= longer - 1;
+                const int ls = __shfl_sync(0xFFFFFFFFu, s, src);
+                const int ll = __shfl_sync(0xFFFFFFFFu, len, src);
+                const int ld = __shfl_sync(0xFFFFFFFFu, dst0, src);
+                for (int i = 4 + lane; i < ll; i += 32) buf[ld + i] = cand[ls + i];
+            }
+            fill += __shfl_sync(0xFFFFFFFFu, inc, 31);
         }
         for (int i = r + lane; i < m; i += 32) buf[i] = 0x7FFFFFFF;
         __syncwarp();
