@@ -63,9 +63,26 @@ raw_count_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict_
                  uint32_t* __restrict__ mid_list, uint32_t* __restrict__ counters, int mid_max) {
     int q = blockIdx.x * blockDim.x + threadIdx.x;
     if (q >= n_q) return;
+    // eight tables at a time, branch-free, so that the dependent loads (bucket id -> bounds) of
+    // different tables are in flight together
     uint64_t c = 0;
-    for (int t = 0; t < L; ++t) {
-        int b = matched[(size_t)q * L + t];
+    const int32_t* mq = matched + (size_t)q * L;
+    int t = 0;
+    for (; t + 8 <= L; t += 8) {
+        int b[8], lo[8], hi[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) b[j] = mq[t + j];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int bb = max(b[j], 0);
+            lo[j] = bucket_offsets[bb];
+            hi[j] = bucket_offsets[bb + 1];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) c += b[j] >= 0 ? (uint64_t)(hi[j] - lo[j]) : 0ull;
+    }
+    for (; t < L; ++t) {
+        const int b = mq[t];
         if (b >= 0) c += (uint64_t)(bucket_offsets[b + 1] - bucket_offsets[b]);
     }
     raw_cnt[q] = c;
@@ -76,11 +93,69 @@ raw_count_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict_
 }
 
 // ---------------------------------------------------------------------------------------
-// Small path: one warp per query, raw <= SMALL_MAX.  Bitonic sort in the warp's slice of
-// shared memory, adjacent-unique, ballot compaction.  Output goes to tmp[raw_off[q] ...].
+// Small path: one warp per query, raw <= SMALL_MAX.  The ids are gathered into the warp's slice
+// of shared memory, sorted in registers (bitonic, shuffles), made unique and compacted by
+// ballots.  Output goes to tmp[raw_off[q] ...].
 // ---------------------------------------------------------------------------------------
 constexpr int SM_THREADS = 256;
 constexpr int SM_WARPS = SM_THREADS / 32;
+
+// Bitonic sort of 32*E ids held E per lane (position p = 32*e + lane lives in v[e] of `lane`),
+// then adjacent-unique and ballot compaction to out[]; returns the number of unique ids.
+// Exchanges at distance >= 32 stay inside a lane, shorter ones are one shuffle each; everything
+// is unrolled at compile time, so the ids never leave registers.
+template <int E>
+__device__ __forceinline__ int warp_sort_unique(const int32_t* __restrict__ buf, int r, int lane,
+                                                int32_t* __restrict__ out) {
+    int32_t v[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const int p = 32 * e + lane;
+        v[e] = p < r ? buf[p] : 0x7FFFFFFF;
+    }
+#pragma unroll
+    for (int ksz = 2; ksz <= 32 * E; ksz <<= 1) {
+#pragma unroll
+        for (int j = ksz >> 1; j > 0; j >>= 1) {
+            if (j >= 32) {
+                const int je = j >> 5;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    if ((e & je) == 0) {
+                        const bool up = ((32 * e + lane) & ksz) == 0;
+                        const int32_t a = v[e], b = v[e | je];
+                        const bool sw = (a > b) == up;
+                        v[e] = sw ? b : a;
+                        v[e | je] = sw ? a : b;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const bool up = ((32 * e + lane) & ksz) == 0;
+                    const int32_t other = __shfl_xor_sync(0xFFFFFFFFu, v[e], j);
+                    const bool keep_min = ((lane & j) == 0) == up;
+                    v[e] = keep_min ? min(v[e], other) : max(v[e], other);
+                }
+            }
+        }
+    }
+    int written = 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        int32_t prev = __shfl_up_sync(0xFFFFFFFFu, v[e], 1);
+        if (e > 0) {
+            const int32_t last = __shfl_sync(0xFFFFFFFFu, v[e - 1], 31);
+            if (lane == 0) prev = last;
+        }
+        const int p = 32 * e + lane;
+        const bool keep = p < r && (p == 0 || prev != v[e]);
+        const uint32_t mask = __ballot_sync(0xFFFFFFFFu, keep);
+        if (keep) out[written + __popc(mask & ((1u << lane) - 1))] = v[e];
+        written += __popc(mask);
+    }
+    return written;
+}
 
 __global__ void __launch_bounds__(SM_THREADS)
 dedupe_small_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
@@ -134,36 +209,14 @@ dedupe_small_kernel(const int32_t* __restrict__ matched, const int32_t* __restri
             }
             fill += __shfl_sync(0xFFFFFFFFu, inc, 31);
         }
-        for (int i = r + lane; i < m; i += 32) buf[i] = 0x7FFFFFFF;
         __syncwarp();
-        for (int ksz = 2; ksz <= m; ksz <<= 1) {
-            for (int j = ksz >> 1; j > 0; j >>= 1) {
-                for (int i = lane; i < m; i += 32) {
-                    int ixj = i ^ j;
-                    if (ixj > i) {
-                        int32_t a = buf[i], b = buf[ixj];
-                        bool up = (i & ksz) == 0;
-                        if ((a > b) == up) { buf[i] = b; buf[ixj] = a; }
-                    }
-                }
-                __syncwarp();
-            }
-        }
-        // unique + compact
         int32_t* out = tmp + raw_off[q];
-        int written = 0;
-        for (int i0 = 0; i0 < r; i0 += 32) {
-            int i = i0 + lane;
-            bool keep = false;
-            int32_t v = 0;
-            if (i < r) {
-                v = buf[i];
-                keep = i == 0 || buf[i - 1] != v;
-            }
-            uint32_t mask = __ballot_sync(0xFFFFFFFFu, keep);
-            if (keep) out[written + __popc(mask & ((1u << lane) - 1))] = v;
-            written += __popc(mask);
-        }
+        int written;
+        if (m <= 32) written = warp_sort_unique<1>(buf, r, lane, out);
+        else if (m <= 64) written = warp_sort_unique<2>(buf, r, lane, out);
+        else if (m <= 128) written = warp_sort_unique<4>(buf, r, lane, out);
+        else if (m <= 256) written = warp_sort_unique<8>(buf, r, lane, out);
+        else written = warp_sort_unique<16>(buf, r, lane, out);
         if (lane == 0) uniq_cnt[q] = (uint64_t)written;
         __syncwarp();
     }
