@@ -166,6 +166,22 @@ def test_pslsh_fit_query_parity(eng, dtype, n, d, L, k, w, scale):
     _assert_candidates_equal(model.query(Q), oracle.query_index(oracle.fit_index(sig, L, k), qsig))
 
 
+def test_large_tables_use_the_chunked_tile_scan(eng):
+    """Tables of 512 tiles or more take the two-level tile scan of the radix sort (here 8-byte
+    keys: 3072 items per tile, 554 tiles per table); index arrays must still equal the oracle's."""
+    culsh, core_mod = eng
+    rng = np.random.RandomState(91)
+    n, d, L, k, w = 1_700_000, 4, 2, 6, 1
+    X = rng.randn(n, d).astype(np.float32)
+    model = culsh.PStableLSH(L, k, window_size=w, seed=21).fit(X)
+    ix = model.index
+    assert ix.elem_bytes == 1
+    sig = _sig_matrix(core_mod.PSLSHCore(L, k, w, 21).hash(X, ix))
+    oidx = _assert_index_equals_oracle(ix, sig, L, k)
+    sel = rng.randint(0, n, 16)
+    _assert_candidates_equal(model.query(X[sel]), oracle.query_index(oidx, sig[sel]))
+
+
 def test_pslsh_consistency_and_auto_window(eng):
     culsh, _ = eng
     rng = np.random.RandomState(5)
