@@ -260,6 +260,54 @@ __device__ __forceinline__ bool epilogue_columns(const TcArgs& a, uint32_t taddr
     return any_ovf;
 }
 
+// Fast form of the p-stable epilogue for one-byte elements and K in {1, 2, 4, 8, 16} hashes per
+// table (16 accumulator columns = 16 / K whole tables, c_begin a multiple of 16): the 16 values of
+// a group are quantised with independent instructions (one add, one float->int with floor
+// rounding, one range test, one byte insert each) and the keys are slices of the resulting 16
+// bytes - no per-element bookkeeping or branches as in the general form.
+template <int K>
+__device__ __forceinline__ bool epilogue_pslsh_bytes(const TcArgs& a, uint32_t taddr, int c_begin, int c_end,
+                                                     int first_table, int bias_base, int row, bool row_ok) {
+    constexpr int PER_GROUP = 16 / K;
+    constexpr int NW = K <= 4 ? 1 : K / 4;
+    bool any_ovf = false;
+    int tbl = first_table;
+    int tables_left = (c_end - c_begin) / K;
+    for (int g0 = c_begin; g0 < c_end; g0 += 16, tbl += PER_GROUP, tables_left -= PER_GROUP) {
+        uint32_t r[16];
+        tc_ld16(taddr + (uint32_t)g0, r);
+        tc_ld_wait();
+        const float* __restrict__ bias = a.bias + bias_base + g0;
+#pragma unroll
+        for (int ti = 0; ti < PER_GROUP; ++ti) {
+            if (ti < tables_left) {  // warp-uniform
+                uint32_t w[NW];
+#pragma unroll
+                for (int i = 0; i < NW; ++i) w[i] = 0u;
+                uint32_t bad = 0u;
+#pragma unroll
+                for (int e = 0; e < K; ++e) {
+                    const int j = ti * K + e;
+                    const int q = __float2int_rd(__uint_as_float(r[j]) + __ldg(bias + j));  // pslsh/hash.cuh:46
+                    bad |= (uint32_t)(q + 128) >> 8;  // non-zero outside [-128, 127]
+                    const int pos = NW * 4 - K + e;    // byte position in the key, 0 = most significant
+                    w[pos >> 2] |= ((uint32_t)q & 0xFFu) << (24 - 8 * (pos & 3));
+                }
+                if (row_ok) {
+                    const size_t item = (size_t)(tbl + ti) * a.n_total + a.row_offset + row;
+                    uint32_t* dst = a.keys + item * NW;
+                    if (NW == 1) dst[0] = w[0];
+                    else if (NW == 2) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                    else *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2 % NW], w[3 % NW]);
+                    if (a.ovf_rows) a.ovf_rows[item] = bad ? 1 : 0;
+                    else any_ovf |= bad != 0u;
+                }
+            }
+        }
+    }
+    return any_ovf;
+}
+
 template <int KBLK, int FAMILY>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmP, TcArgs a) {
@@ -430,7 +478,12 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * TC_BN);
                 if (te > tb) {
                     bool o;
-                    if (NW == 1) o = epilogue_columns<FAMILY, 1>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    const bool byte_form = FAMILY == CULSH_PSLSH && a.elem_bytes == 1 && ((tb * k) & 15) == 0;
+                    if (byte_form && k == 8) o = epilogue_pslsh_bytes<8>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (byte_form && k == 4) o = epilogue_pslsh_bytes<4>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (byte_form && k == 16) o = epilogue_pslsh_bytes<16>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (byte_form && k == 2) o = epilogue_pslsh_bytes<2>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (NW == 1) o = epilogue_columns<FAMILY, 1>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
                     else if (NW == 2) o = epilogue_columns<FAMILY, 2>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
                     else o = epilogue_columns<FAMILY, 0>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
                     any_ovf |= o;
