@@ -478,6 +478,7 @@ int bitmap_window_bits(const CtxPtr& c, int n_rows) {
 //                       multiple of 4096 rows
 //   CULSH_CHAIN_STAGE   ids staged in shared memory per copy-out chunk (default 5632)
 //   CULSH_CHAIN_THREADS threads per CTA: 256, 384 (default) or 512
+//   CULSH_CHAIN_LOADS   loads in flight per lane in the list walks: 4, 8 or 16 (default)
 //   CULSH_CHAIN_SLICES  0 = CTAs search their list slices themselves (default 1: precomputed)
 constexpr int CHAIN_MAX_WINDOWS = 8;
 inline long env_long(const char* name, long dflt) {
@@ -574,20 +575,27 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
                 matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, n_q, L, cbits, n_win, mid_max, slices.p);
             KERNEL_CHECK();
         }
-        auto launch = [&](auto nt_tag) {
+        auto launch = [&](auto nt_tag, auto mk_tag) {
             constexpr int NT = decltype(nt_tag)::value;
+            constexpr int MK = decltype(mk_tag)::value;
             const size_t smem = chain_window_smem_bytes(cbits, stage_ids);
-            CU_CHECK(cudaFuncSetAttribute(dedupe_chained_rank_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            CU_CHECK(cudaFuncSetAttribute(dedupe_chained_rank_kernel<NT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-            dedupe_chained_rank_kernel<NT><<<(unsigned)n_tk, NT, smem, s>>>(
+            CU_CHECK(cudaFuncSetAttribute(dedupe_chained_rank_kernel<NT, MK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CU_CHECK(cudaFuncSetAttribute(dedupe_chained_rank_kernel<NT, MK>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+            dedupe_chained_rank_kernel<NT, MK><<<(unsigned)n_tk, NT, smem, s>>>(
                 matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, raw_off.p, n_q, L, ix.n, cbits, n_win, stage_ids,
                 mid_max, slices.p, tmp.p, status.p, ticket, out.indices.p, out.counts.p, out.offsets.p, c->d_error);
         };
         const long cw_threads = env_long("CULSH_CHAIN_THREADS", 384);
+        const long cw_mk = env_long("CULSH_CHAIN_LOADS", 16);
         if (c->profiling) cudaEventRecord(c->ev_dedupe[0], s);
-        if (cw_threads == 512) launch(std::integral_constant<int, 512>{});
-        else if (cw_threads == 256) launch(std::integral_constant<int, 256>{});
-        else launch(std::integral_constant<int, 384>{});
+        auto with_loads = [&](auto nt_tag) {
+            if (cw_mk == 4) launch(nt_tag, std::integral_constant<int, 4>{});
+            else if (cw_mk == 8) launch(nt_tag, std::integral_constant<int, 8>{});
+            else launch(nt_tag, std::integral_constant<int, 16>{});
+        };
+        if (cw_threads == 512) with_loads(std::integral_constant<int, 512>{});
+        else if (cw_threads == 256) with_loads(std::integral_constant<int, 256>{});
+        else with_loads(std::integral_constant<int, 384>{});
         KERNEL_CHECK();
         if (c->profiling) { cudaEventRecord(c->ev_dedupe[1], s); dedupe_timed = true; }
         if (n_win > 1) {

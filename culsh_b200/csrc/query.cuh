@@ -680,12 +680,12 @@ __device__ __forceinline__ int warp_lower_bound(const int32_t* __restrict__ a, i
 
 // Calls f(id) for every element of the Lg lists [s_lo[t], s_lo[t] + len_t) laid end to end
 // (s_pre[t] = exclusive prefix of the lengths, s_pre[Lg] = total).  The flat sequence is cut into
-// equal stretches, one per warp; lanes read consecutive elements (coalesced), MK loads in flight.
-template <int NT, typename F>
+// equal stretches, one per warp; lanes read consecutive elements (coalesced), MK loads in flight
+// per lane.
+template <int NT, int MK, typename F>
 __device__ __forceinline__ void walk_lists(const int32_t* __restrict__ cand, const int* __restrict__ s_lo,
                                            const int* __restrict__ s_pre, int Lg, F&& f) {
     constexpr int NWARP = NT / 32;
-    constexpr int MK = 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int total = s_pre[Lg];
     const int per_warp = (((total + NWARP - 1) / NWARP) + 31) & ~31;
@@ -754,7 +754,7 @@ slice_lists_kernel(const int32_t* __restrict__ matched, const int32_t* __restric
     if (w == n_win - 1) flat[mine + 1] = we;
 }
 
-template <int NT>
+template <int NT, int MK>
 __global__ void __launch_bounds__(NT)
 dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
                            const int32_t* __restrict__ cand, const uint64_t* __restrict__ raw_cnt,
@@ -860,7 +860,7 @@ dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* _
     }
     __syncthreads();
     // ---- 2. mark ----
-    walk_lists<NT>(cand, s_lo, s_pre, L, [&](int32_t v) {
+    walk_lists<NT, MK>(cand, s_lo, s_pre, L, [&](int32_t v) {
         const uint32_t id = (uint32_t)(v - win_lo);
         atomicOr(&bm32[id >> 5], 1u << (id & 31));
     });
@@ -895,7 +895,7 @@ dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* _
     unsigned long long excl = 0;
     for (uint32_t chunk_lo = 0; chunk_lo == 0 || chunk_lo < wtotal; chunk_lo += (uint32_t)stage_ids) {
         if (wtotal > 0) {
-            walk_lists<NT>(cand, s_lo, s_pre, L, [&](int32_t v) {
+            walk_lists<NT, MK>(cand, s_lo, s_pre, L, [&](int32_t v) {
                 const uint32_t id = (uint32_t)(v - win_lo);
                 const unsigned long long below = bm64[id >> 6] & ((1ull << (id & 63)) - 1ull);
                 const uint32_t r = prefix[id >> 6] + (uint32_t)__popcll(below) - chunk_lo;

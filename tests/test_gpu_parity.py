@@ -298,20 +298,20 @@ def test_sort_path_for_mid_sized_sets_on_a_large_index(eng):
     _assert_candidates_equal(m2.query(X[sel[:3]]), oracle.query_index(oracle.fit_index(sig2, 2, 3), sig2[sel[:3]]))
 
 
-@pytest.mark.parametrize("bits,stage,threads,slices", [
-    (None, None, None, None),        # defaults: two windows at this size
-    (8192, 256, 256, 1),             # many windows (falls back to the windowed bitmap kernel)
-    (65536, 256, 256, 1),            # 5 windows, many copy-out chunks, precomputed slices
-    (65536, 300, 512, 0),            # the CTAs search their slices themselves
-    (131072, 40960, 384, 0),         # 3 windows, one chunk
-    (1 << 20, 5632, 384, 1),         # one window
+@pytest.mark.parametrize("bits,stage,threads,slices,loads", [
+    (None, None, None, None, None),  # defaults: two windows at this size
+    (8192, 256, 256, 1, 16),         # many windows (falls back to the windowed bitmap kernel)
+    (65536, 256, 256, 1, 8),         # 5 windows, many copy-out chunks, precomputed slices
+    (65536, 300, 512, 0, 4),         # the CTAs search their slices themselves
+    (131072, 40960, 384, 0, 8),      # 3 windows, one chunk
+    (1 << 20, 5632, 384, 1, 4),      # one window
 ])
-def test_chained_dedupe_windows_chunks_and_slices(eng, monkeypatch, bits, stage, threads, slices):
+def test_chained_dedupe_windows_chunks_and_slices(eng, monkeypatch, bits, stage, threads, slices, loads):
     """Query sets dominated by large candidate sets take the chained single-pass kernel; its window
     size, stage size, CTA size and slice source must not change the result."""
     culsh, core_mod = eng
     for name, v in (("CULSH_CHAIN_BITS", bits), ("CULSH_CHAIN_STAGE", stage), ("CULSH_CHAIN_THREADS", threads),
-                    ("CULSH_CHAIN_SLICES", slices)):
+                    ("CULSH_CHAIN_SLICES", slices), ("CULSH_CHAIN_LOADS", loads)):
         if v is None:
             monkeypatch.delenv(name, raising=False)
         else:

@@ -88,3 +88,54 @@ def test_peer_exchange_two_processes_one_gpu(tmp_path):
         assert np.array_equal(g["off"].astype(np.int64), woff[r_lo:r_hi + 1] - woff[r_lo])
         assert np.array_equal(g["idx"], w["idx"][woff[r_lo]:woff[r_hi]])
     assert covered == len(woff) - 1
+
+
+def _nccl_worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    try:
+        import culsh_b200
+        from culsh_b200 import sharded
+        rng = np.random.RandomState(5)
+        n, d, L, k = 9001, 24, 6, 10  # ragged split: 4501 + 4500 rows
+        X = rng.randn(n, d).astype(np.float32)
+        lo, hi = sharded.shard_bounds(n, world, rank)
+        Xd = torch.from_numpy(X[lo:hi]).cuda(rank)
+        ex = sharded.PeerExchange(device=rank)
+        fq, (r_lo, r_hi) = sharded.fit_query_sharded(culsh_b200.RPLSH(L, k, seed=9), Xd, ex, batch_size=2000)
+        np.savez(os.path.join(out_dir, f"n{rank}.npz"), idx=fq.get_indices(), off=fq.get_offsets(),
+                 r_lo=r_lo, r_hi=r_hi)
+        if rank == 0:
+            w = culsh_b200.RPLSH(L, k, seed=9).fit_query(X)
+            np.savez(os.path.join(out_dir, "n_whole.npz"), idx=w.get_indices(), off=w.get_offsets())
+        ex.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_fit_query_sharded_two_gpus_nccl(tmp_path):
+    """Real peers: one process per GPU, NCCL for the row all-gather and the barriers, CUDA IPC
+    mappings across two devices for the exchange."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_nccl_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    w = np.load(tmp_path / "n_whole.npz")
+    woff = w["off"].astype(np.int64)
+    covered = 0
+    for r in range(world):
+        g = np.load(tmp_path / f"n{r}.npz")
+        r_lo, r_hi = int(g["r_lo"]), int(g["r_hi"])
+        assert r_lo == covered
+        covered = r_hi
+        assert np.array_equal(g["off"].astype(np.int64), woff[r_lo:r_hi + 1] - woff[r_lo])
+        assert np.array_equal(g["idx"], w["idx"][woff[r_lo]:woff[r_hi]])
+    assert covered == len(woff) - 1
