@@ -428,6 +428,17 @@ def run_ours(args, wl, spec):
                           "note": "4 B per raw candidate id read + 4 B per unique id written (the second walk "
                                   "over the lists is an L2 re-read), over the CUDA-event time of the dedupe "
                                   f"launch alone; peak {peaks['source']}"}
+    if wl == "c2":
+        # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) measured by ncu on the
+        # 400,000-row case of this workload and scaled by the units a launch processes; the
+        # captures and their commands are summarised under profiles/.
+        per_unit = {"hash": ((205.4e6 + 38.3e6) / 400000.0, n),                 # per row
+                    "sort": ((105.7e6 + 52.7e6) / 12.8e6, items),                # per (row, table) pair
+                    "gather": ((78.4e6 + 238.3e6) / 74.3e6, sq["raw_candidates"])}  # per raw candidate id
+        for key, (bytes_per_unit, units) in per_unit.items():
+            if key in roof:
+                roof[key]["traffic"] = bytes_per_unit * units
+                roof[key]["traffic_note"] = "ncu DRAM bytes of the 400,000-row capture scaled to this launch"
     for r in roof.values():
         r["frac"] = r["achieved"] / r["peak"]
     # the stage whose kernel takes the largest share of the step
