@@ -476,7 +476,7 @@ int bitmap_window_bits(const CtxPtr& c, int n_rows) {
 //   CULSH_CHAIN_BITS    rows per window (default 253,952: bitmap, prefix and stage of three CTAs
 //                       fit one SM); the row range is cut into the fewest such windows, each a
 //                       multiple of 4096 rows
-//   CULSH_CHAIN_STAGE   ids staged in shared memory per copy-out chunk (default 5632)
+//   CULSH_CHAIN_STAGE   ids staged in shared memory per copy-out chunk (default 5120)
 //   CULSH_CHAIN_THREADS threads per CTA: 256, 384 (default) or 512
 //   CULSH_CHAIN_LOADS   loads in flight per lane in the list walks: 4, 8 or 16 (default)
 //   CULSH_CHAIN_SLICES  0 = CTAs search their list slices themselves (default 1: precomputed)
@@ -538,7 +538,7 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     // large candidate sets and the row range is a few chain windows; otherwise scratch + compaction.
     int n_win = 1;
     const int cbits = chain_window_bits(ix.n, &n_win);
-    const int stage_ids = (int)std::min<long>(40960, std::max<long>(256, env_long("CULSH_CHAIN_STAGE", 5632)));
+    const int stage_ids = (int)std::min<long>(40960, std::max<long>(256, env_long("CULSH_CHAIN_STAGE", 5120)));
     const bool chained = n_win <= CHAIN_MAX_WINDOWS && L <= CW_MAX_L && (size_t)nb * 2 >= (size_t)n_q &&
                          (uint64_t)n_q * (uint64_t)n_win < (1ull << 31) &&
                          chain_window_smem_bytes(cbits, stage_ids) + 1024 <= c->smem_optin;

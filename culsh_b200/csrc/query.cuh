@@ -642,11 +642,12 @@ __device__ __forceinline__ bool chain_exclusive_prefix(unsigned long long* statu
 // the ids in the CSR.  A CTA
 //   1. narrows every bucket list (ascending row ids) to its window with a 32-way warp search,
 //   2. marks the ids of those slices in a shared-memory bitmap,
-//   3. scans the bitmap once: pop-count prefix per 64-bit word and the number of unique ids,
-//      which it publishes to the chain,
-//   4. walks the slices a second time (L2 hits): the rank of an id among the unique ids of the
-//      window is prefix[word] + popc(bits below it), so the id is dropped at stage[rank] in
-//      shared memory - duplicates write the same value to the same slot,
+//   3. scans the bitmap once: pop-count prefix per 32-bit word (16 bits, inside blocks of 512
+//      rows), a base per block and the number of unique ids, which it publishes to the chain,
+//   4. goes over the ids a second time (from registers when a warp's share fits one batch, else
+//      from L2): the rank of an id among the unique ids of the window is base[block] +
+//      prefix[word] + popc(bits below it), so the id is dropped at stage[rank] in shared memory -
+//      duplicates write the same value to the same slot,
 //   5. resolves its exclusive prefix from the chain and copies the staged ids, now sorted and
 //      unique, to their final CSR position with coalesced stores.
 // Work is proportional to the candidates (two walks) plus one pass over the window, there is no
@@ -657,8 +658,9 @@ __device__ __forceinline__ bool chain_exclusive_prefix(unsigned long long* statu
 constexpr int CW_MAX_L = 256;    // lists per query kept in shared memory (<= threads per CTA)
 
 inline size_t chain_window_smem_bytes(int window_bits, int stage_ids) {
-    return (size_t)window_bits / 8 + (size_t)window_bits / 16 + (size_t)stage_ids * sizeof(int32_t) +
-           (3 * CW_MAX_L + 1) * sizeof(int);
+    // bitmap (1 bit per row) + 16-bit prefix per 32-bit word + 32-bit base per 512 rows + stage + lists
+    return (size_t)window_bits / 8 + (size_t)window_bits / 16 + (size_t)window_bits / 128 +
+           (size_t)stage_ids * sizeof(int32_t) + (3 * CW_MAX_L + 1) * sizeof(int);
 }
 
 // First position p in [lo, hi) with a[p] >= target (hi if there is none).  Called by a full warp.
@@ -678,32 +680,37 @@ __device__ __forceinline__ int warp_lower_bound(const int32_t* __restrict__ a, i
     return lo + __popc(__ballot_sync(0xFFFFFFFFu, below));
 }
 
-// Calls f(id) for every element of the Lg lists [s_lo[t], s_lo[t] + len_t) laid end to end
-// (s_pre[t] = exclusive prefix of the lengths, s_pre[Lg] = total).  The flat sequence is cut into
-// equal stretches, one per warp; lanes read consecutive elements (coalesced), MK loads in flight
-// per lane.
-template <int NT, int MK, typename F>
-__device__ __forceinline__ void walk_lists(const int32_t* __restrict__ cand, const int* __restrict__ s_lo,
-                                           const int* __restrict__ s_pre, int Lg, F&& f) {
-    constexpr int NWARP = NT / 32;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int total = s_pre[Lg];
-    const int per_warp = (((total + NWARP - 1) / NWARP) + 31) & ~31;
-    const int w_begin = warp * per_warp, w_end = min(total, w_begin + per_warp);
-    if (w_begin >= w_end) return;
-    int t;
-    {
-        int a = 0, b = Lg - 1;
-        while (a < b) {  // largest t with s_pre[t] <= w_begin
-            const int mid = (a + b + 1) >> 1;
-            if (s_pre[mid] <= w_begin) a = mid; else b = mid - 1;
+// Walk over the Lg lists [s_lo[t], s_lo[t] + len_t) laid end to end (s_pre[t] = exclusive prefix
+// of the lengths, s_pre[Lg] = total).  The flat sequence is cut into equal stretches, one per warp;
+// a batch is 32 * MK consecutive elements of the stretch: lanes read consecutive elements
+// (coalesced) and every lane has MK independent loads in flight.  The loaded ids are handed back
+// untouched (-1 past the end) so that the caller decides when to consume them.
+template <int NT, int MK>
+struct ListWalk {
+    int t, next, base, w_begin, w_end, per_warp;
+
+    __device__ __forceinline__ void init(const int* __restrict__ s_lo, const int* __restrict__ s_pre, int Lg) {
+        constexpr int NWARP = NT / 32;
+        const int warp = threadIdx.x >> 5;
+        const int total = s_pre[Lg];
+        per_warp = (((total + NWARP - 1) / NWARP) + 31) & ~31;
+        w_begin = warp * per_warp;
+        w_end = min(total, w_begin + per_warp);
+        t = 0; next = 0; base = 0;
+        if (w_begin < w_end) {
+            int a = 0, b = Lg - 1;
+            while (a < b) {  // largest t with s_pre[t] <= w_begin
+                const int mid = (a + b + 1) >> 1;
+                if (s_pre[mid] <= w_begin) a = mid; else b = mid - 1;
+            }
+            t = a;
+            next = s_pre[t + 1];        // first flat position past list t
+            base = s_lo[t] - s_pre[t];  // flat position -> position in cand
         }
-        t = a;
     }
-    int next = s_pre[t + 1];            // first flat position past list t
-    int base = s_lo[t] - s_pre[t];      // flat position -> position in cand
-    for (int e0 = w_begin + lane; e0 - lane < w_end; e0 += 32 * MK) {
-        int32_t v[MK];
+    // batch whose first element (of lane 0) is the flat position e0 - lane
+    __device__ __forceinline__ void load(const int32_t* __restrict__ cand, const int* __restrict__ s_lo,
+                                         const int* __restrict__ s_pre, int e0, int32_t (&v)[MK]) {
 #pragma unroll
         for (int j = 0; j < MK; ++j) {
             const int e = e0 + 32 * j;
@@ -717,11 +724,8 @@ __device__ __forceinline__ void walk_lists(const int32_t* __restrict__ cand, con
                 v[j] = cand[base + e];
             }
         }
-#pragma unroll
-        for (int j = 0; j < MK; ++j)
-            if (v[j] >= 0) f(v[j]);
     }
-}
+};
 
 // Slice of every bucket list that falls into every window: slices[(q * n_win + w) * L + t] =
 // [a, b) in cand.  One thread per (query, list, window) finds the window's lower boundary with a
@@ -766,11 +770,12 @@ dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* _
                            uint64_t* __restrict__ offsets, int* __restrict__ d_error) {
     constexpr int NWARP = NT / 32;
     extern __shared__ __align__(16) uint32_t s_dyn[];
-    const int n64 = window_bits / 64;
-    unsigned long long* bm64 = reinterpret_cast<unsigned long long*>(s_dyn);   // [n64]
-    uint32_t* bm32 = s_dyn;
-    uint32_t* prefix = s_dyn + 2 * n64;                                        // [n64]
-    int32_t* stage = reinterpret_cast<int32_t*>(prefix + n64);                // [stage_ids]
+    const int n32 = window_bits / 32;      // a multiple of 128
+    const int n_blocks = n32 / 16;         // blocks of 512 rows
+    uint32_t* bm32 = s_dyn;                                                    // [n32] bitmap
+    uint16_t* pre16 = reinterpret_cast<uint16_t*>(bm32 + n32);                // [n32] set bits before the word, inside its block
+    uint32_t* base32 = reinterpret_cast<uint32_t*>(pre16 + n32);              // [n_blocks] set bits before the block
+    int32_t* stage = reinterpret_cast<int32_t*>(base32 + n_blocks);          // [stage_ids]
     int* s_lo = reinterpret_cast<int*>(stage + stage_ids);                    // [L] slice start in cand
     int* s_we = s_lo + CW_MAX_L;                                               // [L] slice end
     int* s_pre = s_we + CW_MAX_L;                                              // [L + 1] prefix of slice lengths
@@ -816,7 +821,7 @@ dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* _
     // ---- 1. clear, list bounds, slices ----
     {
         uint4* b4 = reinterpret_cast<uint4*>(s_dyn);
-        for (int i = tid; i < n64 / 2; i += NT) b4[i] = make_uint4(0, 0, 0, 0);
+        for (int i = tid; i < n32 / 4; i += NT) b4[i] = make_uint4(0, 0, 0, 0);
     }
     if (slices) {
         if (tid < L) {
@@ -859,24 +864,61 @@ dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* _
         if (tid == L - 1) s_pre[L] = base + inc;
     }
     __syncthreads();
-    // ---- 2. mark ----
-    walk_lists<NT, MK>(cand, s_lo, s_pre, L, [&](int32_t v) {
-        const uint32_t id = (uint32_t)(v - win_lo);
+    // ---- 2. mark.  A stretch that fits one batch keeps its ids in registers for step 4. ----
+    ListWalk<NT, MK> wk;
+    wk.init(s_lo, s_pre, L);
+    const bool single = wk.per_warp <= 32 * MK;  // same for every warp
+    int32_t v[MK];
+    auto mark = [&](int32_t x) {
+        const uint32_t id = (uint32_t)(x - win_lo);
         atomicOr(&bm32[id >> 5], 1u << (id & 31));
-    });
+    };
+    if (single) {
+        wk.load(cand, s_lo, s_pre, wk.w_begin + lane, v);
+#pragma unroll
+        for (int j = 0; j < MK; ++j)
+            if (v[j] >= 0) mark(v[j]);
+    } else {
+        for (int e0 = wk.w_begin + lane; e0 - lane < wk.w_end; e0 += 32 * MK) {
+            wk.load(cand, s_lo, s_pre, e0, v);
+#pragma unroll
+            for (int j = 0; j < MK; ++j)
+                if (v[j] >= 0) mark(v[j]);
+        }
+    }
     __syncthreads();
-    // ---- 3. pop-count prefix per 64-bit word; a thread owns a contiguous run of words ----
-    const int per_thread = ((n64 + NT - 1) / NT) | 1;  // odd stride: 64-bit loads of a warp spread over all banks
-    const int i_begin = min(n64, tid * per_thread), i_end = min(n64, i_begin + per_thread);
+    // ---- 3. pop-count prefixes.  A warp takes 128 words at a time, a lane four of them; four
+    // lanes make a block of 512 rows: 16-bit prefixes inside the block, block totals on the side,
+    // then one scan over the block totals. ----
+    {
+        const uint4* bm4 = reinterpret_cast<const uint4*>(bm32);
+        uint2* pre2 = reinterpret_cast<uint2*>(pre16);
+        for (int g = warp; g < n32 / 128; g += NWARP) {
+            const uint4 x = bm4[g * 32 + lane];
+            const uint32_t c0 = __popc(x.x), c1 = __popc(x.y), c2 = __popc(x.z), c3 = __popc(x.w);
+            const uint32_t sum = c0 + c1 + c2 + c3;
+            uint32_t inc = sum;
+            uint32_t up = __shfl_up_sync(0xFFFFFFFFu, inc, 1);
+            if ((lane & 3) >= 1) inc += up;
+            up = __shfl_up_sync(0xFFFFFFFFu, inc, 2);
+            if ((lane & 3) >= 2) inc += up;
+            const uint32_t p0 = inc - sum, p1 = p0 + c0, p2 = p1 + c1, p3 = p2 + c2;  // each <= 512
+            pre2[g * 32 + lane] = make_uint2(p0 | (p1 << 16), p2 | (p3 << 16));
+            if ((lane & 3) == 3) base32[g * 8 + (lane >> 2)] = inc;  // block total, turned into a base below
+        }
+    }
+    __syncthreads();
+    const int per_thread = (n_blocks + NT - 1) / NT;
+    const int b_begin = min(n_blocks, tid * per_thread), b_end = min(n_blocks, b_begin + per_thread);
     uint32_t mine = 0;
-    for (int i = i_begin; i < i_end; ++i) mine += __popcll(bm64[i]);
+    for (int i = b_begin; i < b_end; ++i) mine += base32[i];
     uint32_t inc = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
         if (lane >= o) inc += x;
     }
-    if (lane == 31) s_wtot[warp] = inc;  // safe: every thread passed the barrier after its last read
+    if (lane == 31) s_wtot[warp] = inc;  // safe: every thread passed a barrier after its last read
     __syncthreads();
     uint32_t run = inc - mine, wtotal = 0;
     for (int i = 0; i < NWARP; ++i) {
@@ -884,9 +926,10 @@ dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* _
         if (i < warp) run += x;
         wtotal += x;
     }
-    for (int i = i_begin; i < i_end; ++i) {
-        prefix[i] = run;
-        run += __popcll(bm64[i]);
+    for (int i = b_begin; i < b_end; ++i) {
+        const uint32_t x = base32[i];
+        base32[i] = run;
+        run += x;
     }
     // publish the count now; the prefix is resolved after the first chunk has been ranked
     if (tid == 0 && tk > 0) *reinterpret_cast<volatile unsigned long long*>(status + tk) = CH_FLAG_AGG | wtotal;
@@ -894,13 +937,27 @@ dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* _
     // ---- 4 + 5. rank, stage, copy out ----
     unsigned long long excl = 0;
     for (uint32_t chunk_lo = 0; chunk_lo == 0 || chunk_lo < wtotal; chunk_lo += (uint32_t)stage_ids) {
+        auto rank = [&](int32_t x) {
+            const uint32_t id = (uint32_t)(x - win_lo);
+            const uint32_t word = id >> 5;
+            const uint32_t below = bm32[word] & ((1u << (id & 31)) - 1u);
+            const uint32_t r = base32[id >> 9] + (uint32_t)pre16[word] + (uint32_t)__popc(below) - chunk_lo;
+            if (r < (uint32_t)stage_ids) stage[r] = x;
+        };
         if (wtotal > 0) {
-            walk_lists<NT, MK>(cand, s_lo, s_pre, L, [&](int32_t v) {
-                const uint32_t id = (uint32_t)(v - win_lo);
-                const unsigned long long below = bm64[id >> 6] & ((1ull << (id & 63)) - 1ull);
-                const uint32_t r = prefix[id >> 6] + (uint32_t)__popcll(below) - chunk_lo;
-                if (r < (uint32_t)stage_ids) stage[r] = v;
-            });
+            if (single) {
+#pragma unroll
+                for (int j = 0; j < MK; ++j)
+                    if (v[j] >= 0) rank(v[j]);
+            } else {
+                wk.init(s_lo, s_pre, L);
+                for (int e0 = wk.w_begin + lane; e0 - lane < wk.w_end; e0 += 32 * MK) {
+                    wk.load(cand, s_lo, s_pre, e0, v);
+#pragma unroll
+                    for (int j = 0; j < MK; ++j)
+                        if (v[j] >= 0) rank(v[j]);
+                }
+            }
         }
         if (chunk_lo == 0) {
             if (warp == 0) {
