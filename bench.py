@@ -434,7 +434,7 @@ def run_ours(args, wl, spec):
         # captures and their commands are summarised under profiles/.
         per_unit = {"hash": ((205.4e6 + 38.3e6) / 400000.0, n),                 # per row
                     "sort": ((105.7e6 + 52.7e6) / 12.8e6, items),                # per (row, table) pair
-                    "gather": ((78.4e6 + 238.3e6) / 74.3e6, sq["raw_candidates"])}  # per raw candidate id
+                    "gather": ((81.5e6 + 238.4e6) / 74.3e6, sq["raw_candidates"])}  # per raw candidate id
         for key, (bytes_per_unit, units) in per_unit.items():
             if key in roof:
                 roof[key]["traffic"] = bytes_per_unit * units
