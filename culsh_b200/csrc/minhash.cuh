@@ -36,6 +36,19 @@ __device__ __forceinline__ uint32_t hash_mod_prime(uint32_t a, uint32_t c, uint6
     return t < u ? t : t - 5u;                          // carried: s - p; else s
 }
 
+// The same value shifted by 5, without the final correction: returns t = (s + 5) mod 2^32 (s as
+// above) and sets `carried` when the addition wrapped, i.e. when s >= p and the result would have
+// been s - p instead of s.  That happens for about 20 of 2^32 inputs, so the row loop keeps the
+// minimum of t and a flag, and only a flagged (row, hash function) is evaluated again in full.
+__device__ __forceinline__ uint32_t hash_plus5(uint32_t a, uint32_t c, uint64_t b64, bool& carried) {
+    const uint64_t x = mad_wide_u32(a, c, b64);
+    const uint64_t y = mad_wide_u32((uint32_t)(x >> 32), 5u, (uint64_t)(uint32_t)x);
+    const uint32_t u = 5u * (uint32_t)(y >> 32) + 5u;
+    const uint32_t t = (uint32_t)y + u;
+    carried |= t < u;
+    return t;
+}
+
 // keys: [L][n_total][NW] with NW = round_key_words(4k); word j (right-aligned) = bswap32(min).
 // PL = hash functions per lane per sweep; a sweep covers 32*PL consecutive hash functions and
 // H > 256 takes several sweeps.  Slots past H hold a = b = 0, evaluate to 0 and are never stored,
@@ -63,6 +76,9 @@ minhash_kernel(const int32_t* __restrict__ indices, const int32_t* __restrict__ 
                 b[i] = h < H ? (uint64_t)B[h] : 0ull;
                 m[i] = 0xFFFFFFFFu;
             }
+            bool carried[PL];
+#pragma unroll
+            for (int i = 0; i < PL; ++i) carried[i] = false;
             for (int base = start; base < end; base += 32) {
                 const int mine = base + lane < end ? indices[base + lane] : 0;
                 const int cnt = min(32, end - base);
@@ -70,7 +86,19 @@ minhash_kernel(const int32_t* __restrict__ indices, const int32_t* __restrict__ 
                 for (int s = 0; s < cnt; ++s) {
                     const uint32_t c = (uint32_t)__shfl_sync(0xFFFFFFFFu, mine, s);
 #pragma unroll
-                    for (int i = 0; i < PL; ++i) m[i] = min(m[i], hash_mod_prime(a[i], c, b[i]));
+                    for (int i = 0; i < PL; ++i) m[i] = min(m[i], hash_plus5(a[i], c, b[i], carried[i]));
+                }
+            }
+            // m holds min(hash) + 5 unless one of the evaluations wrapped; those few are redone
+#pragma unroll
+            for (int i = 0; i < PL; ++i) {
+                if (carried[i]) {
+                    uint32_t exact = 0xFFFFFFFFu;
+                    for (int e = start; e < end; ++e)
+                        exact = min(exact, hash_mod_prime(a[i], (uint32_t)indices[e], b[i]));
+                    m[i] = exact;
+                } else if (end > start) {
+                    m[i] -= 5u;
                 }
             }
 #pragma unroll

@@ -246,6 +246,32 @@ def test_minhash_fit_query_parity(eng, n, d, L, k, density):
 # ------------------------------------------------------------------------------------------
 # Gather / dedupe paths and edge cases
 # ------------------------------------------------------------------------------------------
+def test_minhash_values_next_to_the_prime(eng):
+    """Hash parameters chosen so that a*c + b lands in [p, 2^32 + 15) before the final reduction -
+    the inputs for which the kernel's fast evaluation wraps and the row is evaluated again in full -
+    and right below p, where it must not."""
+    culsh, core_mod = eng
+    p = oracle.MINHASH_PRIME
+    L, k, d = 2, 4, 64
+    A = np.array([1, 1, 2, 3, 1, 5, 7, 4294967290], dtype=np.uint32)
+    B = np.array([p - 1, p - 3, p - 5, 5, 0, p - 2, p - 1, 17], dtype=np.uint32)
+    rows = [[3, 10], [0], [1, 2, 3, 4, 5, 6, 7], [], [2, 40, 63], [1], list(range(0, 64, 3))]
+    indptr = np.concatenate([[0], np.cumsum([len(r) for r in rows])]).astype(np.int32)
+    indices = np.array([c for r in rows for c in r], dtype=np.int32)
+    want = oracle.minhash_signatures(indices, indptr, A, B)
+    # at least one evaluation per family of cases: wraps (sum >= p) and stays (sum < p)
+    sums = A[None, :].astype(np.uint64) * indices[:, None].astype(np.uint64) + B[None, :].astype(np.uint64)
+    assert ((sums >= p) & (sums < 2**32 + 15)).any() and (sums < p).any()
+    oidx = oracle.fit_index(want, L, k)
+    ix = core_mod.MinHashIndex.load(
+        candidate_indices=oidx.candidate_indices, bucket_signatures=oidx.bucket_signatures,
+        bucket_candidate_offsets=oidx.bucket_candidate_offsets, table_bucket_offsets=oidx.table_bucket_offsets,
+        hash_a=A, hash_b=B, n_total_candidates=len(oidx.candidate_indices), n_total_buckets=oidx.n_total_buckets,
+        n_hash_tables=L, n_hashes=k, sig_nbytes=oidx.sig_nbytes, n_features=d, seed=0)
+    got = _sig_matrix(core_mod.MinHashCore(L, k, 0).hash(indices, indptr, len(rows), ix))
+    assert np.array_equal(got, want)
+
+
 def test_large_buckets_use_the_bitmap_path(eng):
     """k = 2 sign bits -> four buckets per table of ~n/4 rows: raw candidate counts far above
     the warp path's limit; heavy cross-table duplication."""
