@@ -82,7 +82,7 @@ minhash_kernel(const int32_t* __restrict__ indices, const int32_t* __restrict__ 
             for (int base = start; base < end; base += 32) {
                 const int mine = base + lane < end ? indices[base + lane] : 0;
                 const int cnt = min(32, end - base);
-#pragma unroll 4
+#pragma unroll 8
                 for (int s = 0; s < cnt; ++s) {
                     const uint32_t c = (uint32_t)__shfl_sync(0xFFFFFFFFu, mine, s);
 #pragma unroll
