@@ -512,9 +512,14 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     // with more rows than two bitmap windows, mid-sized candidate sets are sorted in shared memory
     const int mid_max = (size_t)ix.n > 2 * (size_t)wbits ? MID_MAX : 0;
     CU_CHECK(cudaMemsetAsync(n_big.p, 0, 2 * sizeof(uint32_t), s));
+    // The count pass keeps the list bounds it reads for the warp path (one coalesced read there
+    // instead of two dependent scattered ones), when the table is worth it and fits 8 GB.
+    Scratch<int2> bounds;
+    const size_t pairs = (size_t)n_q * L;
+    if (pairs >= ((size_t)1 << 22) && pairs <= ((size_t)1 << 30)) bounds.reserve(c, SL_BOUNDS, pairs);
     raw_count_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(matched, ix.bucket_offsets.p, n_q, L,
                                                                  raw_cnt.p, big_list.p, mid_list, n_big.p,
-                                                                 mid_max);
+                                                                 mid_max, bounds.p);
     KERNEL_CHECK();
     exclusive_scan<uint64_t, uint64_t>(s, raw_cnt.p, n_q, raw_off.p, scratch.p);
     uint64_t raw_total = 0;
@@ -549,7 +554,7 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     if (n_other) {
         size_t blocks = std::min<size_t>(ceil_div(n_q, SM_WARPS), (size_t)c->sm_count * 16);
         dedupe_small_kernel<<<(unsigned)blocks, SM_THREADS, 0, s>>>(
-            matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, raw_off.p, n_q, L, tmp.p, out.counts.p);
+            matched, ix.bucket_offsets.p, ix.cand.p, raw_cnt.p, raw_off.p, n_q, L, tmp.p, out.counts.p, bounds.p);
         KERNEL_CHECK();
     }
     if (nm) {

@@ -60,9 +60,11 @@ constexpr int SMALL_MAX = 512;  // largest raw count handled by the warp path
 __global__ void __launch_bounds__(256)
 raw_count_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
                  int n_q, int L, uint64_t* __restrict__ raw_cnt, uint32_t* __restrict__ big_list,
-                 uint32_t* __restrict__ mid_list, uint32_t* __restrict__ counters, int mid_max) {
+                 uint32_t* __restrict__ mid_list, uint32_t* __restrict__ counters, int mid_max,
+                 int2* __restrict__ bounds /* or null: [n_q][L] list bounds for the warp path */) {
     int q = blockIdx.x * blockDim.x + threadIdx.x;
     if (q >= n_q) return;
+    int2* bq = bounds ? bounds + (size_t)q * L : nullptr;
     // eight tables at a time, branch-free, so that the dependent loads (bucket id -> bounds) of
     // different tables are in flight together
     uint64_t c = 0;
@@ -79,11 +81,17 @@ raw_count_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict_
             hi[j] = bucket_offsets[bb + 1];
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) c += b[j] >= 0 ? (uint64_t)(hi[j] - lo[j]) : 0ull;
+        for (int j = 0; j < 8; ++j) {
+            c += b[j] >= 0 ? (uint64_t)(hi[j] - lo[j]) : 0ull;
+            if (bq) bq[t + j] = b[j] >= 0 ? make_int2(lo[j], hi[j]) : make_int2(0, 0);
+        }
     }
     for (; t < L; ++t) {
         const int b = mq[t];
-        if (b >= 0) c += (uint64_t)(bucket_offsets[b + 1] - bucket_offsets[b]);
+        int lo = 0, hi = 0;
+        if (b >= 0) { lo = bucket_offsets[b]; hi = bucket_offsets[b + 1]; }
+        c += (uint64_t)(hi - lo);
+        if (bq) bq[t] = make_int2(lo, hi);
     }
     raw_cnt[q] = c;
     if (c > SMALL_MAX) {
@@ -161,7 +169,8 @@ __global__ void __launch_bounds__(SM_THREADS)
 dedupe_small_kernel(const int32_t* __restrict__ matched, const int32_t* __restrict__ bucket_offsets,
                     const int32_t* __restrict__ cand, const uint64_t* __restrict__ raw_cnt,
                     const uint64_t* __restrict__ raw_off, int n_q, int L, int32_t* __restrict__ tmp,
-                    uint64_t* __restrict__ uniq_cnt) {
+                    uint64_t* __restrict__ uniq_cnt,
+                    const int2* __restrict__ bounds /* or null: list bounds kept by raw_count_kernel */) {
     __shared__ int32_t s_buf[SM_WARPS][SMALL_MAX];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int32_t* buf = s_buf[warp];
@@ -181,9 +190,13 @@ dedupe_small_kernel(const int32_t* __restrict__ matched, const int32_t* __restri
         int fill = 0;
         for (int t0 = 0; t0 < L; t0 += 32) {
             const int t = t0 + lane;
-            const int b = t < L ? matched[(size_t)q * L + t] : -1;
             int s = 0, e = 0;
-            if (b >= 0) { s = bucket_offsets[b]; e = bucket_offsets[b + 1]; }
+            if (bounds) {  // one coalesced read instead of two dependent, scattered ones
+                if (t < L) { const int2 be = bounds[(size_t)q * L + t]; s = be.x; e = be.y; }
+            } else {
+                const int b = t < L ? matched[(size_t)q * L + t] : -1;
+                if (b >= 0) { s = bucket_offsets[b]; e = bucket_offsets[b + 1]; }
+            }
             const int len = e - s;
             int inc = len;
 #pragma unroll

@@ -116,6 +116,26 @@ def test_rplsh_fit_query_self_join_and_batches(eng):
     assert np.array_equal(c.get_indices(), b.get_indices())
 
 
+def test_count_pass_bounds_feed_the_warp_path(eng):
+    """From 2^22 (query, table) pairs on, the count pass keeps the list bounds it reads and the warp
+    dedupe path takes them from there; smaller batches fetch them through the bucket ids.  Both
+    ways, and the self-join, must give the same CSR."""
+    culsh, _ = eng
+    rng = np.random.RandomState(17)
+    n, d, L, k = 140_000, 16, 32, 22
+    X = rng.randn(n, d).astype(np.float32)
+    lsh = culsh.RPLSH(L, k, seed=5)
+    model = lsh.fit(X)
+    whole = model.query(X)                       # 4.48 M pairs in one batch
+    parts = model.query(X, batch_size=50_000)    # 1.6 M pairs per batch
+    joined = lsh.fit_query(X)
+    for f in ("get_indices", "get_offsets", "get_counts"):
+        assert np.array_equal(getattr(whole, f)(), getattr(parts, f)())
+        assert np.array_equal(getattr(whole, f)(), getattr(joined, f)())
+    counts = whole.get_counts().astype(np.int64)
+    assert counts.min() >= 1 and (counts <= 256).mean() > 0.5  # the warp path carries most of this case
+
+
 def test_rplsh_zero_rows_take_the_sign_bit_rule(eng):
     """x.p == +0.0 hashes to 1 (sign bit clear), as upstream's kernel; upstream's Python oracle
     (x > 0) would give 0."""
