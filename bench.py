@@ -456,6 +456,7 @@ def run_ours(args, wl, spec):
                           else f"inputs ({in_bytes >> 10} KB) fit L2: small configuration, no flush"),
                    "parallelism": f"row-sharded x{world}, peer-memory candidate exchange fused with the merge" if world > 1 else "single GPU"},
         "fit_rows_per_s": total_rows / (fit_ms * 1e-3),
+        "hash_rows_per_s": (total_rows / (hash_ms * 1e-3)) if hash_ms > 0 else None,
         "query_qps": (nq / (q_ms * 1e-3)) if q_ms > 0 else None,
         "stage_ms": {"fit_total": fit_ms, "hash": hash_ms, "sort": mean("sort_ms", "fit"),
                      "sort_scatter_last_pass": scatter_ms, "build": mean("build_ms", "fit"),
