@@ -27,6 +27,16 @@ over NVLink (NCCL carries only two one-word all-reduces per step as barriers).
 `--impl reference` times upstream cuLSH's own CUDA build (oracle/_ref, compiled from the
 upstream sources by oracle/Makefile) on the same workload when that module loads, else the
 NumPy restatement of the path on the host cores.
+
+Every fit in the timed regions generates its hash parameters again (the per-handle parameter
+cache is switched off), as upstream does; `cached_params` gives the same step with the cache
+on, `first_call_ms` the very first step of the process (cold scratch, cold allocator).
+
+Outside the timed regions both arms add `parity` (number of candidates and a checksum of the
+CSR of one step), and this arm, when upstream's build loads, counts the signature elements on
+which the two builds disagree and whether each lies inside the 1e-5 rounding band.  With the
+default workload the line also carries `extra`: a few steps of c4 (one 12.5M-row shard per
+GPU) and of the c5 self-join (10M rows over all GPUs).
 """
 import argparse
 import json
@@ -79,7 +89,13 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
-        self.gpu = gpu_index
+        # nvidia-smi numbers GPUs physically, CUDA numbers the visible ones: address by UUID
+        self.gpu = str(gpu_index)
+        try:
+            import torch
+            self.gpu = "GPU-" + str(torch.cuda.get_device_properties(gpu_index).uuid)
+        except Exception:
+            pass
         self.proc = None
         self.lines = []
 
@@ -244,25 +260,127 @@ def measure_tf32_peak(torch, device):
         torch.backends.cuda.matmul.allow_tf32 = old
 
 
-def cpu_baseline(sample_rows=200_000, sample_queries=2_000):
-    """NumPy restatement of the path (oracle/) on a bounded sample of the c2 workload."""
+CPU_SAMPLES = {  # bounded samples of each workload for the CPU leg: (rows, queries)
+    "c1": (10_000, 100), "c2": (200_000, 2_000), "c3": (20_000, 500), "c4": (200_000, 2_000),
+    "c5": (100_000, 0),
+}
+
+
+def cpu_baseline(wl="c2"):
+    """NumPy restatement of the path (oracle/) on a bounded sample of workload `wl`: same value
+    law (the sample is drawn by make_inputs on the CPU), same tables x hashes, hash parameters
+    from NumPy's generator."""
+    import torch
     from oracle import oracle
-    s = WORKLOADS["c2"]
-    rng = np.random.default_rng(100)
-    X = np.clip(np.round(rng.gamma(0.5, 40.0, (sample_rows, s["d"]))), 0, 255).astype(np.float32)
-    Q = np.clip(np.round(rng.gamma(0.5, 40.0, (sample_queries, s["d"]))), 0, 255).astype(np.float32)
-    P = np.random.default_rng(0).standard_normal((s["L"] * s["k"], s["d"])).astype(np.float32)
+    spec = dict(WORKLOADS[wl])
+    rows, queries = CPU_SAMPLES[wl]
+    spec["n"], spec["nq"] = min(rows, spec["n"]), min(queries, spec["nq"])
+    n, nq, L, k, d = spec["n"], spec["nq"], spec["L"], spec["k"], spec["d"]
+    X, Q = make_inputs(torch, torch.device("cpu"), 0, wl, spec)
+    as_np = lambda t: None if t is None else (tuple(x.numpy() for x in t) if isinstance(t, tuple) else t.numpy())  # noqa: E731
+    X, Q = as_np(X), as_np(Q)
+    H = L * k
+    rng = np.random.default_rng(spec["seed"])
+    if spec["family"] == "minhash":
+        A, B = oracle.minhash_normalize(rng.integers(0, 1 << 32, H, dtype=np.uint64),
+                                        rng.integers(0, 1 << 32, H, dtype=np.uint64))
+        hash_fn = lambda M: oracle.minhash_signatures(M[0], M[1], A, B)  # noqa: E731
+    elif spec["family"] == "rplsh":
+        P = rng.standard_normal((H, d)).astype(np.float32)
+        hash_fn = lambda M: (~np.signbit(M @ P.T)).astype(np.uint8)  # noqa: E731
+    else:
+        P = (rng.standard_normal((H, d)) / spec["w"]).astype(np.float32)
+        bias = rng.uniform(0.0, 1.0, H).astype(np.float32)
+        hash_fn = lambda M: np.floor(M @ P.T + bias[None, :]).astype(np.int32)  # noqa: E731
     t0 = time.perf_counter()
-    bits = (~np.signbit(X @ P.T)).astype(np.uint8)
-    tables = oracle.fast_fit_packed(oracle.pack_bits_msb_first(bits, s["L"], s["k"]))
-    t1 = time.perf_counter()
-    qbits = (~np.signbit(Q @ P.T)).astype(np.uint8)
-    oracle.fast_query_packed(tables, oracle.pack_bits_msb_first(qbits, s["L"], s["k"]))
+    sig_x = hash_fn(X)
+    if spec["mode"] == "fit_query":
+        kx, kq = oracle.signature_keys(sig_x, sig_x[:0], L, k)
+        tables = oracle.fast_fit_packed(kx)
+        t1 = time.perf_counter()
+        oracle.fast_query_packed(tables, kx)
+        nq_run = n
+    else:
+        sig_q = hash_fn(Q)
+        kx, kq = oracle.signature_keys(sig_x, sig_q, L, k)
+        tables = oracle.fast_fit_packed(kx)
+        t1 = time.perf_counter()
+        oracle.fast_query_packed(tables, kq)
+        nq_run = nq
     t2 = time.perf_counter()
-    return {"value": sample_rows / (t2 - t0), "unit": "rows/s", "cores": os.cpu_count(), "kind": "port",
-            "fit_rows_per_s": sample_rows / (t1 - t0), "query_qps": sample_queries / (t2 - t1),
-            "sample": f"{sample_rows} rows + {sample_queries} queries of the c2 law, same 32x16 RPLSH "
-                      f"(NumPy matmul/argsort/searchsorted/unique, BLAS threads = all cores)"}
+    return {"value": n / (t2 - t0), "unit": "rows/s", "cores": os.cpu_count(), "kind": "port",
+            "fit_rows_per_s": n / (t1 - t0), "query_qps": nq_run / max(t2 - t1, 1e-9),
+            "sample": f"{n} rows + {nq_run} queries of the {wl} law, same {L}x{k} {spec['family']} "
+                      f"(NumPy matmul / argsort / searchsorted / unique, BLAS threads = all cores)"}
+
+
+# ------------------------------------------------------------------------------------------
+# result checks (outside the timed regions)
+# ------------------------------------------------------------------------------------------
+CHECKSUM_MOD = (1 << 61) - 1
+
+
+def csr_checksum(torch, indices, offsets, device):
+    """sum over (query q, candidate id) of id * (q + 1), mod 2^61 - 1, on the device.
+    `indices` / `offsets` are torch tensors or NumPy arrays (int32 / 64-bit)."""
+    if not torch.is_tensor(offsets):
+        offsets = torch.from_numpy(np.ascontiguousarray(offsets).view(np.int64))
+    offsets = offsets.to(device=device, dtype=torch.int64)
+    total = int(offsets[-1].item())
+    acc, step = 0, 1 << 26
+    for lo in range(0, total, step):
+        hi = min(total, lo + step)
+        chunk = indices[lo:hi]
+        if not torch.is_tensor(chunk):
+            chunk = torch.from_numpy(np.ascontiguousarray(chunk))
+        ids = chunk.to(device=device, dtype=torch.int64)
+        pos = torch.arange(lo, hi, device=device, dtype=torch.int64)
+        q = torch.searchsorted(offsets, pos, right=True)  # = query index + 1
+        acc = (acc + int(((ids * q) % CHECKSUM_MOD).sum().item())) % CHECKSUM_MOD
+    return acc
+
+
+def row_signatures(torch, device, ix, n, L):
+    """uint8 [L, n, s]: raw signature bytes of every (table, row), recovered from an index's
+    four arrays (either implementation's getters)."""
+    s = int(ix.sig_nbytes)
+    bco = torch.from_numpy(ix.get_bucket_candidate_offsets()).to(device).long()
+    bs = torch.from_numpy(ix.get_bucket_signatures()).to(device).view(-1, s)
+    cand = torch.from_numpy(ix.get_candidate_indices()).to(device).long()
+    B = bco.numel() - 1
+    bucket_of_item = torch.repeat_interleave(torch.arange(B, device=device), bco[1:] - bco[:-1])
+    out = torch.empty((L * n, s), dtype=torch.uint8, device=device)
+    table = torch.arange(n * L, device=device) // n
+    out[table * n + cand] = bs[bucket_of_item]
+    return out.view(L, n, s)
+
+
+def signature_mismatch(torch, family, sig_a, sig_b, X, P, bias, k, rel=1e-5):
+    """Compare two [L, n, s] signature arrays element by element (k elements per signature) and
+    classify every differing element by a float64 recomputation of its projection: inside the
+    band when |x.p| <= rel * sum|x_i p_i| (RPLSH) or dist(x.p + b, Z) <= rel * max(1, sum|x_i
+    p_i| + |b|) (p-stable).  Returns counts and the rows that hold a differing element."""
+    L, n, s = sig_a.shape
+    eb = s // k
+    differ = (sig_a.view(L, n, k, eb) != sig_b.view(L, n, k, eb)).any(dim=3)
+    where = differ.nonzero()
+    m = int(where.shape[0])
+    in_band = 0
+    for lo in range(0, m, 1 << 16):
+        t, row, j = where[lo:lo + (1 << 16)].unbind(1)
+        h = t * k + j
+        x, p = X[row].double(), P[h].double()
+        v, scale = (x * p).sum(1), (x.abs() * p.abs()).sum(1)
+        if family == "rplsh":
+            ok = v.abs() <= rel * scale
+        else:
+            b = bias[h].double()
+            v = v + b
+            ok = (v - torch.round(v)).abs() <= rel * torch.clamp(scale + b.abs(), min=1.0)
+        in_band += int(ok.sum().item())
+    rows = torch.unique(where[:, 1]) if m else where.new_zeros(0)
+    return {"elements": int(L * n * k), "mismatch": m, "in_band": in_band, "out_of_band": m - in_band,
+            "rows": rows}
 
 
 def dist_setup():
@@ -322,75 +440,203 @@ def read_back(cand):
     return a.nbytes + b.nbytes + c.nbytes
 
 
+def config_of(wl, spec):
+    """The same dict in both arms."""
+    return {"workload": spec["name"], "id": wl, "rows_per_gpu": spec["n"], "queries": spec["nq"],
+            "seed": spec["seed"]}
+
+
 # ------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------
-def run_ours(args, wl, spec):
-    import torch
-    world, rank, local = dist_setup()
-    device = torch.device(f"cuda:{local}")
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels,
+# from ncu captures of launches of exactly this size (summaries and commands under profiles/);
+# a workload or size without a capture reports null.
+NCU_TRAFFIC = {}
+
+
+def check_exchange(torch, world, rank, n, local_cand, merged, span):
+    """After an exchange every rank checks its merged slice: ids ascending inside a query, ids of
+    shard r inside r's row range, per-query count equal to the sum of the per-shard counts,
+    and for one query per rank the merged list equal to the shards' lists laid end to end."""
+    import torch.distributed as dist
+    from culsh_b200 import sharded
+    lo, hi = span
+    problems = []
+    idx, off = sharded._csr_tensors(merged)
+    l_idx, l_off = sharded._csr_tensors(local_cand)
+    counts = (l_off[1:] - l_off[:-1]).contiguous()
+    total = counts.clone()
+    dist.all_reduce(total)
+    mine = off[1:] - off[:-1]
+    if mine.numel() != hi - lo or not bool((mine == total[lo:hi]).all()):
+        problems.append("per-query counts differ from the sum over shards")
+    if idx.numel():
+        if int(idx.min()) < 0 or int(idx.max()) >= n * world:
+            problems.append("id outside the global row range")
+        d = idx[1:] > idx[:-1]
+        starts = off[1:-1]
+        starts = starts[(starts > 0) & (starts < idx.numel())]
+        d[starts - 1] = True
+        if not bool(d.all()):
+            problems.append("ids not strictly ascending inside a query")
+    for j in range(world):  # rank j's first query, gathered from every shard
+        qj = sharded.shard_bounds(local_cand.n_queries, world, j)[0]
+        piece = (l_idx[int(l_off[qj]):int(l_off[qj + 1])].long() + rank * n).cpu()
+        parts = [None] * world
+        dist.all_gather_object(parts, piece)
+        if j == rank and hi > lo:
+            want = torch.cat(parts)
+            got = idx[int(off[0]):int(off[1])].long().cpu()
+            if want.numel() != got.numel() or not bool((want == got).all()):
+                problems.append(f"query {qj}: merged list differs from the shards' lists")
+    flag = torch.tensor([len(problems)], device=idx.device if idx.numel() else off.device)
+    dist.all_reduce(flag)
+    return "ok" if int(flag.item()) == 0 else ("FAILED: " + "; ".join(problems) if problems else "FAILED on another rank")
+
+
+def run_workload(torch, args, wl, spec, world, rank, local, exchange, steps, warmup, e2e=True, checks=True):
+    """Times `steps` steps of one workload on this rank (collectively at world > 1) and returns
+    the measurements; rank 0 turns them into the JSON line."""
     from culsh_b200 import _culsh_core, sharded
-    if wl == "c5" and world > 1:
-        raise SystemExit("workload c5 is single-GPU in this benchmark")
-    n, nq = spec["n"], spec["nq"]
-    Xd, Qd = make_inputs(torch, device, rank, wl, spec)
-    core = make_core(_culsh_core, spec)
+    import culsh_b200
+    device = torch.device(f"cuda:{local}")
+    sharded_join = spec["mode"] == "fit_query" and world > 1
+    if sharded_join:  # strong scaling: the rows of the one data set are cut over the ranks
+        lo, hi = sharded.shard_bounds(spec["n"], world, rank)
+        full = dict(spec)
+        Xd, Qd = make_inputs(torch, device, 0, wl, full)
+        Xd = Xd[lo:hi].contiguous()
+        n = hi - lo
+    else:
+        Xd, Qd = make_inputs(torch, device, rank, wl, spec)
+        n = spec["n"]
+    nq = spec["nq"]
+    spec_local = dict(spec, n=n)
+    core = make_core(_culsh_core, spec_local)
     core.set_profiling(True)
     batch = nq if wl == "c2" else None
     stage = {"fit": [], "query": []}
-    exchange = sharded.PeerExchange(device=local) if world > 1 else None
+    keep = {}
 
     def step(X, Q, host_out):
-        if spec["mode"] == "fit_query":
+        if sharded_join:
+            est = culsh_b200.RPLSH(spec["L"], spec["k"], seed=spec["seed"])
+            cand, _ = sharded.fit_query_sharded(est, X, exchange)
+            s_fit = core.last_stats()
+            s_q = dict(s_fit, total_ms=0.0, hash_ms=0.0, lookup_ms=0.0, launches=0)
+        elif spec["mode"] == "fit_query":
             cand = core.fit_query_float(X, n, spec["d"])
             s_fit = core.last_stats()
             s_q = dict(s_fit, total_ms=0.0, hash_ms=0.0, lookup_ms=0.0, launches=0)
         else:
-            index = core_fit(core, spec, X)
+            index = core_fit(core, spec_local, X)
             s_fit = core.last_stats()
-            cand = core_query(core, spec, Q, index, batch)
+            cand = core_query(core, spec_local, Q, index, batch)
             s_q = core.last_stats()
             if world > 1:  # each rank pulls the lists of its slice of the queries from its peers
-                cand, _ = exchange.exchange(cand, [r * n for r in range(world)])
+                keep["local"] = cand
+                cand, keep["span"] = exchange.exchange(cand, [r * n for r in range(world)])
+        keep["cand"] = cand
         return s_fit, s_q, (read_back(cand) if host_out else 0)
 
-    for _ in range(args.warmup):
-        step(Xd, Qd, False)
-    sampler = ClockSampler(local)
+    out = {"n": n, "nq": nq, "device": device, "in_bytes": nbytes_of(Xd), "nnz": int(Xd[0].numel()) if isinstance(Xd, tuple) else 0}
     barrier(torch, world)
-    sampler.start()
     t0 = time.perf_counter()
-    launches = 0
-    for _ in range(args.steps):
-        s_fit, s_q, _ = step(Xd, Qd, False)
-        stage["fit"].append(s_fit)
-        stage["query"].append(s_q)
-        launches += s_fit["launches"] + s_q["launches"]
+    step(Xd, Qd, False)
     barrier(torch, world)
-    t_dev = max_over_ranks(torch, time.perf_counter() - t0, world, device)
-    clocks = sampler.stop()
+    out["first_call_ms"] = max_over_ranks(torch, time.perf_counter() - t0, world, device) * 1e3
 
-    # end to end: pinned host arrays in, CSR read back to the host
-    d2h, h2d = 0, 0
-    t_e2e = float("nan")
-    if not args.skip_e2e:
-        Xh, Qh = to_pinned_host(torch, Xd), to_pinned_host(torch, Qd)
-        h2d = nbytes_of(Xh) + nbytes_of(Qh)
-        for _ in range(2):
-            step(Xh, Qh, True)
+    def timed(n_warm, n_steps, X, Q, host_out, record):
+        for _ in range(n_warm):
+            step(X, Q, host_out)
         barrier(torch, world)
         t0 = time.perf_counter()
-        for _ in range(args.steps):
-            _, _, b = step(Xh, Qh, True)
-            d2h = max(d2h, b)
+        launches, moved = 0, 0
+        for _ in range(n_steps):
+            s_fit, s_q, b = step(X, Q, host_out)
+            moved = max(moved, b)
+            if record:
+                stage["fit"].append(s_fit)
+                stage["query"].append(s_q)
+                launches += s_fit["launches"] + s_q["launches"]
         barrier(torch, world)
-        t_e2e = max_over_ranks(torch, time.perf_counter() - t0, world, device)
+        return max_over_ranks(torch, time.perf_counter() - t0, world, device), launches, moved
 
-    if rank != 0:
-        return
-    peaks = load_peaks()
+    # same step with the per-handle parameter cache on (a repeated fit with one seed)
+    out["t_cached"], _, _ = timed(warmup, max(3, steps // 5), Xd, Qd, False, False)
+    core.set_param_cache(False)   # from here on every fit generates its parameters, as upstream does
+    sampler = ClockSampler(local)
+    for _ in range(warmup):
+        step(Xd, Qd, False)
+    barrier(torch, world)
+    sampler.start()
+    out["t_dev"], out["launches"], _ = timed(0, steps, Xd, Qd, False, True)
+    out["clocks"] = sampler.stop()
+    out["stage"] = stage
+
+    out["exchange_check"] = None
+    if world > 1 and checks and not sharded_join:
+        out["exchange_check"] = check_exchange(torch, world, rank, n, keep["local"], keep["cand"], keep["span"])
+
+    out["parity"] = None
+    if checks and world == 1:
+        cand = keep["cand"]
+        idx, off = sharded._csr_tensors(cand)
+        out["parity"] = {"unique_candidates": int(cand.n_total_candidates),
+                         "csr_checksum": csr_checksum(torch, idx, off, device)}
+        out["parity"].update(parity_against_reference(torch, wl, spec_local, core, Xd, device))
+    keep.clear()
+
+    out["t_e2e"], out["h2d"], out["d2h"] = float("nan"), 0, 0
+    if e2e:
+        Xh, Qh = to_pinned_host(torch, Xd), to_pinned_host(torch, Qd)
+        out["h2d"] = nbytes_of(Xh) + nbytes_of(Qh)
+        out["t_e2e"], _, out["d2h"] = timed(2, steps, Xh, Qh, True, False)
+    core.set_param_cache(True)
+    return out
+
+
+def parity_against_reference(torch, wl, spec, core, Xd, device):
+    """When upstream's CUDA build (oracle/_ref) loads: fit the same rows with it and compare the
+    stored signatures of the two indexes element by element (dense families), or the four
+    index arrays (MinHash)."""
+    ref = load_reference_module()
+    n, L, k = spec["n"], spec["L"], spec["k"]
+    sig_bytes = k * (1 if spec["family"] == "rplsh" else 4)
+    if ref is None:
+        return {"reference": "upstream build not loadable"}
+    if float(n) * L * sig_bytes > 8e9:
+        return {"reference": "skipped: signature arrays above 8 GB (covered at reduced size by tests/)"}
+    torch.cuda.synchronize()
+    ours = core_fit(core, spec, Xd)
+    theirs = core_fit(make_core(ref, spec), spec, Xd)
+    if spec["family"] == "minhash":
+        same = all(np.array_equal(getattr(ours, g)(), getattr(theirs, g)())
+                   for g in ("get_table_bucket_offsets", "get_bucket_candidate_offsets",
+                             "get_bucket_signatures", "get_candidate_indices", "get_hash_a", "get_hash_b"))
+        return {"reference": "upstream CUDA build, same rows", "index_arrays_equal": bool(same)}
+    P_ours, P_ref = ours.get_projection_matrix(), theirs.get_projection_matrix()
+    params_equal = bool(np.array_equal(P_ours, P_ref))
+    bias = None
+    if spec["family"] == "pslsh":
+        params_equal = params_equal and bool(np.array_equal(ours.get_bias(), theirs.get_bias()))
+        bias = torch.from_numpy(theirs.get_bias()).to(device)
+    P = torch.from_numpy(P_ref).to(device).view(L * k, spec["d"])
+    mm = signature_mismatch(torch, spec["family"], row_signatures(torch, device, theirs, n, L),
+                            row_signatures(torch, device, ours, n, L), Xd, P, bias, k)
+    return {"reference": "upstream CUDA build, same rows", "hash_parameters_equal": params_equal,
+            "sig_elements": mm["elements"], "sig_mismatch_in_band": mm["in_band"],
+            "sig_mismatch_out_of_band": mm["out_of_band"], "rows_with_mismatch": int(mm["rows"].numel())}
+
+
+def line_of(torch, args, wl, spec, world, m, peaks, tf32):
+    """The JSON line of one measured workload."""
+    steps, stage = m["steps"], m["stage"]
+    n, nq = m["n"], m["nq"]
     mean = lambda key, which: statistics.mean(s[key] for s in stage[which])  # noqa: E731
-    total_rows = n * world
+    sharded_join = spec["mode"] == "fit_query" and world > 1
+    total_rows = spec["n"] if sharded_join else n * world
     fit_ms, hash_ms, scatter_ms = mean("total_ms", "fit"), mean("hash_ms", "fit"), mean("scatter_ms", "fit")
     q_ms, gather_ms = mean("total_ms", "query"), mean("gather_ms", "query")
     sf, sq = stage["fit"][-1], stage["query"][-1]
@@ -398,7 +644,7 @@ def run_ours(args, wl, spec):
     items, kb = sf["n_items"], 4 * sf["key_words"]
     roof = {}
     if spec["family"] == "minhash":
-        nnz = int(Xd[0].numel())
+        nnz = m["nnz"]
         evals = float(nnz) * spec["L"] * spec["k"]
         hbytes = 4.0 * nnz + 4.0 * (n + 1) + 4.0 * n * spec["L"] * sf["key_words"]
         roof["hash"] = {"bound": "hbm", "achieved": hbytes / (hash_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
@@ -406,59 +652,57 @@ def run_ours(args, wl, spec):
                         "note": "integer-issue bound by nature: 4*nnz + 4*(n+1) + 4*n*L*NW bytes over the event "
                                 "time; hash evaluations/s in hash_evals_per_s",
                         "hash_evals_per_s": evals / (hash_ms * 1e-3)}
-    else:
-        tf32 = measure_tf32_peak(torch, device) if not args.skip_cpu else 700.0
+    elif hash_ms > 0:
         flops = 2.0 * n * spec["d"] * spec["L"] * spec["k"]
         roof["hash"] = {"bound": "tensor", "achieved": flops / (hash_ms * 1e-3) / 1e12, "peak": tf32 / 3.0,
                         "unit": "TFLOP/s", "traffic": None,
                         "kernel": "project_tc_kernel" if sf["hash_path"] == 1 else "project_simt_kernel",
                         "note": "fp32-equivalent flop 2*n*d*H over the CUDA-event time of the projection "
-                                "launch; peak = TF32 dense matmul measured in this run (8192^3) / 3 (3xTF32; "
-                                "tiles whose low part is zero issue 2 of the 3 MMAs)",
+                                "launch; peak = TF32 dense matmul measured in this run (8192^3) / 3 (3xTF32)",
                         "tf32_tflops_measured": tf32}
-    roof["sort"] = {"bound": "hbm", "achieved": items * (kb + 4) * 2.0 / (scatter_ms * 1e-3) / 1e9,
-                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "kernel": "radix_scatter_kernel", "traffic": None,
-                    "note": f"(key {kb} B + row id 4 B) read + written per item, one launch (the scatter of the "
-                            f"last of {passes} passes) timed with CUDA events; peak {peaks['source']}"}
+    if scatter_ms > 0:
+        roof["sort"] = {"bound": "hbm", "achieved": items * (kb + 4) * 2.0 / (scatter_ms * 1e-3) / 1e9,
+                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "kernel": "radix_scatter_kernel", "traffic": None,
+                        "note": f"(key {kb} B + row id 4 B) read + written per item, one launch (the scatter of the "
+                                f"last of {passes} passes) timed with CUDA events; peak {peaks['source']}"}
     dedupe_ms = mean("dedupe_ms", "query")
     if dedupe_ms > 0:
         roof["gather"] = {"bound": "hbm", "peak": peaks["hbm_gbs"], "unit": "GB/s", "traffic": None,
                           "achieved": 4.0 * (sq["raw_candidates"] + sq["unique_candidates"]) / (dedupe_ms * 1e-3) / 1e9,
-                          "kernel": "dedupe_chained_rank_kernel",
-                          "note": "4 B per raw candidate id read + 4 B per unique id written (the second walk "
-                                  "over the lists is an L2 re-read), over the CUDA-event time of the dedupe "
-                                  f"launch alone; peak {peaks['source']}"}
-    if wl == "c2":
-        # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) measured by ncu on the
-        # 400,000-row case of this workload and scaled by the units a launch processes; the
-        # captures and their commands are summarised under profiles/.
-        per_unit = {"hash": ((205.4e6 + 38.3e6) / 400000.0, n),                 # per row
-                    "sort": ((105.7e6 + 52.7e6) / 12.8e6, items),                # per (row, table) pair
-                    "gather": ((81.5e6 + 238.4e6) / 74.3e6, sq["raw_candidates"])}  # per raw candidate id
-        for key, (bytes_per_unit, units) in per_unit.items():
-            if key in roof:
-                roof[key]["traffic"] = bytes_per_unit * units
-                roof[key]["traffic_note"] = "ncu DRAM bytes of the 400,000-row capture scaled to this launch"
-    for r in roof.values():
+                          "kernel": "dedupe kernel of the gather (chained rank / bitmap / warp path)",
+                          "note": "4 B per raw candidate id read + 4 B per unique id written, over the CUDA-event "
+                                  f"time of the dedupe launch alone; peak {peaks['source']}"}
+    for key, r in roof.items():
         r["frac"] = r["achieved"] / r["peak"]
-    # the stage whose kernel takes the largest share of the step
-    shares = {"hash": hash_ms, "sort": scatter_ms * passes, "gather": dedupe_ms if "gather" in roof else 0.0}
-    dominant = roof[max(shares, key=shares.get)]
-    in_bytes = nbytes_of(Xd)
+        traffic = NCU_TRAFFIC.get((wl, n), {}).get(key)
+        r["traffic"] = traffic
+        r["traffic_note"] = ("ncu DRAM bytes of one launch of this size (profiles/)" if traffic is not None
+                             else "no ncu capture of a launch of this size")
+    shares = {"hash": hash_ms if "hash" in roof else 0.0, "sort": scatter_ms * passes if "sort" in roof else 0.0,
+              "gather": dedupe_ms if "gather" in roof else 0.0}
+    dominant = roof[max(shares, key=shares.get)] if roof else None
+    t_dev = m["t_dev"]
+    in_bytes = m["in_bytes"]
     line = {
         "metric": METRICS[wl],
-        "value": total_rows / (t_dev / args.steps), "unit": "rows/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_dev / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "value": total_rows / (t_dev / steps), "unit": "rows/s",
+        "n_gpus": world, "steps": steps, "warmup": m["warmup"], "ms_per_step": t_dev / steps * 1e3,
+        "higher_is_better": True, "scaling": "strong" if sharded_join else "weak", "vs_baseline": None,
         "dtype": "u32" if spec["family"] == "minhash" else "f32", "data": "synthetic",
-        "config": {"workload": spec["name"], "id": wl, "rows_per_gpu": n, "queries": nq, "seed": spec["seed"],
-                   "l2": (f"inputs ({in_bytes >> 20} MB per step) larger than L2, no flush" if in_bytes > (130 << 20)
-                          else f"inputs ({in_bytes >> 10} KB) fit L2: small configuration, no flush"),
-                   "parallelism": f"row-sharded x{world}, peer-memory candidate exchange fused with the merge" if world > 1 else "single GPU"},
-        "fit_rows_per_s": total_rows / (fit_ms * 1e-3),
+        "config": config_of(wl, spec),
+        "l2": (f"inputs ({in_bytes >> 20} MB per step) larger than L2, no flush" if in_bytes > (130 << 20)
+               else f"inputs ({in_bytes >> 10} KB) fit L2: small configuration, no flush"),
+        "parallelism": (f"row-sharded x{world}, peer-memory candidate exchange fused with the merge"
+                        if world > 1 else "single GPU"),
+        "hash_parameters": "generated by every fit inside the timed region (parameter cache off)",
+        "cached_params": {"ms_per_step": m["t_cached"] / max(3, steps // 5) * 1e3,
+                          "note": "same step with the per-handle parameter cache on"},
+        "first_call_ms": m["first_call_ms"],
+        "fit_rows_per_s": total_rows / ((fit_ms + mean("params_ms", "fit")) * 1e-3),
         "hash_rows_per_s": (total_rows / (hash_ms * 1e-3)) if hash_ms > 0 else None,
         "query_qps": (nq / (q_ms * 1e-3)) if q_ms > 0 else None,
-        "stage_ms": {"fit_total": fit_ms, "hash": hash_ms, "sort": mean("sort_ms", "fit"),
+        "stage_ms": {"params": mean("params_ms", "fit"), "fit_total": fit_ms, "hash": hash_ms,
+                     "sort": mean("sort_ms", "fit"),
                      "sort_scatter_last_pass": scatter_ms, "build": mean("build_ms", "fit"),
                      "query_total": q_ms, "query_hash": mean("hash_ms", "query"),
                      "lookup": mean("lookup_ms", "query"), "gather": gather_ms, "gather_dedupe_kernel": dedupe_ms},
@@ -466,13 +710,51 @@ def run_ours(args, wl, spec):
                   "unique_candidates": sq["unique_candidates"], "key_words": sf["key_words"],
                   "elem_bytes": sf["elem_bytes"], "sort_passes": passes},
         "roofline": dominant, "roofline_all": roof,
-        "e2e": {"value": total_rows / (t_e2e / args.steps), "unit": "rows/s",
-                "ms_per_step": t_e2e / args.steps * 1e3,
-                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
-        "gpu_launches": launches, "clocks": clocks,
+        "e2e": {"value": total_rows / (m["t_e2e"] / steps), "unit": "rows/s",
+                "ms_per_step": m["t_e2e"] / steps * 1e3,
+                "h2d_bytes_per_step": int(m["h2d"]), "d2h_bytes_per_step": int(m["d2h"])},
+        "gpu_launches": m["launches"], "clocks": m["clocks"],
     }
+    if m["parity"] is not None:
+        line["parity"] = m["parity"]
+    if m["exchange_check"] is not None:
+        line["exchange_check"] = m["exchange_check"]
+    return line
+
+
+def run_ours(args, wl, spec):
+    import torch
+    world, rank, local = dist_setup()
+    device = torch.device(f"cuda:{local}")
+    from culsh_b200 import sharded
+    exchange = sharded.PeerExchange(device=local) if world > 1 else None
+    m = run_workload(torch, args, wl, spec, world, rank, local, exchange, args.steps, args.warmup,
+                     e2e=not args.skip_e2e)
+    m["steps"], m["warmup"] = args.steps, args.warmup
+    extra = {}
+    if wl == "c2" and args.rows is None and not args.no_extra:
+        torch.cuda.empty_cache()
+        for ew in ("c4", "c5"):
+            em = run_workload(torch, args, ew, dict(WORKLOADS[ew]), world, rank, local, exchange, 5, 3,
+                              e2e=False, checks=False)
+            em["steps"], em["warmup"] = 5, 3
+            extra[ew] = em
+            torch.cuda.empty_cache()
+    if exchange is not None:
+        exchange.close()
+    if rank != 0:
+        return
+    peaks = load_peaks()
+    tf32 = measure_tf32_peak(torch, device)
+    line = line_of(torch, args, wl, spec, world, m, peaks, tf32)
+    if extra:
+        line["extra"] = {}
+        for ew, em in extra.items():
+            el = line_of(torch, args, ew, dict(WORKLOADS[ew]), world, em, peaks, tf32)
+            line["extra"][ew] = {key: el[key] for key in ("metric", "value", "unit", "ms_per_step", "steps", "scaling",
+                                                       "config", "stage_ms", "shape", "first_call_ms")}
     if world == 1 and not args.skip_cpu:
-        line["cpu_baseline"] = cpu_baseline()
+        line["cpu_baseline"] = cpu_baseline(wl)
     print(json.dumps(line))
 
 
@@ -506,10 +788,9 @@ def run_reference(args, wl, spec):
     base = {"metric": METRICS[wl], "unit": "rows/s", "impl": "reference",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u32" if spec["family"] == "minhash" else "f32",
-            "data": "synthetic",
-            "config": {"workload": spec["name"], "id": wl, "rows_per_gpu": n, "queries": nq, "seed": spec["seed"]}}
+            "data": "synthetic", "config": config_of(wl, spec)}
     if ref is None or not have_gpu:
-        cb = cpu_baseline()
+        cb = cpu_baseline(wl)
         base.update({"value": cb["value"], "ms_per_step": None, "cpu_baseline": cb,
                      "e2e": {"value": cb["value"], "unit": "rows/s", "h2d_bytes_per_step": 0,
                              "d2h_bytes_per_step": 0}})
@@ -531,6 +812,8 @@ def run_reference(args, wl, spec):
             return tuple(to_dev(x) for x in h)
         return torch.from_numpy(h).to(device, non_blocking=True)
 
+    keep = {}
+
     def step(X, Q, host):
         if host:
             X, Q = to_dev(X), to_dev(Q)
@@ -547,6 +830,7 @@ def run_reference(args, wl, spec):
             t1 = time.perf_counter()
             cand = core_query(core, spec, Q, ix, batch)
         t2 = time.perf_counter()
+        keep["cand"] = cand
         return t1 - t0, t2 - t1, (read_back(cand) if host else 0)
 
     for _ in range(args.warmup):
@@ -560,6 +844,10 @@ def run_reference(args, wl, spec):
         queries.append(q)
     torch.cuda.synchronize()
     t_dev = time.perf_counter() - t0
+    cand = keep.pop("cand")
+    parity = {"unique_candidates": int(cand.n_total_candidates),
+              "csr_checksum": csr_checksum(torch, cand.get_indices(), cand.get_offsets(), device)}
+    del cand
     e2e = {"value": None, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     if not args.skip_e2e:
         Xh, Qh = to_pinned_host(torch, Xd), to_pinned_host(torch, Qd)
@@ -581,10 +869,10 @@ def run_reference(args, wl, spec):
         "cpu_baseline": {"value": n / (t_dev / args.steps), "unit": "rows/s", "cores": 0, "kind": "reference",
                          "sample": "full workload; upstream cuLSH CUDA build (its cuBLAS/CUB kernels compiled for "
                                    "sm_100) on one B200 - upstream has no CPU implementation of this path"},
-        "e2e": e2e, "reference_device": "B200 (upstream CUDA build)",
+        "e2e": e2e, "reference_device": "B200 (upstream CUDA build)", "parity": parity,
     })
     if world > 1:
-        base["config"]["note"] = "upstream is single-GPU: rank 0 runs one shard"
+        base["note"] = "upstream is single-GPU: rank 0 runs one shard"
     print(json.dumps(base))
 
 
@@ -598,7 +886,9 @@ def main():
     ap.add_argument("--rows", type=int, default=None, help="rows per GPU (default: the workload's)")
     ap.add_argument("--queries", type=int, default=None)
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: no host-input leg")
-    ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: no CPU baseline / TF32 peak leg")
+    ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: no CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="default workload only: leave out the short c4 / c5 runs reported under `extra`")
     ap.add_argument("--reference-cpu", action="store_true",
                     help="reference arm: time the NumPy restatement on the host cores instead of "
                          "upstream's CUDA build")

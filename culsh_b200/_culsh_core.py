@@ -405,6 +405,11 @@ class _CoreBase:
     def set_profiling(self, enabled: bool):
         _lib.check(self._h.lib.culsh_set_profiling(self._h.ptr, int(bool(enabled))))
 
+    def set_param_cache(self, enabled: bool):
+        """False: every fit generates its hash parameters again (upstream's behaviour) instead
+        of reusing the set this handle made for the same (family, shape, seed)."""
+        _lib.check(self._h.lib.culsh_set_param_cache(self._h.ptr, int(bool(enabled))))
+
     def set_projection_path(self, path: int):
         _lib.check(self._h.lib.culsh_set_projection_path(self._h.ptr, int(path)))
 

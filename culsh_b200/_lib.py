@@ -28,6 +28,7 @@ class Stats(C.Structure):
         ("hash_ms", C.c_float), ("sort_ms", C.c_float), ("build_ms", C.c_float),
         ("lookup_ms", C.c_float), ("gather_ms", C.c_float), ("total_ms", C.c_float),
         ("scatter_ms", C.c_float), ("dedupe_ms", C.c_float),
+        ("params_ms", C.c_float), ("reserved0", C.c_float),
         ("n_items", C.c_uint64), ("n_buckets", C.c_uint64), ("raw_candidates", C.c_uint64),
         ("unique_candidates", C.c_uint64),
         ("sort_passes", C.c_int32), ("key_words", C.c_int32), ("elem_bytes", C.c_int32),
@@ -46,6 +47,7 @@ SIGNATURES = {
     "culsh_destroy": [VP],
     "culsh_get_stats": [VP, C.POINTER(Stats)],
     "culsh_set_profiling": [VP, I],
+    "culsh_set_param_cache": [VP, I],
     "culsh_set_projection_path": [VP, I],
     "culsh_rplsh_fit_f32": [VP, VP, I, I, I, I, U64, PP],
     "culsh_rplsh_fit_f64": [VP, VP, I, I, I, I, U64, PP],

@@ -144,6 +144,9 @@ struct Ctx {
     // hash parameters already generated on this handle (they depend only on the key): the
     // cuRAND generator set-up costs more than a tenth of a 1M-row fit
     std::map<ParamKey, std::shared_ptr<void>> param_cache;
+    bool param_cache_enabled = true;
+    float last_params_ms = 0.f;       // host wall time of the last parameter generation (0: cache hit)
+    curandGenerator_t curand = nullptr;  // created on first use, re-seeded per parameter set
     void* slot_ptr[SL_COUNT] = {};
     size_t slot_cap[SL_COUNT] = {};
     cudaStream_t stream = nullptr;
@@ -164,6 +167,7 @@ struct Ctx {
     ~Ctx() {
         cudaSetDevice(device);
         if (stream) cudaStreamSynchronize(stream);
+        if (curand) curandDestroyGenerator(curand);
         for (auto& e : ev) if (e) cudaEventDestroy(e);
         for (auto& e : ev_pass) if (e) cudaEventDestroy(e);
         for (auto& e : ev_dedupe) if (e) cudaEventDestroy(e);

@@ -166,42 +166,58 @@ __global__ void minhash_normalize_kernel(uint32_t* A, uint32_t* B, int n) {
     }
 }
 
-struct CurandGen {
-    curandGenerator_t g = nullptr;
-    CurandGen(cudaStream_t s, uint64_t seed) {
+// The handle keeps one XORWOW generator for its lifetime (creating one allocates device
+// memory and synchronises the device); a call re-seeds it, which restarts the sequence at
+// offset 0 exactly as a freshly created generator would.
+curandGenerator_t seeded_generator(const CtxPtr& c, uint64_t seed) {
+    if (!c->curand) {
+        curandGenerator_t g = nullptr;
         CURAND_CHECK(curandCreateGenerator(&g, CURAND_RNG_PSEUDO_DEFAULT));
-        curandStatus_t st = curandSetStream(g, s);
-        if (st == CURAND_STATUS_SUCCESS) st = curandSetPseudoRandomGeneratorSeed(g, seed);
+        curandStatus_t st = curandSetStream(g, c->stream);
         if (st != CURAND_STATUS_SUCCESS) {
             curandDestroyGenerator(g);
             fail(CULSH_ERR_CUDA, "cuRAND generator setup failed: status %d", (int)st);
         }
+        c->curand = g;
     }
-    ~CurandGen() {
-        if (g) curandDestroyGenerator(g);
-    }
-};
+    CURAND_CHECK(curandSetPseudoRandomGeneratorSeed(c->curand, seed));
+    CURAND_CHECK(curandSetGeneratorOffset(c->curand, 0ull));
+    return c->curand;
+}
 
 void generate_params_uncached(culsh_index& ix);
 
+void prepare_tc_split(culsh_index& ix);
+
+// Parameters + (fp32 dense families) the hi/lo split of the projection for the tensor-core
+// kernel.  last_params_ms is the host wall time of the generation (0 on a cache hit).
 void generate_params(culsh_index& ix) {
     const CtxPtr& c = ix.ctx;
+    c->last_params_ms = 0.f;
     ParamKey key{ix.family, ix.L * ix.k, ix.family == CULSH_MINHASH ? 0 : ix.d, ix.window, ix.is_double, ix.seed};
-    auto it = c->param_cache.find(key);
-    if (it != c->param_cache.end()) {
-        ix.params = std::static_pointer_cast<ParamSet>(it->second);
-        return;
+    if (c->param_cache_enabled) {
+        auto it = c->param_cache.find(key);
+        if (it != c->param_cache.end()) {
+            ix.params = std::static_pointer_cast<ParamSet>(it->second);
+            return;
+        }
     }
+    const auto t0 = std::chrono::steady_clock::now();
     generate_params_uncached(ix);
-    if (c->param_cache.size() >= 16) c->param_cache.clear();
-    c->param_cache[key] = ix.params;
+    prepare_tc_split(ix);
+    CU_CHECK(cudaStreamSynchronize(c->stream));
+    c->last_params_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    if (c->param_cache_enabled) {
+        if (c->param_cache.size() >= 16) c->param_cache.clear();
+        c->param_cache[key] = ix.params;
+    }
 }
 
 void generate_params_uncached(culsh_index& ix) {
     const CtxPtr& c = ix.ctx;
     const int H = ix.L * ix.k;
     ix.params = std::make_shared<ParamSet>();
-    CurandGen gen(c->stream, ix.seed);
+    struct { curandGenerator_t g; } gen{seeded_generator(c, ix.seed)};
     if (ix.family == CULSH_MINHASH) {
         ix.params->p0.alloc(c, sizeof(uint32_t) * H);
         ix.params->p1.alloc(c, sizeof(uint32_t) * H);
@@ -235,8 +251,6 @@ void generate_params_uncached(culsh_index& ix) {
         }
         KERNEL_CHECK();
     }
-    // the generator is destroyed at scope exit; its work is ordered on the stream
-    CU_CHECK(cudaStreamSynchronize(c->stream));
 }
 
 // -----------------------------------------------------------------------------------------
@@ -427,6 +441,7 @@ template <typename HashFn>
 void fit_common(culsh_index& ix, HashFn&& hash_fn, Scratch<int32_t>* item_to_bucket) {
     const CtxPtr& c = ix.ctx;
     c->stats = culsh_stats{};
+    c->stats.params_ms = c->last_params_ms;
     launch_counter() = 0;
     int eb = ix.family == CULSH_PSLSH ? 1 : (ix.family == CULSH_MINHASH ? 4 : 0);
     const size_t items = (size_t)ix.n * ix.L;
@@ -787,6 +802,7 @@ void fit_query_dense(culsh_handle* h, int family, const T* X, int n, int d, int 
     tm.mark();
     query_from_matched(*ix, i2b.p, n, *res, tm);
     h->ctx->stats.gather_ms = tm.between(0, 1);
+    check_error_word(read_error_word(h->ctx));  // the gather's bounded waits report here
     *out = res.release();
 }
 
@@ -913,6 +929,14 @@ int culsh_set_profiling(culsh_handle* h, int enabled) {
     });
 }
 
+int culsh_set_param_cache(culsh_handle* h, int enabled) {
+    return guarded([&] {
+        if (!h) fail(CULSH_ERR_INVALID, "null handle");
+        h->ctx->param_cache_enabled = enabled != 0;
+        if (!enabled) h->ctx->param_cache.clear();
+    });
+}
+
 int culsh_set_projection_path(culsh_handle* h, int path) {
     return guarded([&] {
         if (!h) fail(CULSH_ERR_INVALID, "null handle");
@@ -1033,6 +1057,7 @@ int culsh_minhash_fit_query(culsh_handle* h, const int32_t* indices, const int32
         tm.mark();
         query_from_matched(*ix, i2b.p, n, *res, tm);
         h->ctx->stats.gather_ms = tm.between(0, 1);
+        check_error_word(read_error_word(h->ctx));  // the gather's bounded waits report here
         *out = res.release();
     });
 }

@@ -185,18 +185,28 @@ class PeerExchange:
         self.peers = []        # device addresses of every rank's buffer as mapped here
 
     def _close(self):
+        """Collective teardown in two phases: every rank first unmaps its peers' buffers, the
+        group meets at a barrier, and only then each rank frees the buffer it exported - a
+        buffer must not be freed while another process still has it mapped.  If a rank
+        failed on the way (the barrier raises), the export is left to the driver at process
+        exit rather than freed early."""
         import ctypes as C
+        import torch.distributed as dist
         from . import _lib
+        if not self.local and not self.peers:
+            return
         for r, p in enumerate(self.peers):
             if r != self.rank and p:
                 _lib.check(self.h.lib.culsh_peer_close(self.h.ptr, C.c_void_p(p)))
-        if self.local:
-            _lib.check(self.h.lib.culsh_peer_free(self.h.ptr, C.c_void_p(self.local)))
-        self.peers, self.local, self.capacity = [], None, 0
+        self.peers = []
+        local, self.local, self.capacity = self.local, None, 0
+        dist.barrier(self.group)   # all importers have unmapped
+        if local:
+            _lib.check(self.h.lib.culsh_peer_free(self.h.ptr, C.c_void_p(local)))
 
     def close(self):
         import torch.distributed as dist
-        dist.barrier(self.group)
+        dist.barrier(self.group)   # nobody is still reading
         self._close()
 
     def _sync_max(self, value: int) -> int:

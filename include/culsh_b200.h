@@ -74,6 +74,8 @@ typedef struct culsh_stats {
     float hash_ms, sort_ms, build_ms, lookup_ms, gather_ms, total_ms;
     float scatter_ms; /* the scatter launch of the last radix pass alone */
     float dedupe_ms;  /* the dedupe launch (chained or bitmap kernel) of the query batches alone */
+    float params_ms;  /* fit: host wall time of the hash-parameter generation (0 on a cache hit) */
+    float reserved0;
     uint64_t n_items, n_buckets, raw_candidates, unique_candidates;
     int32_t sort_passes, key_words, elem_bytes, hash_path; /* hash_path: 0 SIMT, 1 tcgen05 */
     int32_t launches;  /* kernels of this library launched by the call */
@@ -88,6 +90,10 @@ const char* culsh_last_error(void);
 int culsh_get_stats(const culsh_handle* h, culsh_stats* out);
 /* 1 = time stages with CUDA events (adds a few event records per call). Default 0. */
 int culsh_set_profiling(culsh_handle* h, int enabled);
+/* 1 (default) = hash parameters generated on this handle are kept and reused by later fits
+ * with the same (family, shape, window, dtype, seed); 0 = every fit generates them again,
+ * as upstream does (rplsh/hash.cuh:59-78, pslsh/hash.cuh:60-89, minhash/hash.cuh:42-54). */
+int culsh_set_param_cache(culsh_handle* h, int enabled);
 /* Force the projection path: 0 auto, 1 SIMT fp32/fp64 kernel, 2 tcgen05 3xTF32 kernel. */
 int culsh_set_projection_path(culsh_handle* h, int path);
 

@@ -325,3 +325,27 @@ def fast_query_packed(tables, qkeys: np.ndarray):
     np.cumsum(counts, out=offsets[1:])
     indices = np.concatenate(pieces).astype(np.int32) if pieces else np.zeros(0, np.int32)
     return indices, offsets, counts
+
+
+def signature_keys(sig_x: np.ndarray, sig_q: np.ndarray, L: int, k: int):
+    """(uint64 [L, n], uint64 [L, n_q]): one word per (table, row) such that two rows of a table
+    have equal words exactly when their k signature elements are equal (bucket membership is
+    an equality relation, core/fit.cuh:77-84, so any injective relabelling keeps the candidate
+    sets).  Signatures of at most 8 bytes are packed directly; wider ones are numbered per
+    table over the rows of both inputs."""
+    n, nq = sig_x.shape[0], sig_q.shape[0]
+    item = sig_x.dtype.itemsize
+    both = np.concatenate([sig_x, sig_q.astype(sig_x.dtype, copy=False)], axis=0)
+    both = np.ascontiguousarray(both.reshape(n + nq, L, k).transpose(1, 0, 2))  # [L, n+nq, k]
+    out = np.empty((L, n + nq), dtype=np.uint64)
+    if k * item <= 8:
+        raw = both.view(np.uint8).reshape(L, n + nq, k * item)
+        padded = np.zeros((L, n + nq, 8), dtype=np.uint8)
+        padded[:, :, :k * item] = raw
+        out[:] = padded.view(np.uint64).reshape(L, n + nq)
+    else:
+        rows = both.view(np.dtype((np.void, k * item))).reshape(L, n + nq)
+        for t in range(L):
+            _, inv = np.unique(rows[t], return_inverse=True)
+            out[t] = inv.astype(np.uint64)
+    return np.ascontiguousarray(out[:, :n]), np.ascontiguousarray(out[:, n:])

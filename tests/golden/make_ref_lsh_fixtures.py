@@ -24,7 +24,12 @@ import sys
 import numpy as np
 import scipy.sparse as sp
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) > 1:
+    REF = sys.argv[1]
+elif os.environ.get("CULSH_REFERENCE"):
+    REF = os.environ["CULSH_REFERENCE"]
+else:
+    raise SystemExit("usage: make_ref_lsh_fixtures.py /path/to/cuLSH   (or set CULSH_REFERENCE)")
 sys.path.insert(0, os.path.join(REF, "python", "tests"))
 import ref_lsh  # noqa: E402  (upstream module, imported as-is)
 

@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header():
     from culsh_b200 import _lib
     assert ctypes.sizeof(_lib.IndexMeta) == 12 * 4 + 2 * 8
-    assert ctypes.sizeof(_lib.Stats) == 8 * 4 + 4 * 8 + 6 * 4
+    assert ctypes.sizeof(_lib.Stats) == 10 * 4 + 4 * 8 + 6 * 4
 
 
 def test_python_layer_mirrors_upstream_surface():
@@ -88,3 +88,16 @@ def test_product_code_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text, f"{f} mentions the oracle"
+
+
+def test_every_entry_point_that_runs_the_gather_reads_the_device_error_word():
+    """The gather's look-back waits are bounded and report through the handle's error word; a
+    call that returns a result without reading that word could hand back a CSR written at
+    wrong offsets.  Source-level check: between a call of the gather and the release of its
+    result the error word is read and checked."""
+    text = open(os.path.join(ROOT, "culsh_b200", "csrc", "culsh_b200.cu")).read()
+    sites = [m.start() for m in re.finditer(r"\bquery_from_matched\(\*ix|\brun\(Q, n_q, \*res\)|\bquery_batch\(\*ix, n_q", text)]
+    assert len(sites) >= 4
+    for pos in sites:
+        end = text.index("*out = res.release();", pos)
+        assert "check_error_word(read_error_word(" in text[pos:end], text[pos:pos + 80]

@@ -62,7 +62,6 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.timeout(300)
 def test_peer_exchange_two_processes_one_gpu(tmp_path):
     import torch.multiprocessing as mp
     world = 2
@@ -118,7 +117,6 @@ def _nccl_worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.timeout(300)
 def test_fit_query_sharded_two_gpus_nccl(tmp_path):
     """Real peers: one process per GPU, NCCL for the row all-gather and the barriers, CUDA IPC
     mappings across two devices for the exchange."""
