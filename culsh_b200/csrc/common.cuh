@@ -136,7 +136,7 @@ enum ScratchSlot {
     SL_STAGE0, SL_STAGE1, SL_CSR_INDPTR, SL_CSR_INDICES, SL_KEYS0, SL_KEYS1, SL_VALS, SL_GHIST,
     SL_STATUS, SL_COUNTER, SL_TILE_HEADS, SL_TILE_BASE, SL_SCAN, SL_RAW_CNT, SL_RAW_OFF,
     SL_BIG_LIST, SL_NBIG, SL_TMP, SL_QKEYS, SL_QOVF, SL_MATCHED, SL_I2B, SL_MISC0, SL_MISC1,
-    SL_MISC2, SL_CHAIN, SL_SLICES, SL_I2B_TM, SL_BOUNDS, SL_COUNT
+    SL_MISC2, SL_CHAIN, SL_SLICES, SL_I2B_TM, SL_BOUNDS, SL_TK_CNT, SL_TK_BASE, SL_TK_DESC, SL_COUNT
 };
 
 struct Ctx {

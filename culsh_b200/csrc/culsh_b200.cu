@@ -1,5 +1,6 @@
 // Host orchestration and the C ABI of the engine (see include/culsh_b200.h).
 #include "common.cuh"
+#include "dedupe_stream.cuh"
 #include "index_build.cuh"
 #include "minhash.cuh"
 #include "project_simt.cuh"
@@ -563,6 +564,7 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
                          (uint64_t)n_q * (uint64_t)n_win < (1ull << 31) &&
                          chain_window_smem_bytes(cbits, stage_ids) + 1024 <= c->smem_optin;
     const uint32_t n_other = (uint32_t)n_q - nb - nm;  // queries on the warp path (incl. empty ones)
+    bool streamed = false;
     Scratch<int32_t> tmp;
     tmp.reserve(c, SL_TMP, raw_total);
     tr.lap("alloc tmp");
@@ -581,7 +583,80 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
                                                        raw_cnt.p, raw_off.p, L, id_bytes, tmp.p, out.counts.p);
         KERNEL_CHECK();
     }
-    if (chained) {
+    // Streamed form (persistent CTAs, id-balanced tickets, cp.async staging); the one-ticket-per-CTA
+    // kernel below stays for indexes whose bucket lists are not 16-byte aligned in memory and as
+    // the form selected by CULSH_CHAIN_V=1.
+    //   CULSH_CHAIN_BITS   largest window in rows (default 200,704)
+    //   CULSH_CHAIN_STAGE  ids per shared-memory buffer = stage size (default 4096)
+    //   CULSH_CHAIN_IDS    raw ids aimed at per ticket (default 3/4 of the buffer less the pad words)
+    //   CULSH_CHAIN_THREADS threads per CTA: 256, 384 or 512
+    if (chained && env_long("CULSH_CHAIN_V", 2) != 1 && (reinterpret_cast<uintptr_t>(ix.cand.p) & 15) == 0) {
+        const int W = (int)std::min<size_t>(std::max<size_t>(4096, (size_t)env_long("CULSH_CHAIN_BITS", 200704) / 4096 * 4096),
+                                            ceil_div((size_t)ix.n, 4096) * 4096);
+        const int cap = (int)std::min<long>(16384, std::max<long>(256, env_long("CULSH_CHAIN_STAGE", 4096))) / 4 * 4;
+        const int ids_per_ticket = (int)std::max<long>(64, env_long("CULSH_CHAIN_IDS", ((long)cap - 6L * L) * 3 / 4));
+        const int min_win = (int)ceil_div((size_t)ix.n, (size_t)W);
+        const int max_win = std::max(min_win, (int)std::min<size_t>(TK_MAX_WINDOWS, ceil_div((size_t)ix.n, 4096)));
+        const size_t n_tk_max = (size_t)(raw_total / (uint64_t)ids_per_ticket) + (size_t)n_q * ((size_t)min_win + 1);
+        const size_t smem = stream_smem_bytes(W, cap, L);
+        if (min_win <= CHAIN_MAX_WINDOWS && n_tk_max * (size_t)L <= ((size_t)64 << 20) && smem + 1024 <= c->smem_optin) {
+            out.indices.alloc(c, raw_total);  // capacity: the unique total is not known yet
+            Scratch<uint32_t> tk_cnt(c, SL_TK_CNT, n_q), tk_base(c, SL_TK_BASE, (size_t)n_q + 1);
+            Scratch<TicketDesc> descs(c, SL_TK_DESC, n_tk_max);
+            Scratch<int2> slices(c, SL_SLICES, n_tk_max * (size_t)L);
+            Scratch<unsigned long long> status(c, SL_CHAIN, n_tk_max + 1);
+            uint32_t* ticket = reinterpret_cast<uint32_t*>(status.p + n_tk_max);
+            CU_CHECK(cudaMemsetAsync(status.p, 0, sizeof(unsigned long long) * (n_tk_max + 1), s));
+            ticket_count_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(raw_cnt.p, n_q, mid_max, ids_per_ticket,
+                                                                           min_win, max_win, tk_cnt.p);
+            KERNEL_CHECK();
+            exclusive_scan<uint32_t, uint32_t>(s, tk_cnt.p, n_q, tk_base.p, reinterpret_cast<uint32_t*>(scratch.p));
+            ticket_table_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(raw_cnt.p, tk_base.p, n_q, ix.n, mid_max, descs.p);
+            KERNEL_CHECK();
+            ticket_slices_kernel<<<(unsigned)ceil_div(n_tk_max * (size_t)L, 256), 256, 0, s>>>(
+                descs.p, tk_base.p + n_q, matched, ix.bucket_offsets.p, ix.cand.p, L, ix.n, slices.p);
+            KERNEL_CHECK();
+            StreamArgs a{};
+            a.cand = ix.cand.p; a.raw_off = raw_off.p; a.tmp = tmp.p; a.descs = descs.p; a.slices = slices.p;
+            a.n_tickets = tk_base.p + n_q; a.status = status.p; a.ticket = ticket; a.out_indices = out.indices.p;
+            a.counts = out.counts.p; a.offsets = out.offsets.p; a.d_error = c->d_error;
+            a.n_q = n_q; a.L = L; a.n_rows = ix.n; a.window_bits = W; a.cap = cap;
+            auto launch = [&](auto nt_tag) {
+                constexpr int NT = decltype(nt_tag)::value;
+                CU_CHECK(cudaFuncSetAttribute(dedupe_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                CU_CHECK(cudaFuncSetAttribute(dedupe_stream_kernel<NT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+                int per_sm = 0;
+                CU_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dedupe_stream_kernel<NT>, NT, smem));
+                const size_t grid = std::min<size_t>(n_tk_max, (size_t)c->sm_count * std::max(per_sm, 1));
+                dedupe_stream_kernel<NT><<<(unsigned)grid, NT, smem, s>>>(a);
+            };
+            const long st_threads = env_long("CULSH_CHAIN_THREADS", 384);
+            if (c->profiling) cudaEventRecord(c->ev_dedupe[0], s);
+            if (st_threads == 512) launch(std::integral_constant<int, 512>{});
+            else if (st_threads == 256) launch(std::integral_constant<int, 256>{});
+            else launch(std::integral_constant<int, 384>{});
+            KERNEL_CHECK();
+            if (c->profiling) { cudaEventRecord(c->ev_dedupe[1], s); dedupe_timed = true; }
+            counts_from_offsets_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(out.offsets.p, n_q, out.counts.p);
+            KERNEL_CHECK();
+            uint64_t total = 0;
+            read_words(c, out.offsets.p + n_q, sizeof(uint64_t), &total);
+            tr.lap("streamed dedupe+sync");
+            out.total = total;
+            c->stats.unique_candidates += total;
+            if (total == 0) {
+                out.indices.release();
+            } else if (total * 4 < raw_total * 3) {  // much smaller than the capacity: keep an exact copy
+                DevBuf<int32_t> exact(c, total);
+                CU_CHECK(cudaMemcpyAsync(exact.p, out.indices.p, sizeof(int32_t) * total, cudaMemcpyDeviceToDevice, s));
+                out.indices = std::move(exact);
+            }
+            streamed = true;
+        }
+    }
+    if (streamed) {
+        // done above
+    } else if (chained) {
         out.indices.alloc(c, raw_total);  // capacity: the unique total is not known yet
         const size_t n_tk = (size_t)n_q * n_win;
         Scratch<unsigned long long> status(c, SL_CHAIN, n_tk + 1);

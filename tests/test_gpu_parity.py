@@ -563,15 +563,30 @@ def test_shard_merge_equals_unsharded(eng):
 # ------------------------------------------------------------------------------------------
 # tensor-core projection (tcgen05 3xTF32) against the CUDA-core projection and the oracle
 # ------------------------------------------------------------------------------------------
+def test_tensor_core_projection_wide_k_block_variant():
+    """The 32-wide K-block variant of the tensor-core kernel is chosen once per process
+    (CULSH_TC_KBLK), so its cases run in a child process with the variable set."""
+    import subprocess
+    import sys
+    if os.environ.get("CULSH_TC_KBLK") == "32":
+        pytest.skip("already inside the child process")
+    env = dict(os.environ, CULSH_TC_KBLK="32")
+    res = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-x", "-m", "gpu",
+                          "-p", "no:cacheprovider", "-k",
+                          "test_tensor_core_projection and not wide_k_block"],
+                         env=env, capture_output=True, text=True, timeout=900)
+    tail = (res.stdout + res.stderr)[-2000:]
+    assert res.returncode == 0, tail
+    assert "7 passed" in res.stdout, tail
+
+
 @pytest.mark.parametrize("fam,n,d,L,k", [("rplsh", 5000, 128, 32, 16), ("rplsh", 1000, 100, 8, 12),
                                          ("rplsh", 3333, 256, 48, 24), ("rplsh", 130, 64, 3, 40),
                                          ("pslsh", 4097, 96, 16, 8), ("pslsh", 999, 32, 5, 3),
                                          ("pslsh", 2000, 128, 4, 16)])
-@pytest.mark.parametrize("kblk", [16, 32])
+@pytest.mark.parametrize("kblk", [int(os.environ.get("CULSH_TC_KBLK", "16"))])  # chosen per process
 def test_tensor_core_projection(eng, fam, n, d, L, k, kblk):
     culsh, core_mod = eng
-    if kblk != int(os.environ.get("CULSH_TC_KBLK", "16")):
-        pytest.skip("the K-block variant is chosen per process (CULSH_TC_KBLK)")
     rng = np.random.RandomState(n + d + L)
     X = rng.randn(n, d).astype(np.float32)
     X[: n // 4] = np.round(X[: n // 4] * (50 if fam == "rplsh" else 4))  # integer rows: zero-lo fast path
