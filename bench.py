@@ -654,8 +654,12 @@ def line_of(torch, args, wl, spec, world, m, peaks, tf32):
                         "hash_evals_per_s": evals / (hash_ms * 1e-3)}
     elif hash_ms > 0:
         flops = 2.0 * n * spec["d"] * spec["L"] * spec["k"]
+        lo_frac = statistics.mean(s.get("hash_lo_fraction", 1.0) for s in stage["fit"])
         roof["hash"] = {"bound": "tensor", "achieved": flops / (hash_ms * 1e-3) / 1e12, "peak": tf32 / 3.0,
                         "unit": "TFLOP/s", "traffic": None,
+                        "frac_fp32_equiv": flops / (hash_ms * 1e-3) / 1e12 / (tf32 / 3.0),
+                        "frac_tensor_issue": flops * (2.0 + lo_frac) / (hash_ms * 1e-3) / 1e12 / tf32,
+                        "mma_per_k_block": 2.0 + lo_frac,
                         "kernel": "project_tc_kernel" if sf["hash_path"] == 1 else "project_simt_kernel",
                         "note": "fp32-equivalent flop 2*n*d*H over the CUDA-event time of the projection "
                                 "launch; peak = TF32 dense matmul measured in this run (8192^3) / 3 (3xTF32)",
@@ -729,7 +733,7 @@ def run_ours(args, wl, spec):
     from culsh_b200 import sharded
     exchange = sharded.PeerExchange(device=local) if world > 1 else None
     m = run_workload(torch, args, wl, spec, world, rank, local, exchange, args.steps, args.warmup,
-                     e2e=not args.skip_e2e)
+                     e2e=not args.skip_e2e, checks=not args.skip_checks)
     m["steps"], m["warmup"] = args.steps, args.warmup
     extra = {}
     if wl == "c2" and args.rows is None and not args.no_extra:
@@ -887,6 +891,7 @@ def main():
     ap.add_argument("--queries", type=int, default=None)
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: no host-input leg")
     ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: no CPU baseline leg")
+    ap.add_argument("--skip-checks", action="store_true", help="profiling runs: no parity / exchange checks")
     ap.add_argument("--no-extra", action="store_true",
                     help="default workload only: leave out the short c4 / c5 runs reported under `extra`")
     ap.add_argument("--reference-cpu", action="store_true",

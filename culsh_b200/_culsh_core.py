@@ -227,6 +227,14 @@ class Candidates:
     def get_offsets(self, as_cupy: bool = False, as_torch: bool = False):
         return self._get(self._h.lib.culsh_candidates_get_offsets, self._n_queries + 1, np.uint64, as_cupy, as_torch)
 
+    def _attach(self, indices_ptr: int, total: int, keepalive=None):
+        """Point this result at an id array it does not own (the receive buffer of a shard
+        exchange); `keepalive` is held as long as this object lives."""
+        _lib.check(self._h.lib.culsh_candidates_attach_indices(self._ptr, indices_ptr or None, int(total)))
+        self._total = int(total)
+        self._empty = False
+        self._keepalive = keepalive
+
     def device_pointers(self):
         """(indices, counts, offsets) raw device addresses, borrowed from this object."""
         a, b, c = C.c_void_p(), C.c_void_p(), C.c_void_p()

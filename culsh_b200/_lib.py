@@ -28,7 +28,7 @@ class Stats(C.Structure):
         ("hash_ms", C.c_float), ("sort_ms", C.c_float), ("build_ms", C.c_float),
         ("lookup_ms", C.c_float), ("gather_ms", C.c_float), ("total_ms", C.c_float),
         ("scatter_ms", C.c_float), ("dedupe_ms", C.c_float),
-        ("params_ms", C.c_float), ("reserved0", C.c_float),
+        ("params_ms", C.c_float), ("hash_lo_fraction", C.c_float),
         ("n_items", C.c_uint64), ("n_buckets", C.c_uint64), ("raw_candidates", C.c_uint64),
         ("unique_candidates", C.c_uint64),
         ("sort_passes", C.c_int32), ("key_words", C.c_int32), ("elem_bytes", C.c_int32),
@@ -89,6 +89,9 @@ SIGNATURES = {
     "culsh_host_alloc": [C.c_size_t, PP],
     "culsh_host_free": [VP],
     "culsh_merge_shard_candidates": [VP, I, I, PP, PP, C.POINTER(C.c_int64), PP],
+    "culsh_exchange_plan": [VP, I, I, I, VP, VP, C.POINTER(C.c_uint64), PP],
+    "culsh_exchange_push": [VP, I, I, VP, VP, VP, PP, C.c_int64, U64],
+    "culsh_candidates_attach_indices": [VP, VP, U64],
     "culsh_merge_shard_candidates_noalloc": [VP, I, I, PP, PP, C.POINTER(C.c_int64), VP, U64, VP, VP,
                                              C.POINTER(C.c_uint64)],
 }

@@ -136,7 +136,7 @@ enum ScratchSlot {
     SL_STAGE0, SL_STAGE1, SL_CSR_INDPTR, SL_CSR_INDICES, SL_KEYS0, SL_KEYS1, SL_VALS, SL_GHIST,
     SL_STATUS, SL_COUNTER, SL_TILE_HEADS, SL_TILE_BASE, SL_SCAN, SL_RAW_CNT, SL_RAW_OFF,
     SL_BIG_LIST, SL_NBIG, SL_TMP, SL_QKEYS, SL_QOVF, SL_MATCHED, SL_I2B, SL_MISC0, SL_MISC1,
-    SL_MISC2, SL_CHAIN, SL_SLICES, SL_I2B_TM, SL_BOUNDS, SL_TK_CNT, SL_TK_BASE, SL_TK_DESC, SL_COUNT
+    SL_MISC2, SL_CHAIN, SL_SLICES, SL_I2B_TM, SL_BOUNDS, SL_COUNT
 };
 
 struct Ctx {
@@ -158,6 +158,7 @@ struct Ctx {
     cudaEvent_t chunk_free[2] = {};
     uint64_t* pinned = nullptr;       // 64 x u64 words of pinned host memory
     int* d_error = nullptr;           // device-side self-check word
+    unsigned long long* d_mma = nullptr;  // tensor-core projection: K-blocks issued / with the low-part MMA
     bool profiling = false;
     int projection_path = 0;
     culsh_stats stats{};
@@ -177,6 +178,7 @@ struct Ctx {
         for (auto& q : slot_ptr) if (q) cudaFree(q);
         if (pinned) cudaFreeHost(pinned);
         if (d_error) cudaFree(d_error);
+        if (d_mma) cudaFree(d_mma);
         if (copy_stream) cudaStreamDestroy(copy_stream);
         if (stream) cudaStreamDestroy(stream);
     }

@@ -1,6 +1,5 @@
 // Host orchestration and the C ABI of the engine (see include/culsh_b200.h).
 #include "common.cuh"
-#include "dedupe_stream.cuh"
 #include "index_build.cuh"
 #include "minhash.cuh"
 #include "project_simt.cuh"
@@ -126,6 +125,11 @@ struct HostTrace {
         t = std::chrono::steady_clock::now();
     }
 };
+
+inline long env_long_early(const char* name, long dflt) {
+    const char* e = getenv(name);
+    return e && *e ? atol(e) : dflt;
+}
 
 void reset_error_word(const CtxPtr& c) {
     CU_CHECK(cudaMemsetAsync(c->d_error, 0, sizeof(int), c->stream));
@@ -309,25 +313,78 @@ void hash_dense(const culsh_index& ix, const KeySpec& ks, const T* X, int n, uin
     }
 }
 
-// CSR rows (host or device) -> keys.  indptr is rebased on the host side of a chunk, so
-// host inputs are copied whole (indices + indptr) before hashing.
+// CSR rows (host or device) -> keys.  When both arrays are host memory the rows are streamed in
+// chunks of about 32 MB of column ids through two pairs of device staging buffers, so that the
+// copy of chunk i+1 overlaps the hashing of chunk i; a chunk's indptr entries keep their
+// absolute values and the kernel is handed the staging address minus the chunk's first entry,
+// so nothing has to be rebased.
 void hash_csr(const culsh_index& ix, const KeySpec& ks, const int32_t* indices, const int32_t* indptr,
               int n, uint32_t* keys, int n_total, int row_offset) {
     const CtxPtr& c = ix.ctx;
     if (n == 0) return;
+    const uint32_t* A = reinterpret_cast<const uint32_t*>(ix.params->p0.p);
+    const uint32_t* B = reinterpret_cast<const uint32_t*>(ix.params->p1.p);
+    const bool ptr_host = !is_device_pointer(indptr), idx_host = !is_device_pointer(indices);
+    if (ptr_host && idx_host) {
+        const int64_t nnz = indptr[n];
+        if (nnz < 0) fail(CULSH_ERR_INVALID, "indptr[n] is negative");
+        if (nnz > 0 && !indices) fail(CULSH_ERR_INVALID, "indices is null");
+        const int64_t chunk_nnz = std::max<int64_t>(1 << 16, env_long_early("CULSH_CSR_CHUNK_NNZ", 8 << 20));
+        // chunk boundaries: rows [r0, r1) with at most chunk_nnz entries (one row at least)
+        std::vector<int> cuts{0};
+        while (cuts.back() < n) {
+            const int r0 = cuts.back();
+            const int32_t* hi = std::upper_bound(indptr + r0 + 1, indptr + n + 1, (int32_t)std::min<int64_t>(
+                                                     (int64_t)indptr[r0] + chunk_nnz, INT32_MAX));
+            int r1 = (int)(hi - indptr) - 1;
+            cuts.push_back(std::min(n, std::max(r1, r0 + 1)));
+        }
+        size_t max_rows = 0, max_nnz = 0;
+        for (size_t i = 0; i + 1 < cuts.size(); ++i) {
+            max_rows = std::max<size_t>(max_rows, (size_t)(cuts[i + 1] - cuts[i]));
+            max_nnz = std::max<size_t>(max_nnz, (size_t)(indptr[cuts[i + 1]] - indptr[cuts[i]]));
+        }
+        Scratch<int32_t> st_idx[2], st_ptr[2];
+        st_idx[0].reserve(c, SL_STAGE0, std::max<size_t>(max_nnz, 1));
+        st_idx[1].reserve(c, SL_STAGE1, std::max<size_t>(max_nnz, 1));
+        st_ptr[0].reserve(c, SL_CSR_INDPTR, max_rows + 1);
+        st_ptr[1].reserve(c, SL_CSR_INDICES, max_rows + 1);
+        CU_CHECK(cudaEventRecord(c->chunk_free[0], c->stream));
+        CU_CHECK(cudaEventRecord(c->chunk_free[1], c->stream));
+        int slot = 0;
+        for (size_t i = 0; i + 1 < cuts.size(); ++i, slot ^= 1) {
+            const int r0 = cuts[i], rows = cuts[i + 1] - r0;
+            const int64_t e0 = indptr[r0], cnt = indptr[r0 + rows] - e0;
+            if (cnt < 0) fail(CULSH_ERR_INVALID, "indptr is not ascending");
+            CU_CHECK(cudaStreamWaitEvent(c->copy_stream, c->chunk_free[slot], 0));
+            CU_CHECK(cudaMemcpyAsync(st_ptr[slot].p, indptr + r0, sizeof(int32_t) * ((size_t)rows + 1),
+                                     cudaMemcpyHostToDevice, c->copy_stream));
+            if (cnt)
+                CU_CHECK(cudaMemcpyAsync(st_idx[slot].p, indices + e0, sizeof(int32_t) * (size_t)cnt,
+                                         cudaMemcpyHostToDevice, c->copy_stream));
+            CU_CHECK(cudaEventRecord(c->copy_done[slot], c->copy_stream));
+            CU_CHECK(cudaStreamWaitEvent(c->stream, c->copy_done[slot], 0));
+            // entry e of the chunk sits at st_idx[e - e0]: the kernel indexes with absolute values
+            const int32_t* shifted = reinterpret_cast<const int32_t*>(
+                reinterpret_cast<uintptr_t>(st_idx[slot].p) - (uintptr_t)e0 * sizeof(int32_t));
+            launch_minhash(c, c->stream, shifted, st_ptr[slot].p, A, B, rows, ix.L, ix.k, ks, keys, n_total,
+                           row_offset + r0);
+            CU_CHECK(cudaEventRecord(c->chunk_free[slot], c->stream));
+        }
+        return;
+    }
     Scratch<int32_t> d_indptr, d_indices;
     const int32_t* ip = indptr;
     const int32_t* ii = indices;
-    if (!is_device_pointer(indptr)) {
+    if (ptr_host) {
         d_indptr.reserve(c, SL_CSR_INDPTR, (size_t)n + 1);
         CU_CHECK(cudaMemcpyAsync(d_indptr.p, indptr, sizeof(int32_t) * ((size_t)n + 1),
                                  cudaMemcpyHostToDevice, c->stream));
         ip = d_indptr.p;
     }
-    if (!is_device_pointer(indices)) {
+    if (idx_host) {
         int32_t nnz = 0;
-        if (is_device_pointer(indptr)) read_words(c, indptr + n, sizeof(int32_t), &nnz);
-        else nnz = indptr[n];
+        read_words(c, indptr + n, sizeof(int32_t), &nnz);  // indptr is on the device here
         if (nnz < 0) fail(CULSH_ERR_INVALID, "indptr[n] is negative");
         if (nnz > 0 && !indices) fail(CULSH_ERR_INVALID, "indices is null");
         d_indices.reserve(c, SL_CSR_INDICES, (size_t)nnz);
@@ -336,9 +393,7 @@ void hash_csr(const culsh_index& ix, const KeySpec& ks, const int32_t* indices, 
                                      cudaMemcpyHostToDevice, c->stream));
         ii = d_indices.p;
     }
-    launch_minhash(c, c->stream, ii, ip, reinterpret_cast<const uint32_t*>(ix.params->p0.p),
-                   reinterpret_cast<const uint32_t*>(ix.params->p1.p), n, ix.L, ix.k, ks, keys, n_total,
-                   row_offset);
+    launch_minhash(c, c->stream, ii, ip, A, B, n, ix.L, ix.k, ks, keys, n_total, row_offset);
     // staging buffers are released in stream order after the kernel
 }
 
@@ -352,15 +407,22 @@ struct SortBuffers {
     Scratch<uint32_t> vals_tmp;
     Scratch<uint32_t> tile_hist;
     int final_buf = 0;
+    // p-stable keys of one byte per hash may be sorted two bytes per pass (10-bit digits)
+    static bool may_pair_bytes(const KeySpec& ks) {
+        return ks.family == CULSH_PSLSH && ks.elem_bytes == 1 && ks.key_words <= 4 && ks.key_bytes >= 2;
+    }
     void alloc(const CtxPtr& c, size_t items, const KeySpec& ks, int n, int L) {
         keys[0].reserve(c, SL_KEYS0, items * ks.key_words);
         keys[1].reserve(c, SL_KEYS1, items * ks.key_words);
-        final_buf = ks.key_bytes & 1;  // one buffer flip per radix pass
         vals_out.alloc(c, items);
         vals_tmp.reserve(c, SL_VALS, items);
+        tile_hist.reserve(c, SL_STATUS, radix_sort_tile_words(n, L, ks.key_words, may_pair_bytes(ks) ? 10 : 8));
+    }
+    // one buffer flip per radix pass: the last pass must write the row ids into vals_out
+    void set_passes(int passes) {
+        final_buf = passes & 1;
         vals[final_buf] = vals_out.p;
         vals[final_buf ^ 1] = vals_tmp.p;
-        tile_hist.reserve(c, SL_STATUS, radix_sort_tile_words(n, L, ks.key_words));
     }
 };
 
@@ -371,9 +433,30 @@ int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_buck
     const CtxPtr& c = ix.ctx;
     const int n = ix.n, L = ix.L, NW = ix.ks.key_words;
     HostTrace tr;
+    // digit width: two ranked key bytes per pass when the hash values span at most 32 levels
+    int DB = 8;
+    uint32_t sub = 0;
+    if (SortBuffers::may_pair_bytes(ix.ks) && !getenv("CULSH_SORT_BYTE_DIGITS")) {
+        static const uint32_t init[2] = {0u, 256u};
+        Scratch<uint32_t> range(c, SL_MISC1, 2);
+        CU_CHECK(cudaMemcpyAsync(range.p, init, sizeof(init), cudaMemcpyHostToDevice, c->stream));
+        const size_t n_words = (size_t)n * L * NW;
+        key_byte_range_kernel<<<(unsigned)std::min<size_t>(ceil_div(n_words, 256), (size_t)c->sm_count * 16), 256, 0,
+                                c->stream>>>(sb.keys[0].p, n_words, range.p);
+        KERNEL_CHECK();
+        uint32_t r[2] = {0, 256};
+        read_words(c, range.p, sizeof(r), r);
+        const uint32_t n_pos = r[0] + 1, n_neg = 256 - r[1];
+        if (n_pos + n_neg <= 32) {
+            DB = 10;
+            sub = n_neg ? r[1] - n_pos : 0u;
+        }
+    }
+    const int passes = radix_sort_passes(ix.ks.key_bytes, DB);
+    sb.set_passes(passes);
     uint32_t* kp[2] = {sb.keys[0].p, sb.keys[1].p};
     uint32_t* vp[2] = {sb.vals[0], sb.vals[1]};
-    int cur = radix_sort_tables(c, NW, kp, vp, n, L, ix.ks.key_bytes, sb.tile_hist.p);
+    int cur = radix_sort_tables(c, NW, kp, vp, n, L, ix.ks.key_bytes, sb.tile_hist.p, DB, sub);
     tm.mark();
     const int tpt = (int)ceil_div(n, IB_TILE);
     const size_t n_tiles = (size_t)tpt * L;
@@ -421,7 +504,7 @@ int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_buck
     tm.mark();
     c->stats.n_items = (uint64_t)n * L;
     c->stats.n_buckets = B;
-    c->stats.sort_passes = ix.ks.key_bytes;
+    c->stats.sort_passes = passes;
     c->stats.key_words = NW;
     c->stats.elem_bytes = ix.ks.elem_bytes;
     return 0;
@@ -455,6 +538,7 @@ void fit_common(culsh_index& ix, HashFn&& hash_fn, Scratch<int32_t>* item_to_buc
         SortBuffers sb;
         sb.alloc(c, items, ix.ks, ix.n, ix.L);
         reset_error_word(c);
+        if (c->profiling) CU_CHECK(cudaMemsetAsync(c->d_mma, 0, 2 * sizeof(unsigned long long), c->stream));
         tm.mark();
         hash_fn(ix.ks, sb.keys[0].p);
         tm.mark();
@@ -471,6 +555,11 @@ void fit_common(culsh_index& ix, HashFn&& hash_fn, Scratch<int32_t>* item_to_buc
         c->stats.scatter_ms = tm.last_scatter();
         c->stats.build_ms = tm.between(2, 3);
         c->stats.total_ms = tm.between(0, 3);
+        if (c->profiling && c->stats.hash_path == 1) {
+            unsigned long long mma[2] = {0, 0};
+            read_words(c, c->d_mma, sizeof(mma), mma);
+            c->stats.hash_lo_fraction = mma[0] ? (float)((double)mma[1] / (double)mma[0]) : 0.f;
+        }
         break;
     }
 }
@@ -564,7 +653,6 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
                          (uint64_t)n_q * (uint64_t)n_win < (1ull << 31) &&
                          chain_window_smem_bytes(cbits, stage_ids) + 1024 <= c->smem_optin;
     const uint32_t n_other = (uint32_t)n_q - nb - nm;  // queries on the warp path (incl. empty ones)
-    bool streamed = false;
     Scratch<int32_t> tmp;
     tmp.reserve(c, SL_TMP, raw_total);
     tr.lap("alloc tmp");
@@ -583,80 +671,7 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
                                                        raw_cnt.p, raw_off.p, L, id_bytes, tmp.p, out.counts.p);
         KERNEL_CHECK();
     }
-    // Streamed form (persistent CTAs, id-balanced tickets, cp.async staging); the one-ticket-per-CTA
-    // kernel below stays for indexes whose bucket lists are not 16-byte aligned in memory and as
-    // the form selected by CULSH_CHAIN_V=1.
-    //   CULSH_CHAIN_BITS   largest window in rows (default 200,704)
-    //   CULSH_CHAIN_STAGE  ids per shared-memory buffer = stage size (default 4096)
-    //   CULSH_CHAIN_IDS    raw ids aimed at per ticket (default 3/4 of the buffer less the pad words)
-    //   CULSH_CHAIN_THREADS threads per CTA: 256, 384 or 512
-    if (chained && env_long("CULSH_CHAIN_V", 2) != 1 && (reinterpret_cast<uintptr_t>(ix.cand.p) & 15) == 0) {
-        const int W = (int)std::min<size_t>(std::max<size_t>(4096, (size_t)env_long("CULSH_CHAIN_BITS", 200704) / 4096 * 4096),
-                                            ceil_div((size_t)ix.n, 4096) * 4096);
-        const int cap = (int)std::min<long>(16384, std::max<long>(256, env_long("CULSH_CHAIN_STAGE", 4096))) / 4 * 4;
-        const int ids_per_ticket = (int)std::max<long>(64, env_long("CULSH_CHAIN_IDS", ((long)cap - 6L * L) * 3 / 4));
-        const int min_win = (int)ceil_div((size_t)ix.n, (size_t)W);
-        const int max_win = std::max(min_win, (int)std::min<size_t>(TK_MAX_WINDOWS, ceil_div((size_t)ix.n, 4096)));
-        const size_t n_tk_max = (size_t)(raw_total / (uint64_t)ids_per_ticket) + (size_t)n_q * ((size_t)min_win + 1);
-        const size_t smem = stream_smem_bytes(W, cap, L);
-        if (min_win <= CHAIN_MAX_WINDOWS && n_tk_max * (size_t)L <= ((size_t)64 << 20) && smem + 1024 <= c->smem_optin) {
-            out.indices.alloc(c, raw_total);  // capacity: the unique total is not known yet
-            Scratch<uint32_t> tk_cnt(c, SL_TK_CNT, n_q), tk_base(c, SL_TK_BASE, (size_t)n_q + 1);
-            Scratch<TicketDesc> descs(c, SL_TK_DESC, n_tk_max);
-            Scratch<int2> slices(c, SL_SLICES, n_tk_max * (size_t)L);
-            Scratch<unsigned long long> status(c, SL_CHAIN, n_tk_max + 1);
-            uint32_t* ticket = reinterpret_cast<uint32_t*>(status.p + n_tk_max);
-            CU_CHECK(cudaMemsetAsync(status.p, 0, sizeof(unsigned long long) * (n_tk_max + 1), s));
-            ticket_count_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(raw_cnt.p, n_q, mid_max, ids_per_ticket,
-                                                                           min_win, max_win, tk_cnt.p);
-            KERNEL_CHECK();
-            exclusive_scan<uint32_t, uint32_t>(s, tk_cnt.p, n_q, tk_base.p, reinterpret_cast<uint32_t*>(scratch.p));
-            ticket_table_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(raw_cnt.p, tk_base.p, n_q, ix.n, mid_max, descs.p);
-            KERNEL_CHECK();
-            ticket_slices_kernel<<<(unsigned)ceil_div(n_tk_max * (size_t)L, 256), 256, 0, s>>>(
-                descs.p, tk_base.p + n_q, matched, ix.bucket_offsets.p, ix.cand.p, L, ix.n, slices.p);
-            KERNEL_CHECK();
-            StreamArgs a{};
-            a.cand = ix.cand.p; a.raw_off = raw_off.p; a.tmp = tmp.p; a.descs = descs.p; a.slices = slices.p;
-            a.n_tickets = tk_base.p + n_q; a.status = status.p; a.ticket = ticket; a.out_indices = out.indices.p;
-            a.counts = out.counts.p; a.offsets = out.offsets.p; a.d_error = c->d_error;
-            a.n_q = n_q; a.L = L; a.n_rows = ix.n; a.window_bits = W; a.cap = cap;
-            auto launch = [&](auto nt_tag) {
-                constexpr int NT = decltype(nt_tag)::value;
-                CU_CHECK(cudaFuncSetAttribute(dedupe_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                CU_CHECK(cudaFuncSetAttribute(dedupe_stream_kernel<NT>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-                int per_sm = 0;
-                CU_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dedupe_stream_kernel<NT>, NT, smem));
-                const size_t grid = std::min<size_t>(n_tk_max, (size_t)c->sm_count * std::max(per_sm, 1));
-                dedupe_stream_kernel<NT><<<(unsigned)grid, NT, smem, s>>>(a);
-            };
-            const long st_threads = env_long("CULSH_CHAIN_THREADS", 384);
-            if (c->profiling) cudaEventRecord(c->ev_dedupe[0], s);
-            if (st_threads == 512) launch(std::integral_constant<int, 512>{});
-            else if (st_threads == 256) launch(std::integral_constant<int, 256>{});
-            else launch(std::integral_constant<int, 384>{});
-            KERNEL_CHECK();
-            if (c->profiling) { cudaEventRecord(c->ev_dedupe[1], s); dedupe_timed = true; }
-            counts_from_offsets_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(out.offsets.p, n_q, out.counts.p);
-            KERNEL_CHECK();
-            uint64_t total = 0;
-            read_words(c, out.offsets.p + n_q, sizeof(uint64_t), &total);
-            tr.lap("streamed dedupe+sync");
-            out.total = total;
-            c->stats.unique_candidates += total;
-            if (total == 0) {
-                out.indices.release();
-            } else if (total * 4 < raw_total * 3) {  // much smaller than the capacity: keep an exact copy
-                DevBuf<int32_t> exact(c, total);
-                CU_CHECK(cudaMemcpyAsync(exact.p, out.indices.p, sizeof(int32_t) * total, cudaMemcpyDeviceToDevice, s));
-                out.indices = std::move(exact);
-            }
-            streamed = true;
-        }
-    }
-    if (streamed) {
-        // done above
-    } else if (chained) {
+    if (chained) {
         out.indices.alloc(c, raw_total);  // capacity: the unique total is not known yet
         const size_t n_tk = (size_t)n_q * n_win;
         Scratch<unsigned long long> status(c, SL_CHAIN, n_tk + 1);
@@ -967,6 +982,8 @@ int culsh_create(int device, culsh_handle** out) {
         CU_CHECK(cudaMallocHost(&c->pinned, 64 * sizeof(uint64_t)));
         CU_CHECK(cudaMalloc(&c->d_error, sizeof(int)));
         CU_CHECK(cudaMemset(c->d_error, 0, sizeof(int)));
+        CU_CHECK(cudaMalloc(&c->d_mma, 2 * sizeof(unsigned long long)));
+        CU_CHECK(cudaMemset(c->d_mma, 0, 2 * sizeof(unsigned long long)));
         cudaDeviceProp prop{};
         CU_CHECK(cudaGetDeviceProperties(&prop, device));
         c->sm_count = prop.multiProcessorCount;
@@ -1542,6 +1559,75 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_q,
         CU_CHECK(cudaStreamSynchronize(s));
         tr.lap("merge: interleave+sync");
         *out = res.release();
+    });
+}
+
+// ---- shard exchange, push form -----------------------------------------------------------
+int culsh_exchange_plan(culsh_handle* h, int n_ranks, int rank, int n_q, const uint64_t* counts_all,
+                        uint64_t* dstpos, uint64_t* slice_totals, culsh_candidates** out) {
+    return guarded([&] {
+        if (!h || !counts_all || !dstpos || !slice_totals || !out) fail(CULSH_ERR_INVALID, "null argument");
+        if (n_ranks <= 0 || n_ranks > 64 || rank < 0 || rank >= n_ranks || n_q <= 0)
+            fail(CULSH_ERR_INVALID, "bad rank, rank count (1..64) or query count");
+        DeviceGuard g(h->ctx->device);
+        const CtxPtr& c = h->ctx;
+        cudaStream_t s = c->stream;
+        const int per = (int)ceil_div(n_q, n_ranks);
+        const int my_lo = std::min(n_q, rank * per), my_hi = std::min(n_q, my_lo + per);
+        auto res = std::make_unique<culsh_candidates>();
+        res->ctx = c;
+        res->n_queries = my_hi - my_lo;
+        res->counts.alloc(c, (size_t)std::max(1, my_hi - my_lo));
+        res->offsets.alloc(c, (size_t)(my_hi - my_lo) + 1);
+        Scratch<uint64_t> merged(c, SL_RAW_CNT, n_q), before(c, SL_MISC0, n_q), S(c, SL_RAW_OFF, (size_t)n_q + 1),
+            scratch(c, SL_SCAN, scan_scratch_elems(n_q)), totals(c, SL_MISC1, n_ranks);
+        exchange_counts_kernel<<<(unsigned)ceil_div(n_q, 256), 256, 0, s>>>(counts_all, n_ranks, rank, n_q, merged.p, before.p);
+        KERNEL_CHECK();
+        exclusive_scan<uint64_t, uint64_t>(s, merged.p, n_q, S.p, scratch.p);
+        exchange_positions_kernel<<<(unsigned)ceil_div((size_t)std::max(n_q + 1, n_ranks), 256), 256, 0, s>>>(
+            S.p, merged.p, before.p, n_q, per, n_ranks, my_lo, my_hi, dstpos, res->counts.p, res->offsets.p, totals.p);
+        KERNEL_CHECK();
+        read_words(c, totals.p, sizeof(uint64_t) * n_ranks, slice_totals);
+        res->total = slice_totals[rank];
+        *out = res.release();
+    });
+}
+
+int culsh_exchange_push(culsh_handle* h, int n_ranks, int n_q, const int32_t* indices, const uint64_t* offsets,
+                        const uint64_t* dstpos, void* const* recv, int64_t row_base, uint64_t total) {
+    return guarded([&] {
+        if (!h || !offsets || !dstpos || !recv) fail(CULSH_ERR_INVALID, "null argument");
+        if (n_ranks <= 0 || n_ranks > 64 || n_q <= 0) fail(CULSH_ERR_INVALID, "bad rank count (1..64) or query count");
+        DeviceGuard g(h->ctx->device);
+        const CtxPtr& c = h->ctx;
+        cudaStream_t s = c->stream;
+        if (total) {
+            if (!indices) fail(CULSH_ERR_INVALID, "indices is null");
+            Scratch<int32_t*> d_recv(c, SL_MISC2, n_ranks);
+            CU_CHECK(cudaMemcpyAsync(d_recv.p, recv, sizeof(void*) * n_ranks, cudaMemcpyHostToDevice, s));
+            const int per = (int)ceil_div(n_q, n_ranks);
+            if (total / (uint64_t)n_q >= 512) {
+                size_t blocks = std::min<size_t>((size_t)n_q, (size_t)c->sm_count * 8);
+                shard_push_kernel<<<(unsigned)blocks, 256, 0, s>>>(indices, offsets, dstpos, d_recv.p, per, n_q, (int32_t)row_base);
+            } else {
+                size_t blocks = std::min<size_t>(ceil_div((size_t)n_q * 32, 256), (size_t)c->sm_count * 32);
+                shard_push_small_kernel<<<(unsigned)blocks, 256, 0, s>>>(indices, offsets, dstpos, d_recv.p, per, n_q, (int32_t)row_base);
+            }
+            KERNEL_CHECK();
+        }
+        CU_CHECK(cudaStreamSynchronize(s));
+    });
+}
+
+int culsh_candidates_attach_indices(culsh_candidates* cd, const int32_t* indices, uint64_t total) {
+    return guarded([&] {
+        if (!cd) fail(CULSH_ERR_INVALID, "null candidates");
+        if (total && !indices) fail(CULSH_ERR_INVALID, "indices is null");
+        cd->indices.release();
+        cd->indices.p = const_cast<int32_t*>(indices);  // borrowed: no context, so release() frees nothing
+        cd->indices.n = total;
+        cd->indices.ctx = nullptr;
+        cd->total = total;
     });
 }
 

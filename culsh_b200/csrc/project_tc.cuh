@@ -52,6 +52,7 @@ struct TcArgs {
     uint32_t* keys;
     uint8_t* ovf_rows;
     int* d_error;
+    unsigned long long* d_mma;  // [0] K-blocks issued, [1] of them with the low-part MMA (or null)
     const float* bias;
     int n, d, L, k;
     int n_tiles, n_chunks, tables_per_chunk, n_mma, n_kblocks;
@@ -386,6 +387,7 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         if (lane == 0) {
             const uint32_t idesc = make_idesc_tf32(TC_BM, a.n_mma);
             uint32_t it = 0, u = 0;
+            unsigned long long n_kb = 0, n_lo = 0;
             bool live = true;
             for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
                 for (int c = 0; c < n_units_per_tile && live; ++c, ++u) {
@@ -402,6 +404,8 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                         tc_fence_after();
                         const int use_lo = s_lo_flag[s];
                         s_lo_flag[s] = 0;
+                        ++n_kb;
+                        n_lo += use_lo ? 1u : 0u;
                         const uint64_t dxh = make_smem_desc<KBLK>(smem_u32(xh(s)));
                         const uint64_t dxl = make_smem_desc<KBLK>(smem_u32(xl(s)));
                         const uint64_t dph = make_smem_desc<KBLK>(smem_u32(ph(s)));
@@ -417,6 +421,10 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     }
                     if (live) tc_commit(&acc_full[ab]);
                 }
+            }
+            if (a.d_mma) {
+                atomicAdd(a.d_mma, n_kb);
+                atomicAdd(a.d_mma + 1, n_lo);
             }
         }
     } else if (warp < 6) {
@@ -614,6 +622,7 @@ inline bool launch_project_tc(const CtxPtr& c, cudaStream_t stream, int family, 
         return false;
     TcArgs a{};
     a.keys = keys; a.ovf_rows = ovf_rows; a.d_error = c->d_error; a.bias = bias;
+    a.d_mma = c->d_mma;
     a.n = n; a.d = d; a.L = L; a.k = k;
     a.n_tiles = (int)ceil_div(n, TC_BM);
     a.n_chunks = p.n_chunks; a.tables_per_chunk = p.tables_per_chunk; a.n_mma = p.n_mma;

@@ -1139,4 +1139,89 @@ shard_interleave_small_kernel(const int32_t* const* __restrict__ shard_indices,
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Push form of the shard exchange.  Every rank holds the per-query unique counts of all ranks
+// (counts_all[r][q]); rank `rank` needs, for each query, where its own list starts inside the
+// merged list held by the query's owner (owner = q / per: the ranks own equal slices of the
+// queries), and the owner needs the counts / offsets of its slice.
+// ---------------------------------------------------------------------------------------
+// merged[q] = sum over ranks of counts_all[r][q]; before_me[q] = the part of it from ranks below `rank`
+__global__ void __launch_bounds__(256)
+exchange_counts_kernel(const uint64_t* __restrict__ counts_all, int n_ranks, int rank, int n_q,
+                       uint64_t* __restrict__ merged, uint64_t* __restrict__ before_me) {
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= n_q) return;
+    uint64_t all = 0, below = 0;
+    for (int r = 0; r < n_ranks; ++r) {
+        const uint64_t c = counts_all[(size_t)r * n_q + q];
+        if (r < rank) below += c;
+        all += c;
+    }
+    merged[q] = all;
+    before_me[q] = below;
+}
+
+// S = exclusive scan of merged over all queries (n_q + 1 entries).  dstpos[q] = position of this
+// rank's list of query q inside the owner's merged id array; the owner's own slice [my_lo, my_hi)
+// gets its counts and offsets; slice_totals[j] = ids of slice j.
+__global__ void __launch_bounds__(256)
+exchange_positions_kernel(const uint64_t* __restrict__ S, const uint64_t* __restrict__ merged,
+                          const uint64_t* __restrict__ before_me, int n_q, int per, int n_ranks, int my_lo,
+                          int my_hi, uint64_t* __restrict__ dstpos, uint64_t* __restrict__ my_counts,
+                          uint64_t* __restrict__ my_offsets, uint64_t* __restrict__ slice_totals) {
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q < n_ranks) {
+        const int lo = min(n_q, q * per), hi = min(n_q, lo + per);
+        slice_totals[q] = S[hi] - S[lo];
+    }
+    if (q > n_q) return;
+    if (q < n_q) dstpos[q] = S[q] - S[min(n_q, (q / per) * per)] + before_me[q];
+    if (q >= my_lo && q <= my_hi) {
+        my_offsets[q - my_lo] = S[q] - S[my_lo];
+        if (q < my_hi) my_counts[q - my_lo] = merged[q];
+    }
+}
+
+// This rank's lists, shifted to global row ids, stored into the owners' id arrays (recv[j] may
+// be peer memory: plain coalesced stores, reads are local).  CTA per query for long lists.
+__global__ void __launch_bounds__(256)
+shard_push_kernel(const int32_t* __restrict__ idx, const uint64_t* __restrict__ off,
+                  const uint64_t* __restrict__ dstpos, int32_t* const* __restrict__ recv, int per, int n_q,
+                  int32_t row_base) {
+    for (size_t q = blockIdx.x; q < (size_t)n_q; q += gridDim.x) {
+        const uint64_t s = off[q], len = off[q + 1] - s;
+        if (len == 0) continue;
+        const int32_t* src = idx + s;
+        int32_t* dst = recv[q / per] + dstpos[q];
+        for (uint64_t i0 = threadIdx.x; i0 < len; i0 += 256 * SI_UNROLL) {
+            int32_t v[SI_UNROLL];
+#pragma unroll
+            for (int j = 0; j < SI_UNROLL; ++j) {
+                const uint64_t i = i0 + 256 * j;
+                v[j] = i < len ? src[i] : 0;
+            }
+#pragma unroll
+            for (int j = 0; j < SI_UNROLL; ++j) {
+                const uint64_t i = i0 + 256 * j;
+                if (i < len) dst[i] = v[j] + row_base;
+            }
+        }
+    }
+}
+
+// warp per query, for results with short lists
+__global__ void __launch_bounds__(256)
+shard_push_small_kernel(const int32_t* __restrict__ idx, const uint64_t* __restrict__ off,
+                        const uint64_t* __restrict__ dstpos, int32_t* const* __restrict__ recv, int per,
+                        int n_q, int32_t row_base) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t n_warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t q = warp; q < (size_t)n_q; q += n_warps) {
+        const uint64_t s = off[q], len = off[q + 1] - s;
+        int32_t* dst = recv[q / per] + dstpos[q];
+        for (uint64_t i = lane; i < len; i += 32) dst[i] = idx[s + i] + row_base;
+    }
+}
+
 }  // namespace culsh_b200

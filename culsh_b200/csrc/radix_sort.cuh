@@ -7,6 +7,12 @@
 // offsets, and the stable scatter - so no CTA ever waits on another one: a chained
 // look-back between tiles was measured to cost more than the extra 4 bytes per item that
 // the histogram read adds at this bandwidth.
+//
+// Digits are 8 bits (one key byte per pass) or, for p-stable keys of one byte per hash whose
+// values span at most 32 levels, 10 bits: two key bytes per pass, each byte replaced by its rank
+// among the values in use (5 bits), which halves the number of passes.  The rank keeps the
+// unsigned order of the byte - non-negative values first, then the negative ones (two's
+// complement bytes 128..255) - so the sorted order is the same as with one byte per pass.
 #pragma once
 
 #include "common.cuh"
@@ -19,14 +25,15 @@ constexpr int RS_THREADS = 256;
 #endif
 constexpr int RS_WARPS = RS_THREADS / 32;
 
-template <int NW>
+template <int NW, int DB = 8>
 struct SortCfg {
     // items per thread: fewer for wide keys so that the tile's keys stay in registers at an
     // occupancy of 2-3 CTAs per SM
     static constexpr int IPT = NW == 1 ? 16 : (NW == 2 ? 12 : (NW == 4 ? 8 : (NW == 8 ? 4 : 2)));
     static constexpr int TILE = RS_THREADS * IPT;
+    static constexpr int NBINS = 1 << DB;
     static constexpr size_t SMEM =
-        sizeof(uint32_t) * ((size_t)TILE * NW + TILE + RS_WARPS * 256 + 256 + 256 + 32);
+        sizeof(uint32_t) * ((size_t)TILE * NW + TILE + RS_WARPS * NBINS + NBINS + NBINS + 32);
 };
 
 inline int sort_tile_items(int NW) {
@@ -39,15 +46,24 @@ inline int sort_tile_items(int NW) {
     }
 }
 
-// Byte p of a key (p = 0 least significant): word NW-1-p/4, shift 8*(p%4).
-template <int NW>
-__device__ __forceinline__ uint32_t key_digit(const uint32_t* key, int p) {
-    const int sel = NW - 1 - (p >> 2);
+// Digit p of a key (p = 0 least significant).  DB = 8: byte p (word NW-1-p/4, shift 8*(p%4)).
+// DB = 10: bytes 2p and 2p+1 (always in one word), each mapped to its 5-bit rank: a byte below 128
+// keeps its value, a byte from 128 up (a negative hash value) has `sub` taken off, where
+// sub = 256 + smallest negative value - (largest non-negative value + 1).
+template <int NW, int DB = 8>
+__device__ __forceinline__ uint32_t key_digit(const uint32_t* key, int p, uint32_t sub = 0u) {
+    const int b = DB == 8 ? p : 2 * p;
+    const int sel = NW - 1 - (b >> 2);
     uint32_t word = key[0];
 #pragma unroll
     for (int w = 1; w < NW; ++w)  // select chain keeps the key in registers
         if (w == sel) word = key[w];
-    return (word >> (8 * (p & 3))) & 0xFFu;
+    if (DB == 8) return (word >> (8 * (b & 3))) & 0xFFu;
+    const uint32_t v = (word >> (8 * (b & 3))) & 0xFFFFu;
+    uint32_t lo = v & 0xFFu, hi = v >> 8;
+    lo -= (lo >> 7) * sub;
+    hi -= (hi >> 7) * sub;
+    return ((hi << 5) | lo) & 0x3FFu;
 }
 
 template <int NW>
@@ -84,26 +100,39 @@ __device__ __forceinline__ void store_key(uint32_t* __restrict__ dst, const uint
 // Pass step 1: digit histogram of every tile (a tile is TILE consecutive items of one
 // table).  tile_hist layout: [tile][256].
 // ---------------------------------------------------------------------------------------
-template <int NW>
+template <int NW, int DB>
 __global__ void __launch_bounds__(RS_THREADS)
-radix_tile_hist_kernel(const uint32_t* __restrict__ keys, int n, int tiles_per_table, int p,
+radix_tile_hist_kernel(const uint32_t* __restrict__ keys, int n, int tiles_per_table, int p, uint32_t sub,
                        uint32_t* __restrict__ tile_hist) {
-    using Cfg = SortCfg<NW>;
-    __shared__ uint32_t s_hist[256];
+    using Cfg = SortCfg<NW, DB>;
+    constexpr int NBINS = Cfg::NBINS;
+    __shared__ uint32_t s_hist[NBINS];
     const int tile = blockIdx.x;
     const int t = tile / tiles_per_table;
     const int lt = tile - t * tiles_per_table;
     const int item0 = lt * Cfg::TILE;
     const int count = min(Cfg::TILE, n - item0);
-    const uint32_t* base = keys + ((size_t)t * n + item0) * NW + (NW - 1 - (p >> 2));
-    const int shift = 8 * (p & 3);
-    s_hist[threadIdx.x] = 0;
+    const int b = DB == 8 ? p : 2 * p;
+    const uint32_t* base = keys + ((size_t)t * n + item0) * NW + (NW - 1 - (b >> 2));
+    const int shift = 8 * (b & 3);
+    for (int i = threadIdx.x; i < NBINS; i += RS_THREADS) s_hist[i] = 0;
     __syncthreads();
 #pragma unroll 4
-    for (int i = threadIdx.x; i < count; i += RS_THREADS)
-        atomicAdd(&s_hist[(base[(size_t)i * NW] >> shift) & 0xFFu], 1u);
+    for (int i = threadIdx.x; i < count; i += RS_THREADS) {
+        const uint32_t w = base[(size_t)i * NW] >> shift;
+        uint32_t d;
+        if (DB == 8) {
+            d = w & 0xFFu;
+        } else {
+            uint32_t lo = w & 0xFFu, hi = (w >> 8) & 0xFFu;
+            lo -= (lo >> 7) * sub;
+            hi -= (hi >> 7) * sub;
+            d = ((hi << 5) | lo) & 0x3FFu;
+        }
+        atomicAdd(&s_hist[d], 1u);
+    }
     __syncthreads();
-    tile_hist[(size_t)tile * 256 + threadIdx.x] = s_hist[threadIdx.x];
+    for (int i = threadIdx.x; i < NBINS; i += RS_THREADS) tile_hist[(size_t)tile * NBINS + i] = s_hist[i];
 }
 
 // ---------------------------------------------------------------------------------------
@@ -113,26 +142,27 @@ radix_tile_hist_kernel(const uint32_t* __restrict__ keys, int n, int tiles_per_t
 // 1024 threads = 4 tile segments x 256 digits.
 // ---------------------------------------------------------------------------------------
 constexpr int RS_SCAN_THREADS = 1024;
-constexpr int RS_SCAN_SEGS = RS_SCAN_THREADS / 256;
 
+template <int NBINS>
 __global__ void __launch_bounds__(RS_SCAN_THREADS)
 radix_tile_scan_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table) {
-    __shared__ uint32_t s_seg[RS_SCAN_SEGS][256];
-    __shared__ uint32_t s_base[256];
-    __shared__ uint32_t s_warp[8];
-    const int d = threadIdx.x & 255, seg = threadIdx.x >> 8;
-    uint32_t* h = tile_hist + (size_t)blockIdx.x * tiles_per_table * 256 + d;
-    const int per_seg = (tiles_per_table + RS_SCAN_SEGS - 1) / RS_SCAN_SEGS;
+    constexpr int SEGS = RS_SCAN_THREADS / NBINS;  // 4 tile segments x 256 digits, or 1 x 1024
+    __shared__ uint32_t s_seg[SEGS][NBINS];
+    __shared__ uint32_t s_base[NBINS];
+    __shared__ uint32_t s_warp[NBINS / 32];
+    const int d = threadIdx.x & (NBINS - 1), seg = threadIdx.x / NBINS;
+    uint32_t* h = tile_hist + (size_t)blockIdx.x * tiles_per_table * NBINS + d;
+    const int per_seg = (tiles_per_table + SEGS - 1) / SEGS;
     const int i0 = seg * per_seg, i1 = min(tiles_per_table, i0 + per_seg);
     uint32_t sum = 0;
 #pragma unroll 8
-    for (int i = i0; i < i1; ++i) sum += h[(size_t)i * 256];
+    for (int i = i0; i < i1; ++i) sum += h[(size_t)i * NBINS];
     s_seg[seg][d] = sum;
     __syncthreads();
-    if (seg == 0) {  // exclusive scan of the digit totals over the 256 digits
+    if (seg == 0) {  // exclusive scan of the digit totals over the digits
         uint32_t tot = 0;
 #pragma unroll
-        for (int g = 0; g < RS_SCAN_SEGS; ++g) tot += s_seg[g][d];
+        for (int g = 0; g < SEGS; ++g) tot += s_seg[g][d];
         const int lane = d & 31, w = d >> 5;
         uint32_t inc = tot;
 #pragma unroll
@@ -149,8 +179,8 @@ radix_tile_scan_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table) {
     for (int g = 0; g < seg; ++g) run += s_seg[g][d];
 #pragma unroll 8
     for (int i = i0; i < i1; ++i) {
-        uint32_t x = h[(size_t)i * 256];
-        h[(size_t)i * 256] = run;
+        uint32_t x = h[(size_t)i * NBINS];
+        h[(size_t)i * NBINS] = run;
         run += x;
     }
 }
@@ -163,45 +193,48 @@ radix_tile_scan_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table) {
 constexpr int RS_CHUNK_TILES = 256;
 constexpr int RS_CHUNK_MIN_TILES = 512;  // tables with fewer tiles keep the single-launch scan
 
+template <int NBINS>
 __global__ void __launch_bounds__(RS_SCAN_THREADS)
 radix_tile_scan_chunk_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table, int n_chunks,
-                             uint32_t* __restrict__ chunk_tot /* [table][chunk][256] */) {
-    __shared__ uint32_t s_seg[RS_SCAN_SEGS][256];
-    const int d = threadIdx.x & 255, seg = threadIdx.x >> 8;
+                             uint32_t* __restrict__ chunk_tot /* [table][chunk][NBINS] */) {
+    constexpr int SEGS = RS_SCAN_THREADS / NBINS;
+    __shared__ uint32_t s_seg[SEGS][NBINS];
+    const int d = threadIdx.x & (NBINS - 1), seg = threadIdx.x / NBINS;
     const int table = blockIdx.x / n_chunks, chunk = blockIdx.x - table * n_chunks;
     const int t_begin = chunk * RS_CHUNK_TILES, t_end = min(tiles_per_table, t_begin + RS_CHUNK_TILES);
-    uint32_t* h = tile_hist + (size_t)table * tiles_per_table * 256 + d;
-    const int per_seg = (t_end - t_begin + RS_SCAN_SEGS - 1) / RS_SCAN_SEGS;
+    uint32_t* h = tile_hist + (size_t)table * tiles_per_table * NBINS + d;
+    const int per_seg = (t_end - t_begin + SEGS - 1) / SEGS;
     const int i0 = t_begin + seg * per_seg, i1 = min(t_end, i0 + per_seg);
     uint32_t sum = 0;
 #pragma unroll 8
-    for (int i = i0; i < i1; ++i) sum += h[(size_t)i * 256];
+    for (int i = i0; i < i1; ++i) sum += h[(size_t)i * NBINS];
     s_seg[seg][d] = sum;
     __syncthreads();
     uint32_t run = 0, tot = 0;
 #pragma unroll
-    for (int g = 0; g < RS_SCAN_SEGS; ++g) {
+    for (int g = 0; g < SEGS; ++g) {
         const uint32_t x = s_seg[g][d];
         if (g < seg) run += x;
         tot += x;
     }
-    if (seg == 0) chunk_tot[(size_t)blockIdx.x * 256 + d] = tot;
+    if (seg == 0) chunk_tot[(size_t)blockIdx.x * NBINS + d] = tot;
 #pragma unroll 8
     for (int i = i0; i < i1; ++i) {
-        const uint32_t x = h[(size_t)i * 256];
-        h[(size_t)i * 256] = run;
+        const uint32_t x = h[(size_t)i * NBINS];
+        h[(size_t)i * NBINS] = run;
         run += x;
     }
 }
 
-// one block of 256 threads per table: chunk_tot -> chunk bases, in place
-__global__ void __launch_bounds__(256)
+// one block of NBINS threads per table: chunk_tot -> chunk bases, in place
+template <int NBINS>
+__global__ void __launch_bounds__(NBINS)
 radix_chunk_base_kernel(uint32_t* __restrict__ chunk_tot, int n_chunks) {
-    __shared__ uint32_t s_warp[8];
+    __shared__ uint32_t s_warp[NBINS / 32];
     const int d = threadIdx.x, lane = d & 31, w = d >> 5;
-    uint32_t* ct = chunk_tot + (size_t)blockIdx.x * n_chunks * 256 + d;
+    uint32_t* ct = chunk_tot + (size_t)blockIdx.x * n_chunks * NBINS + d;
     uint32_t tot = 0;
-    for (int c = 0; c < n_chunks; ++c) tot += ct[(size_t)c * 256];
+    for (int c = 0; c < n_chunks; ++c) tot += ct[(size_t)c * NBINS];
     uint32_t inc = tot;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -213,31 +246,33 @@ radix_chunk_base_kernel(uint32_t* __restrict__ chunk_tot, int n_chunks) {
     uint32_t run = inc - tot;
     for (int i = 0; i < w; ++i) run += s_warp[i];
     for (int c = 0; c < n_chunks; ++c) {
-        const uint32_t x = ct[(size_t)c * 256];
-        ct[(size_t)c * 256] = run;
+        const uint32_t x = ct[(size_t)c * NBINS];
+        ct[(size_t)c * NBINS] = run;
         run += x;
     }
 }
 
 // ---------------------------------------------------------------------------------------
-// Pass step 3: stable scatter of one tile on byte `p`.
+// Pass step 3: stable scatter of one tile on digit `p`.
 // ---------------------------------------------------------------------------------------
-template <int NW, bool FIRST>
-__global__ void __launch_bounds__(RS_THREADS, (NW == 1 ? 4 : RS_MIN_BLOCKS))
+template <int NW, bool FIRST, int DB>
+__global__ void __launch_bounds__(RS_THREADS, (DB == 8 ? (NW == 1 ? 4 : RS_MIN_BLOCKS) : 2))
 radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int n,
-                     int tiles_per_table, int p, const uint32_t* __restrict__ tile_off,
+                     int tiles_per_table, int p, uint32_t sub, const uint32_t* __restrict__ tile_off,
                      const uint32_t* __restrict__ chunk_base /* or null */, int n_chunks) {
-    using Cfg = SortCfg<NW>;
+    using Cfg = SortCfg<NW, DB>;
     constexpr int IPT = Cfg::IPT;
     constexpr int TILE = Cfg::TILE;
+    constexpr int NBINS = Cfg::NBINS;
+    constexpr int BPT = NBINS / RS_THREADS;  // bins per thread: 1 or 4, contiguous
     extern __shared__ __align__(16) uint32_t smem[];
     uint32_t* s_keys = smem;                       // [TILE][NW]
     uint32_t* s_vals = s_keys + (size_t)TILE * NW; // [TILE]
-    uint32_t* s_whist = s_vals + TILE;             // [RS_WARPS][256]
-    uint32_t* s_gdst = s_whist + RS_WARPS * 256;   // [256] global dst of local position 0 of a bin
-    uint32_t* s_binstart = s_gdst + 256;           // [256]
-    uint32_t* s_misc = s_binstart + 256;           // [32]
+    uint32_t* s_whist = s_vals + TILE;             // [RS_WARPS][NBINS]
+    uint32_t* s_gdst = s_whist + RS_WARPS * NBINS; // [NBINS] global dst of local position 0 of a bin
+    uint32_t* s_binstart = s_gdst + NBINS;         // [NBINS]
+    uint32_t* s_misc = s_binstart + NBINS;         // [32]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = blockIdx.x;
@@ -248,9 +283,14 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     const size_t base = (size_t)t * n + item0;
     // needed late: fetched early, and summed only where used (an add here would stall the warp on
     // both loads before the key loads are issued)
-    const uint32_t my_off = tile_off[(size_t)tile * 256 + tid];
-    const uint32_t my_base = chunk_base ? chunk_base[((size_t)t * n_chunks + lt / RS_CHUNK_TILES) * 256 + tid] : 0u;
-    for (int i = tid; i < RS_WARPS * 256; i += RS_THREADS) s_whist[i] = 0;
+    uint32_t my_off[BPT], my_base[BPT];
+#pragma unroll
+    for (int j = 0; j < BPT; ++j) {
+        const int bin = tid * BPT + j;
+        my_off[j] = tile_off[(size_t)tile * NBINS + bin];
+        my_base[j] = chunk_base ? chunk_base[((size_t)t * n_chunks + lt / RS_CHUNK_TILES) * NBINS + bin] : 0u;
+    }
+    for (int i = tid; i < RS_WARPS * NBINS; i += RS_THREADS) s_whist[i] = 0;
 
     // ---- load (all loads in flight together) ------------------------------------------
     uint32_t key[IPT][NW];
@@ -276,12 +316,12 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     for (int i = 0; i < IPT; ++i) {
         const int li = warp * (32 * IPT) + i * 32 + lane;
         const bool valid = li < count;
-        const uint32_t d = valid ? key_digit<NW>(key[i], p) : 0x100u;
+        const uint32_t d = valid ? key_digit<NW, DB>(key[i], p, sub) : 0xFFFFu;
         // lanes with the same digit.  For one-word keys the kernel is bound by the latency of the
         // shared-memory / match pipeline, and nine ballots (digit bits + validity) are cheaper
         // than match.any; wider keys are bandwidth-bound and take the shorter instruction.
         uint32_t peers;
-        if constexpr (NW == 1) {
+        if constexpr (NW == 1 && DB == 8) {
             peers = count == TILE ? 0xFFFFFFFFu : __ballot_sync(0xFFFFFFFFu, valid);
             if (!valid) peers = ~peers;
 #pragma unroll
@@ -296,7 +336,7 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
         const int leader = __ffs(peers) - 1;
         const uint32_t below = __popc(peers & ((1u << lane) - 1));
         uint32_t old = 0;
-        if (valid && lane == leader) old = atomicAdd(&s_whist[warp * 256 + d], (uint32_t)__popc(peers));
+        if (valid && lane == leader) old = atomicAdd(&s_whist[warp * NBINS + d], (uint32_t)__popc(peers));
         old = __shfl_sync(0xFFFFFFFFu, old, leader);
         rank[i] = (uint16_t)(old + below);
         dig[i] = (uint16_t)d;
@@ -304,17 +344,21 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     __syncthreads();
 
     // ---- per bin: exclusive offsets of the warps, tile count, start inside the tile ----
-    uint32_t cnt = 0;
-    {
-        const int b = tid;
+    uint32_t cnt[BPT], tsum = 0;
+#pragma unroll
+    for (int j = 0; j < BPT; ++j) {
+        const int b = tid * BPT + j;
+        uint32_t c = 0;
 #pragma unroll
         for (int w = 0; w < RS_WARPS; ++w) {
-            uint32_t x = s_whist[w * 256 + b];
-            s_whist[w * 256 + b] = cnt;
-            cnt += x;
+            uint32_t x = s_whist[w * NBINS + b];
+            s_whist[w * NBINS + b] = c;
+            c += x;
         }
+        cnt[j] = c;
+        tsum += c;
     }
-    uint32_t inc = cnt;
+    uint32_t inc = tsum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
@@ -324,17 +368,22 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     __syncthreads();
     uint32_t wbase = 0;
     for (int i = 0; i < warp; ++i) wbase += s_misc[1 + i];
-    const uint32_t binstart = wbase + inc - cnt;
-    s_binstart[tid] = binstart;
-    s_gdst[tid] = (uint32_t)((size_t)t * n) + my_off + my_base - binstart;
+    uint32_t binstart = wbase + inc - tsum;
+#pragma unroll
+    for (int j = 0; j < BPT; ++j) {
+        const int b = tid * BPT + j;
+        s_binstart[b] = binstart;
+        s_gdst[b] = (uint32_t)((size_t)t * n) + my_off[j] + my_base[j] - binstart;
+        binstart += cnt[j];
+    }
     __syncthreads();
 
     // ---- reorder inside shared memory ------------------------------------------------
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
         const uint32_t d = dig[i];
-        if (d < 256u) {
-            const uint32_t pos = s_binstart[d] + s_whist[warp * 256 + d] + rank[i];
+        if (d < (uint32_t)NBINS) {
+            const uint32_t pos = s_binstart[d] + s_whist[warp * NBINS + d] + rank[i];
 #pragma unroll
             for (int w = 0; w < NW; ++w) s_keys[(size_t)pos * NW + w] = key[i][w];
             s_vals[pos] = val[i];
@@ -347,7 +396,7 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
         uint32_t kk[NW];
 #pragma unroll
         for (int w = 0; w < NW; ++w) kk[w] = s_keys[(size_t)pos * NW + w];
-        const uint32_t d = key_digit<NW>(kk, p);
+        const uint32_t d = key_digit<NW, DB>(kk, p, sub);
         const uint32_t g = s_gdst[d] + (uint32_t)pos;
         store_key<NW>(keys_out + (size_t)g * NW, kk);
         vals_out[g] = s_vals[pos];
@@ -355,47 +404,78 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
 }
 
 // ---------------------------------------------------------------------------------------
-// Host driver.  keys[0]/vals[0] hold the input (vals[0] is never read: the first pass
-// takes the row id from the position); returns which buffer (0/1) holds the result.
-// tile_hist must hold radix_sort_tile_words(n, L, NW) words.
+// Range of the key bytes of p-stable keys with one byte per hash: out[0] = largest byte below
+// 128 (largest non-negative hash value, 0 if none), out[1] = smallest byte from 128 up (the
+// smallest negative value as an unsigned byte, 256 if none).  out must hold {0, 256} before.
 // ---------------------------------------------------------------------------------------
-template <int NW>
+__global__ void __launch_bounds__(256)
+key_byte_range_kernel(const uint32_t* __restrict__ keys, size_t n_words, uint32_t* __restrict__ out) {
+    uint32_t hi_pos = 0, lo_neg = 256;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t w = keys[i];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const uint32_t u = (w >> (8 * b)) & 0xFFu;
+            if (u < 128u) hi_pos = max(hi_pos, u); else lo_neg = min(lo_neg, u);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        hi_pos = max(hi_pos, __shfl_xor_sync(0xFFFFFFFFu, hi_pos, o));
+        lo_neg = min(lo_neg, __shfl_xor_sync(0xFFFFFFFFu, lo_neg, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicMax(&out[0], hi_pos);
+        atomicMin(&out[1], lo_neg);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host driver.  keys[0]/vals[0] hold the input (vals[0] is never read: the first pass
+// takes the row id from the position); after `passes` passes the result is in buffer
+// passes & 1.  tile_hist must hold radix_sort_tile_words(n, L, NW, DB) words.
+// ---------------------------------------------------------------------------------------
+inline int radix_sort_passes(int KB, int DB) { return DB == 8 ? KB : (KB + 1) / 2; }
+
+template <int NW, int DB>
 inline int radix_sort_tables_nw(const CtxPtr& c, uint32_t* keys[2], uint32_t* vals[2], int n, int L,
-                                int KB, uint32_t* tile_hist) {
-    using Cfg = SortCfg<NW>;
+                                int KB, uint32_t sub, uint32_t* tile_hist) {
+    using Cfg = SortCfg<NW, DB>;
+    constexpr int NBINS = Cfg::NBINS;
     cudaStream_t s = c->stream;
     const int tiles_per_table = (int)ceil_div(n, Cfg::TILE);
     const size_t total_tiles = (size_t)tiles_per_table * L;
-    auto k_first = radix_scatter_kernel<NW, true>;
-    auto k_next = radix_scatter_kernel<NW, false>;
+    auto k_first = radix_scatter_kernel<NW, true, DB>;
+    auto k_next = radix_scatter_kernel<NW, false, DB>;
     CU_CHECK(cudaFuncSetAttribute(k_first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     CU_CHECK(cudaFuncSetAttribute(k_next, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     const bool chunked = tiles_per_table >= RS_CHUNK_MIN_TILES;
     const int n_chunks = chunked ? (int)ceil_div(tiles_per_table, RS_CHUNK_TILES) : 1;
-    uint32_t* chunk_tot = tile_hist + total_tiles * 256;  // [L][n_chunks][256], behind the tile histograms
+    uint32_t* chunk_tot = tile_hist + total_tiles * NBINS;  // [L][n_chunks][NBINS], behind the tile histograms
+    const int passes = radix_sort_passes(KB, DB);
     int cur = 0;
-    for (int p = 0; p < KB; ++p) {
-        radix_tile_hist_kernel<NW><<<(unsigned)total_tiles, RS_THREADS, 0, s>>>(keys[cur], n, tiles_per_table,
-                                                                              p, tile_hist);
+    for (int p = 0; p < passes; ++p) {
+        radix_tile_hist_kernel<NW, DB><<<(unsigned)total_tiles, RS_THREADS, 0, s>>>(keys[cur], n, tiles_per_table,
+                                                                                  p, sub, tile_hist);
         KERNEL_CHECK();
         if (chunked) {
-            radix_tile_scan_chunk_kernel<<<(unsigned)(L * n_chunks), RS_SCAN_THREADS, 0, s>>>(
+            radix_tile_scan_chunk_kernel<NBINS><<<(unsigned)(L * n_chunks), RS_SCAN_THREADS, 0, s>>>(
                 tile_hist, tiles_per_table, n_chunks, chunk_tot);
             KERNEL_CHECK();
-            radix_chunk_base_kernel<<<(unsigned)L, 256, 0, s>>>(chunk_tot, n_chunks);
+            radix_chunk_base_kernel<NBINS><<<(unsigned)L, NBINS, 0, s>>>(chunk_tot, n_chunks);
         } else {
-            radix_tile_scan_kernel<<<(unsigned)L, RS_SCAN_THREADS, 0, s>>>(tile_hist, tiles_per_table);
+            radix_tile_scan_kernel<NBINS><<<(unsigned)L, RS_SCAN_THREADS, 0, s>>>(tile_hist, tiles_per_table);
         }
         KERNEL_CHECK();
-        const bool last = p == KB - 1;
+        const bool last = p == passes - 1;
         if (last && c->profiling) cudaEventRecord(c->ev_pass[0], s);
         if (p == 0)
             k_first<<<(unsigned)total_tiles, RS_THREADS, Cfg::SMEM, s>>>(
-                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, tile_hist,
+                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, sub, tile_hist,
                 chunked ? chunk_tot : nullptr, n_chunks);
         else
             k_next<<<(unsigned)total_tiles, RS_THREADS, Cfg::SMEM, s>>>(
-                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, tile_hist,
+                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, sub, tile_hist,
                 chunked ? chunk_tot : nullptr, n_chunks);
         KERNEL_CHECK();
         if (last && c->profiling) cudaEventRecord(c->ev_pass[1], s);
@@ -404,19 +484,28 @@ inline int radix_sort_tables_nw(const CtxPtr& c, uint32_t* keys[2], uint32_t* va
     return cur;
 }
 
-inline size_t radix_sort_tile_words(int n, int L, int NW) {
+inline size_t radix_sort_tile_words(int n, int L, int NW, int DB = 8) {
     const size_t tiles = ceil_div(n, sort_tile_items(NW));
-    return (tiles + ceil_div(tiles, (size_t)RS_CHUNK_TILES)) * (size_t)L * 256;  // tile histograms + chunk totals
+    return (tiles + ceil_div(tiles, (size_t)RS_CHUNK_TILES)) * (size_t)L * ((size_t)1 << DB);  // tile histograms + chunk totals
 }
 
+// DB = 10 (two ranked bytes per pass) is available for keys of up to four words.
 inline int radix_sort_tables(const CtxPtr& c, int NW, uint32_t* keys[2], uint32_t* vals[2], int n,
-                             int L, int KB, uint32_t* tile_hist) {
+                             int L, int KB, uint32_t* tile_hist, int DB = 8, uint32_t sub = 0u) {
+    if (DB == 10) {
+        switch (NW) {
+            case 1: return radix_sort_tables_nw<1, 10>(c, keys, vals, n, L, KB, sub, tile_hist);
+            case 2: return radix_sort_tables_nw<2, 10>(c, keys, vals, n, L, KB, sub, tile_hist);
+            case 4: return radix_sort_tables_nw<4, 10>(c, keys, vals, n, L, KB, sub, tile_hist);
+        }
+        fail(CULSH_ERR_INTERNAL, "10-bit digits need a key of at most four words");
+    }
     switch (NW) {
-        case 1: return radix_sort_tables_nw<1>(c, keys, vals, n, L, KB, tile_hist);
-        case 2: return radix_sort_tables_nw<2>(c, keys, vals, n, L, KB, tile_hist);
-        case 4: return radix_sort_tables_nw<4>(c, keys, vals, n, L, KB, tile_hist);
-        case 8: return radix_sort_tables_nw<8>(c, keys, vals, n, L, KB, tile_hist);
-        case 16: return radix_sort_tables_nw<16>(c, keys, vals, n, L, KB, tile_hist);
+        case 1: return radix_sort_tables_nw<1, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
+        case 2: return radix_sort_tables_nw<2, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
+        case 4: return radix_sort_tables_nw<4, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
+        case 8: return radix_sort_tables_nw<8, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
+        case 16: return radix_sort_tables_nw<16, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
     }
     fail(CULSH_ERR_UNSUPPORTED, "unsupported key width: %d words", NW);
 }

@@ -157,20 +157,22 @@ def exchange_by_query(cand, row_base: int, group=None, row_bases: Optional[List[
 
 
 class PeerExchange:
-    """Shard exchange over peer memory: every rank publishes its per-shard CSR in a device buffer
-    that the other processes of the box have mapped (CUDA IPC), and the merge kernel of each
-    rank pulls the lists of ITS query slice straight out of the peers' buffers over NVLink
-    while it interleaves them - transfer and merge are one kernel, there is no staging copy
-    and no collective on the data path.  The process group (any backend) only carries the
-    64-byte handles and one one-word all-reduce per exchange (barrier + capacity agreement).
+    """Shard exchange over peer memory, push form.  Rank j owns the j-th slice of the queries and
+    keeps a receive buffer that the other processes of the box have mapped (CUDA IPC).  Per
+    exchange the ranks all-gather their per-query candidate counts (small), every rank works out
+    where each of its lists belongs inside the owner's merged id array, and one kernel per rank
+    stores its lists, shifted to global row ids, straight into the owners' buffers over NVLink
+    (plain coalesced stores to peer memory; the reads are local).  A barrier later the owners'
+    buffers hold the merged CSR of their slices - there is no staging copy and no collective on
+    the data path.
 
-    Every rank's buffer has two halves used alternately, so a rank may publish its next result
-    while a slower peer is still reading the previous one; a peer has always finished reading a
-    half before it joins the barrier of the following exchange, after which that half is free.
-    Layout of a half: [n_queries + 1 int64 offsets | padding to 256 B | int32 indices].
+    A receive buffer has two halves used alternately, and the returned result's ids live in the
+    half just filled: a result stays valid until the second exchange after the one that made it
+    (and no longer than this object).  When a result outgrows the halves every rank allocates
+    larger ones; the old buffers are kept for two more exchanges for the same reason.
     """
 
-    GROW_ALIGN = 1 << 21   # buffer halves grow to 1.25x the need, rounded up to this many bytes
+    GROW_ALIGN = 1 << 21   # halves grow to 1.25x the need, rounded up to this many bytes
 
     def __init__(self, group=None, device: Optional[int] = None):
         import torch.distributed as dist
@@ -183,48 +185,54 @@ class PeerExchange:
         self.phase = 0         # half used by the next exchange
         self.local = None      # device address of my buffer (two halves)
         self.peers = []        # device addresses of every rank's buffer as mapped here
+        self.retired = []      # [age, local, peers] of outgrown buffers that results may still use
 
-    def _close(self):
-        """Collective teardown in two phases: every rank first unmaps its peers' buffers, the
-        group meets at a barrier, and only then each rank frees the buffer it exported - a
-        buffer must not be freed while another process still has it mapped.  If a rank
-        failed on the way (the barrier raises), the export is left to the driver at process
-        exit rather than freed early."""
+    def _unmap_and_free(self, sets):
+        """Collective, two phases: every rank unmaps its peers' buffers, the group meets at a
+        barrier, and only then each rank frees what it exported - a buffer must not be freed
+        while another process still has it mapped.  If a rank failed on the way (the barrier
+        raises), the exports are left to the driver at process exit rather than freed early."""
         import ctypes as C
         import torch.distributed as dist
         from . import _lib
-        if not self.local and not self.peers:
+        if not sets:
             return
-        for r, p in enumerate(self.peers):
-            if r != self.rank and p:
-                _lib.check(self.h.lib.culsh_peer_close(self.h.ptr, C.c_void_p(p)))
-        self.peers = []
-        local, self.local, self.capacity = self.local, None, 0
+        for local, peers in sets:
+            for r, p in enumerate(peers):
+                if r != self.rank and p:
+                    _lib.check(self.h.lib.culsh_peer_close(self.h.ptr, C.c_void_p(p)))
         dist.barrier(self.group)   # all importers have unmapped
-        if local:
-            _lib.check(self.h.lib.culsh_peer_free(self.h.ptr, C.c_void_p(local)))
+        for local, peers in sets:
+            if local:
+                _lib.check(self.h.lib.culsh_peer_free(self.h.ptr, C.c_void_p(local)))
 
     def close(self):
+        """Collective.  Results obtained from this object must not be used afterwards."""
         import torch.distributed as dist
-        dist.barrier(self.group)   # nobody is still reading
-        self._close()
+        dist.barrier(self.group)   # nobody is still writing or reading
+        sets = [(loc, peers) for _, loc, peers in self.retired]
+        if self.local or self.peers:
+            sets.append((self.local, self.peers))
+        self.retired, self.local, self.peers, self.capacity = [], None, [], 0
+        self._unmap_and_free(sets)
 
-    def _sync_max(self, value: int) -> int:
-        """All-reduce(max) of one integer; doubles as a barrier over the group."""
+    def _barrier(self):
+        """One-word all-reduce: a barrier over the group on any backend."""
         import torch
         import torch.distributed as dist
         on_gpu = dist.get_backend(self.group) == "nccl"
-        t = torch.tensor([int(value)], dtype=torch.int64,
-                         device=f"cuda:{self.h.device}" if on_gpu else "cpu")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
-        return int(t.item())
+        t = torch.zeros(1, dtype=torch.int64, device=f"cuda:{self.h.device}" if on_gpu else "cpu")
+        dist.all_reduce(t, group=self.group)
+        t.item()
 
     def _grow(self, need: int):
-        """Collective (every rank calls it with the same `need`): allocate, export, map."""
+        """Collective (every rank calls it with the same `need`): allocate, export, map.  The
+        outgrown buffers are retired, not freed: earlier results may still point into them."""
         import ctypes as C
         import torch.distributed as dist
         from . import _lib
-        self._close()
+        if self.local or self.peers:
+            self.retired.append([0, self.local, self.peers])
         a = self.GROW_ALIGN
         cap = (int(need * 1.25) + a) // a * a
         ptr = C.c_void_p()
@@ -242,36 +250,57 @@ class PeerExchange:
                 _lib.check(self.h.lib.culsh_peer_open(self.h.ptr, hb, C.byref(q)))
                 self.peers.append(q.value)
 
-    def exchange(self, cand, row_bases: List[int]):
-        """Returns (Candidates of my query slice with global row ids, (q_lo, q_hi))."""
-        import ctypes as C
+    def _all_counts(self, cand):
+        """[world, n_queries] int64 device tensor of every rank's per-query candidate counts."""
+        import torch
         import torch.distributed as dist
+        _, cp, _ = cand.device_pointers()
+        dev = f"cuda:{self.h.device}"
+        nq = cand.n_queries
+        mine = torch.as_tensor(_DeviceView(cp, nq, "<i8", cand), device=dev)
+        if dist.get_backend(self.group) == "nccl":
+            out = torch.empty(self.world * nq, dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(out, mine, group=self.group)
+            return out
+        parts = [torch.empty(nq, dtype=torch.int64) for _ in range(self.world)]
+        dist.all_gather(parts, mine.cpu(), group=self.group)
+        return torch.cat(parts).to(dev)
+
+    def exchange(self, cand, row_bases: List[int]):
+        """Returns (Candidates of my query slice with global row ids, (q_lo, q_hi)).  Collective:
+        every rank passes the result of the same queries over its own rows."""
+        import ctypes as C
+        import torch
         from . import _culsh_core, _lib
         nq = cand.n_queries
-        off_bytes = ((nq + 1) * 8 + 255) // 256 * 256
-        ip, _, op = cand.device_pointers()
         lib, hp = self.h.lib, self.h.ptr
-
-        def publish():
-            base = self.local + self.phase * self.capacity
-            _lib.check(lib.culsh_device_copy(hp, C.c_void_p(base), C.c_void_p(op), (nq + 1) * 8))
-            if cand.n_total_candidates:
-                _lib.check(lib.culsh_device_copy(hp, C.c_void_p(base + off_bytes), C.c_void_p(ip),
-                                                 4 * cand.n_total_candidates))
-
-        mine = off_bytes + 4 * cand.n_total_candidates
-        if mine <= self.capacity:
-            publish()
-        need = self._sync_max(mine)   # barrier: if nobody has to grow, every rank's half is complete
-        if need > self.capacity:      # same decision on every rank
-            self._grow(need)
-            publish()
-            self._sync_max(0)
-        shift = self.phase * self.capacity
         lo, hi = shard_bounds(nq, self.world, self.rank)
-        merged = _culsh_core.merge_shard_candidates(
-            [p + shift + off_bytes for p in self.peers], [p + shift + 8 * lo for p in self.peers], row_bases,
-            hi - lo, device=self.h.device)
+        # outgrown buffers: results that pointed into them have expired two exchanges later
+        for entry in self.retired:
+            entry[0] += 1
+        expired = [(loc, peers) for age, loc, peers in self.retired if age > 2]
+        self.retired = [e for e in self.retired if e[0] <= 2]
+        self._unmap_and_free(expired)
+        # the all-gather is also the point after which the half about to be written is free:
+        # every rank has entered this exchange, so results of the exchange before last are dead
+        counts_all = self._all_counts(cand)
+        dstpos = torch.empty(max(nq, 1), dtype=torch.int64, device=counts_all.device)
+        totals = (C.c_uint64 * self.world)()
+        out = C.c_void_p()
+        torch.cuda.synchronize(counts_all.device)
+        _lib.check(lib.culsh_exchange_plan(hp, self.world, self.rank, nq, counts_all.data_ptr(),
+                                           dstpos.data_ptr(), totals, C.byref(out)))
+        merged = _culsh_core.Candidates(out, self.h)
+        need = 4 * max(int(t) for t in totals)
+        if need > self.capacity:      # the totals are the same on every rank: same decision everywhere
+            self._grow(max(need, 256))
+        shift = self.phase * self.capacity
+        recv = (C.c_void_p * self.world)(*[C.c_void_p(p + shift) for p in self.peers])
+        ip, _, op = cand.device_pointers()
+        _lib.check(lib.culsh_exchange_push(hp, self.world, nq, ip or None, op, dstpos.data_ptr(), recv,
+                                           int(row_bases[self.rank]), int(cand.n_total_candidates)))
+        self._barrier()               # every rank's stores have landed
+        merged._attach(self.local + shift, int(totals[self.rank]), keepalive=self)
         self.phase ^= 1
         return merged, (lo, hi)
 

@@ -75,7 +75,8 @@ typedef struct culsh_stats {
     float scatter_ms; /* the scatter launch of the last radix pass alone */
     float dedupe_ms;  /* the dedupe launch (chained or bitmap kernel) of the query batches alone */
     float params_ms;  /* fit: host wall time of the hash-parameter generation (0 on a cache hit) */
-    float reserved0;
+    float hash_lo_fraction; /* tensor-core projection with profiling on: share of the K-blocks whose rows had
+                               a non-zero low part, i.e. that issued three MMAs instead of two */
     uint64_t n_items, n_buckets, raw_candidates, unique_candidates;
     int32_t sort_passes, key_words, elem_bytes, hash_path; /* hash_path: 0 SIMT, 1 tcgen05 */
     int32_t launches;  /* kernels of this library launched by the call */
@@ -207,6 +208,27 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_queries,
                                  const int32_t* const* shard_indices,
                                  const uint64_t* const* shard_offsets, const int64_t* row_base,
                                  culsh_candidates** out);
+
+/* Push form of the exchange between R ranks that answered the same n_queries queries over
+ * their own row shards (no upstream counterpart).  Rank j owns the queries [j*per, (j+1)*per),
+ * per = ceil(n_queries / R), and ends up with their merged lists.
+ *   culsh_exchange_plan: from the per-query unique counts of all ranks (counts_all, device,
+ *     [R][n_queries], e.g. all-gathered) compute where this rank's list of every query starts
+ *     inside its owner's merged id array (dstpos, device, n_queries), the id count of every
+ *     slice (slice_totals, host, R) and a result object for this rank's slice that holds the
+ *     merged counts and offsets but no ids yet.
+ *   culsh_exchange_push: store this rank's lists (indices / offsets, device, local row ids),
+ *     shifted by row_base, at dstpos inside recv[owner] - device pointers, peer memory for the
+ *     other ranks (culsh_peer_open), each with room for its slice total.  Returns when the
+ *     stores have been issued and the stream is idle; the owners may read after a barrier.
+ *   culsh_candidates_attach_indices: point a result object at an id array it does not own
+ *     (the owner's receive buffer, which must outlive it). */
+int culsh_exchange_plan(culsh_handle* h, int n_ranks, int rank, int n_queries, const uint64_t* counts_all,
+                        uint64_t* dstpos, uint64_t* slice_totals, culsh_candidates** out);
+int culsh_exchange_push(culsh_handle* h, int n_ranks, int n_queries, const int32_t* indices,
+                        const uint64_t* offsets, const uint64_t* dstpos, void* const* recv, int64_t row_base,
+                        uint64_t total);
+int culsh_candidates_attach_indices(culsh_candidates* c, const int32_t* indices, uint64_t total);
 
 /* Peer-memory plumbing for the row-sharded exchange (no upstream counterpart).  A rank exports
  * a plain device allocation to the other processes of the box; peers map it and the merge

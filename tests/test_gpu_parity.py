@@ -222,6 +222,26 @@ def test_pslsh_consistency_and_auto_window(eng):
     assert m.window_size == 100 or m.window_size == 99  # python/tests/test_pslsh.py:243-255
 
 
+def test_pslsh_paired_byte_digits_sort_like_single_bytes(eng, monkeypatch):
+    """One-byte p-stable keys whose values span at most 32 levels are sorted two ranked bytes per
+    pass; the index must be the one the byte-per-pass sort builds (negative and non-negative hash
+    values, odd and even numbers of hashes, one to four key words, more than one sort tile)."""
+    culsh, _ = eng
+    rng = np.random.RandomState(41)
+    for n, d, L, k, w in [(20000, 24, 5, 8, 4), (9000, 16, 3, 3, 2), (5000, 32, 4, 16, 8), (7000, 12, 6, 5, 3)]:
+        X = rng.randn(n, d).astype(np.float32)
+        monkeypatch.delenv("CULSH_SORT_BYTE_DIGITS", raising=False)
+        a = culsh.PStableLSH(L, k, window_size=w, seed=3).fit(X)
+        monkeypatch.setenv("CULSH_SORT_BYTE_DIGITS", "1")
+        b = culsh.PStableLSH(L, k, window_size=w, seed=3).fit(X)
+        assert a.index.elem_bytes == 1
+        for g in ("get_candidate_indices", "get_bucket_signatures", "get_bucket_candidate_offsets",
+                  "get_table_bucket_offsets"):
+            assert np.array_equal(getattr(a.index, g)(), getattr(b.index, g)()), (g, n, k)
+        sig = a.index.get_bucket_signatures().view(np.int32)
+        assert sig.min() < 0 < sig.max()
+
+
 # ------------------------------------------------------------------------------------------
 # MinHash
 # ------------------------------------------------------------------------------------------
@@ -433,9 +453,9 @@ def test_errors_are_python_exceptions(eng):
         culsh.MinHashLSH(2, 2, seed=1).fit(Xs)
 
 
-def test_device_inputs_match_host_inputs(eng):
+def test_device_inputs_match_host_inputs(eng, monkeypatch):
     import torch
-    culsh, _ = eng
+    culsh, core_mod = eng
     rng = np.random.RandomState(12)
     X = rng.randn(3000, 48).astype(np.float32)
     Q = rng.randn(100, 48).astype(np.float32)
@@ -453,6 +473,27 @@ def test_device_inputs_match_host_inputs(eng):
     i2 = culsh.RPLSH(2, 16, seed=3).fit(torch.from_numpy(Xb).cuda()).index
     assert np.array_equal(i1.get_candidate_indices(), i2.get_candidate_indices())
     assert np.array_equal(i1.get_bucket_signatures(), i2.get_bucket_signatures())
+    # host CSR larger than one staging chunk (chunks of 65,536 column ids here): rows streamed in
+    # chunks, with empty rows at chunk borders and one row longer than a chunk
+    monkeypatch.setenv("CULSH_CSR_CHUNK_NNZ", "65536")
+    Xs = _random_csr(rng, 9000, 5000, 0.01).tolil()
+    Xs[4000, :] = 0
+    Xs[4001, :] = 0
+    Xs = Xs.tocsr()
+    long_row = sp.csr_matrix((np.ones(70000, np.float32), (np.zeros(70000, int), np.arange(70000))), shape=(1, 80000))
+    Xs = sp.vstack([sp.csr_matrix((Xs.data, Xs.indices, Xs.indptr), shape=(9000, 80000)), long_row,
+                    sp.csr_matrix((1, 80000), dtype=np.float32)]).tocsr()
+    Xs.sort_indices()
+    assert Xs.nnz > 4 * 65536
+    mh = culsh.MinHashLSH(6, 3, seed=8).fit(Xs)
+    xi = torch.from_numpy(Xs.indices.astype(np.int32)).cuda()
+    xp = torch.from_numpy(Xs.indptr.astype(np.int32)).cuda()
+    dev = core_mod.MinHashCore(6, 3, 8).fit(xi, xp, Xs.shape[0], Xs.shape[1])
+    for g in ("get_candidate_indices", "get_bucket_signatures", "get_bucket_candidate_offsets"):
+        assert np.array_equal(getattr(mh.index, g)(), getattr(dev, g)()), g
+    a = mh.query(Xs[:300])
+    b = core_mod.MinHashCore(6, 3, 8).query(xi[:int(Xs.indptr[300])], xp[:301], 300, dev)
+    assert np.array_equal(a.get_indices(), b.get_indices())
 
 
 # ------------------------------------------------------------------------------------------
