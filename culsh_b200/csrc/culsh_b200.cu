@@ -407,16 +407,16 @@ struct SortBuffers {
     Scratch<uint32_t> vals_tmp;
     Scratch<uint32_t> tile_hist;
     int final_buf = 0;
-    // p-stable keys of one byte per hash may be sorted two bytes per pass (10-bit digits)
-    static bool may_pair_bytes(const KeySpec& ks) {
-        return ks.family == CULSH_PSLSH && ks.elem_bytes == 1 && ks.key_words <= 4 && ks.key_bytes >= 2;
+    // p-stable keys of one byte per hash (up to eight) may be sorted in compressed form
+    static bool may_compress(const KeySpec& ks) {
+        return ks.family == CULSH_PSLSH && ks.elem_bytes == 1 && ks.key_words <= 2 && ks.key_bytes >= 2;
     }
     void alloc(const CtxPtr& c, size_t items, const KeySpec& ks, int n, int L) {
         keys[0].reserve(c, SL_KEYS0, items * ks.key_words);
         keys[1].reserve(c, SL_KEYS1, items * ks.key_words);
         vals_out.alloc(c, items);
         vals_tmp.reserve(c, SL_VALS, items);
-        tile_hist.reserve(c, SL_STATUS, radix_sort_tile_words(n, L, ks.key_words, may_pair_bytes(ks) ? 10 : 8));
+        tile_hist.reserve(c, SL_STATUS, radix_sort_tile_words(n, L, ks.key_words));
     }
     // one buffer flip per radix pass: the last pass must write the row ids into vals_out
     void set_passes(int passes) {
@@ -433,10 +433,10 @@ int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_buck
     const CtxPtr& c = ix.ctx;
     const int n = ix.n, L = ix.L, NW = ix.ks.key_words;
     HostTrace tr;
-    // digit width: two ranked key bytes per pass when the hash values span at most 32 levels
-    int DB = 8;
-    uint32_t sub = 0;
-    if (SortBuffers::may_pair_bytes(ix.ks) && !getenv("CULSH_SORT_BYTE_DIGITS")) {
+    // compressed sort (5 bits per hash) when the hash values span at most 32 levels
+    bool compressed = false;
+    KeyComp kc{0u, 0u};
+    if (SortBuffers::may_compress(ix.ks) && !getenv("CULSH_SORT_PLAIN_KEYS")) {
         static const uint32_t init[2] = {0u, 256u};
         Scratch<uint32_t> range(c, SL_MISC1, 2);
         CU_CHECK(cudaMemcpyAsync(range.p, init, sizeof(init), cudaMemcpyHostToDevice, c->stream));
@@ -447,16 +447,17 @@ int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_buck
         uint32_t r[2] = {0, 256};
         read_words(c, range.p, sizeof(r), r);
         const uint32_t n_pos = r[0] + 1, n_neg = 256 - r[1];
-        if (n_pos + n_neg <= 32) {
-            DB = 10;
-            sub = n_neg ? r[1] - n_pos : 0u;
+        if (n_pos + n_neg <= 32 && radix_sort_passes(ix.ks.key_bytes, true) < ix.ks.key_bytes) {
+            compressed = true;
+            kc.n_pos = n_pos;
+            kc.sub = n_neg ? r[1] - n_pos : 0u;
         }
     }
-    const int passes = radix_sort_passes(ix.ks.key_bytes, DB);
+    const int passes = radix_sort_passes(ix.ks.key_bytes, compressed);
     sb.set_passes(passes);
     uint32_t* kp[2] = {sb.keys[0].p, sb.keys[1].p};
     uint32_t* vp[2] = {sb.vals[0], sb.vals[1]};
-    int cur = radix_sort_tables(c, NW, kp, vp, n, L, ix.ks.key_bytes, sb.tile_hist.p, DB, sub);
+    int cur = radix_sort_tables(c, NW, kp, vp, n, L, ix.ks.key_bytes, sb.tile_hist.p, compressed, kc);
     tm.mark();
     const int tpt = (int)ceil_div(n, IB_TILE);
     const size_t n_tiles = (size_t)tpt * L;

@@ -8,11 +8,13 @@
 // look-back between tiles was measured to cost more than the extra 4 bytes per item that
 // the histogram read adds at this bandwidth.
 //
-// Digits are 8 bits (one key byte per pass) or, for p-stable keys of one byte per hash whose
-// values span at most 32 levels, 10 bits: two key bytes per pass, each byte replaced by its rank
-// among the values in use (5 bits), which halves the number of passes.  The rank keeps the
-// unsigned order of the byte - non-negative values first, then the negative ones (two's
-// complement bytes 128..255) - so the sorted order is the same as with one byte per pass.
+// P-stable keys of one byte per hash (at most eight hashes) whose values span at most 32 levels
+// are sorted in COMPRESSED form: the first pass replaces every key byte by its 5-bit rank among
+// the values in use and packs the ranks (hash 0 most significant), the passes in between see a
+// key of 5 bits per hash - 5 passes instead of 8 for eight hashes -, and the last pass writes the
+// original bytes back.  The rank keeps the unsigned order of the byte (non-negative values
+// first, then the negative ones, two's complement bytes 128..255), so the sorted order is the
+// one a byte-per-pass sort of the original keys gives.
 #pragma once
 
 #include "common.cuh"
@@ -25,15 +27,14 @@ constexpr int RS_THREADS = 256;
 #endif
 constexpr int RS_WARPS = RS_THREADS / 32;
 
-template <int NW, int DB = 8>
+template <int NW>
 struct SortCfg {
     // items per thread: fewer for wide keys so that the tile's keys stay in registers at an
     // occupancy of 2-3 CTAs per SM
     static constexpr int IPT = NW == 1 ? 16 : (NW == 2 ? 12 : (NW == 4 ? 8 : (NW == 8 ? 4 : 2)));
     static constexpr int TILE = RS_THREADS * IPT;
-    static constexpr int NBINS = 1 << DB;
     static constexpr size_t SMEM =
-        sizeof(uint32_t) * ((size_t)TILE * NW + TILE + RS_WARPS * NBINS + NBINS + NBINS + 32);
+        sizeof(uint32_t) * ((size_t)TILE * NW + TILE + RS_WARPS * 256 + 256 + 256 + 32);
 };
 
 inline int sort_tile_items(int NW) {
@@ -46,24 +47,15 @@ inline int sort_tile_items(int NW) {
     }
 }
 
-// Digit p of a key (p = 0 least significant).  DB = 8: byte p (word NW-1-p/4, shift 8*(p%4)).
-// DB = 10: bytes 2p and 2p+1 (always in one word), each mapped to its 5-bit rank: a byte below 128
-// keeps its value, a byte from 128 up (a negative hash value) has `sub` taken off, where
-// sub = 256 + smallest negative value - (largest non-negative value + 1).
-template <int NW, int DB = 8>
-__device__ __forceinline__ uint32_t key_digit(const uint32_t* key, int p, uint32_t sub = 0u) {
-    const int b = DB == 8 ? p : 2 * p;
-    const int sel = NW - 1 - (b >> 2);
+// Byte p of a key (p = 0 least significant): word NW-1-p/4, shift 8*(p%4).
+template <int NW>
+__device__ __forceinline__ uint32_t key_digit(const uint32_t* key, int p) {
+    const int sel = NW - 1 - (p >> 2);
     uint32_t word = key[0];
 #pragma unroll
     for (int w = 1; w < NW; ++w)  // select chain keeps the key in registers
         if (w == sel) word = key[w];
-    if (DB == 8) return (word >> (8 * (b & 3))) & 0xFFu;
-    const uint32_t v = (word >> (8 * (b & 3))) & 0xFFFFu;
-    uint32_t lo = v & 0xFFu, hi = v >> 8;
-    lo -= (lo >> 7) * sub;
-    hi -= (hi >> 7) * sub;
-    return ((hi << 5) | lo) & 0x3FFu;
+    return (word >> (8 * (p & 3))) & 0xFFu;
 }
 
 template <int NW>
@@ -97,42 +89,84 @@ __device__ __forceinline__ void store_key(uint32_t* __restrict__ dst, const uint
 }
 
 // ---------------------------------------------------------------------------------------
+// Compressed form of one-byte-per-hash keys (NW = 1 or 2).  rank(u) = u for a byte below 128
+// (n_pos such values in use: 0 .. n_pos-1), u - sub for a byte from 128 up, with
+// sub = smallest negative byte - n_pos; every rank is below 32.
+// ---------------------------------------------------------------------------------------
+struct KeyComp {
+    uint32_t sub;    // see above
+    uint32_t n_pos;  // ranks below n_pos are non-negative values
+};
+
+__device__ __forceinline__ uint32_t comp_word(uint32_t w, uint32_t sub) {  // 4 bytes -> 20 bits
+    const uint32_t neg = (w >> 7) & 0x01010101u;
+    uint32_t c = w - neg * sub;                                   // four ranks, one per byte
+    c = (c & 0x001F001Fu) | ((c & 0x1F001F00u) >> 3);             // two 10-bit fields
+    return (c & 0x3FFu) | ((c >> 6) & 0xFFC00u);
+}
+__device__ __forceinline__ uint32_t decomp_word(uint32_t c20, KeyComp kc) {  // 20 bits -> 4 bytes
+    uint32_t c = (c20 & 0x3FFu) | ((c20 & 0xFFC00u) << 6);
+    c = (c & 0x001F001Fu) | ((c << 3) & 0x1F001F00u);
+    uint32_t w = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const uint32_t r = (c >> (8 * b)) & 0xFFu;
+        w |= (r + (r >= kc.n_pos ? kc.sub : 0u)) << (8 * b);
+    }
+    return w;
+}
+template <int NW>
+__device__ __forceinline__ void comp_key(uint32_t* k, uint32_t sub) {
+    if (NW == 1) {
+        k[0] = comp_word(k[0], sub);
+    } else {
+        const uint64_t v = ((uint64_t)comp_word(k[0], sub) << 20) | comp_word(k[1], sub);
+        k[0] = (uint32_t)(v >> 32);
+        k[1] = (uint32_t)v;
+    }
+}
+template <int NW>
+__device__ __forceinline__ void decomp_key(uint32_t* k, KeyComp kc) {
+    if (NW == 1) {
+        k[0] = decomp_word(k[0], kc);
+    } else {
+        const uint64_t v = ((uint64_t)k[0] << 32) | k[1];
+        k[0] = decomp_word((uint32_t)(v >> 20) & 0xFFFFFu, kc);
+        k[1] = decomp_word((uint32_t)v & 0xFFFFFu, kc);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // Pass step 1: digit histogram of every tile (a tile is TILE consecutive items of one
 // table).  tile_hist layout: [tile][256].
 // ---------------------------------------------------------------------------------------
-template <int NW, int DB>
+template <int NW, bool COMP0>
 __global__ void __launch_bounds__(RS_THREADS)
 radix_tile_hist_kernel(const uint32_t* __restrict__ keys, int n, int tiles_per_table, int p, uint32_t sub,
                        uint32_t* __restrict__ tile_hist) {
-    using Cfg = SortCfg<NW, DB>;
-    constexpr int NBINS = Cfg::NBINS;
-    __shared__ uint32_t s_hist[NBINS];
+    using Cfg = SortCfg<NW>;
+    __shared__ uint32_t s_hist[256];
     const int tile = blockIdx.x;
     const int t = tile / tiles_per_table;
     const int lt = tile - t * tiles_per_table;
     const int item0 = lt * Cfg::TILE;
     const int count = min(Cfg::TILE, n - item0);
-    const int b = DB == 8 ? p : 2 * p;
-    const uint32_t* base = keys + ((size_t)t * n + item0) * NW + (NW - 1 - (b >> 2));
-    const int shift = 8 * (b & 3);
-    for (int i = threadIdx.x; i < NBINS; i += RS_THREADS) s_hist[i] = 0;
+    const uint32_t* base = keys + ((size_t)t * n + item0) * NW + (NW - 1 - (p >> 2));
+    const int shift = 8 * (p & 3);
+    s_hist[threadIdx.x] = 0;
     __syncthreads();
+    if (COMP0) {  // p == 0 of a compressed sort: the digit is the low byte of the compressed key
+        const uint32_t* last = keys + ((size_t)t * n + item0) * NW + (NW - 1);
 #pragma unroll 4
-    for (int i = threadIdx.x; i < count; i += RS_THREADS) {
-        const uint32_t w = base[(size_t)i * NW] >> shift;
-        uint32_t d;
-        if (DB == 8) {
-            d = w & 0xFFu;
-        } else {
-            uint32_t lo = w & 0xFFu, hi = (w >> 8) & 0xFFu;
-            lo -= (lo >> 7) * sub;
-            hi -= (hi >> 7) * sub;
-            d = ((hi << 5) | lo) & 0x3FFu;
-        }
-        atomicAdd(&s_hist[d], 1u);
+        for (int i = threadIdx.x; i < count; i += RS_THREADS)
+            atomicAdd(&s_hist[comp_word(last[(size_t)i * NW], sub) & 0xFFu], 1u);
+    } else {
+#pragma unroll 4
+        for (int i = threadIdx.x; i < count; i += RS_THREADS)
+            atomicAdd(&s_hist[(base[(size_t)i * NW] >> shift) & 0xFFu], 1u);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < NBINS; i += RS_THREADS) tile_hist[(size_t)tile * NBINS + i] = s_hist[i];
+    tile_hist[(size_t)tile * 256 + threadIdx.x] = s_hist[threadIdx.x];
 }
 
 // ---------------------------------------------------------------------------------------
@@ -142,27 +176,26 @@ radix_tile_hist_kernel(const uint32_t* __restrict__ keys, int n, int tiles_per_t
 // 1024 threads = 4 tile segments x 256 digits.
 // ---------------------------------------------------------------------------------------
 constexpr int RS_SCAN_THREADS = 1024;
+constexpr int RS_SCAN_SEGS = RS_SCAN_THREADS / 256;
 
-template <int NBINS>
 __global__ void __launch_bounds__(RS_SCAN_THREADS)
 radix_tile_scan_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table) {
-    constexpr int SEGS = RS_SCAN_THREADS / NBINS;  // 4 tile segments x 256 digits, or 1 x 1024
-    __shared__ uint32_t s_seg[SEGS][NBINS];
-    __shared__ uint32_t s_base[NBINS];
-    __shared__ uint32_t s_warp[NBINS / 32];
-    const int d = threadIdx.x & (NBINS - 1), seg = threadIdx.x / NBINS;
-    uint32_t* h = tile_hist + (size_t)blockIdx.x * tiles_per_table * NBINS + d;
-    const int per_seg = (tiles_per_table + SEGS - 1) / SEGS;
+    __shared__ uint32_t s_seg[RS_SCAN_SEGS][256];
+    __shared__ uint32_t s_base[256];
+    __shared__ uint32_t s_warp[8];
+    const int d = threadIdx.x & 255, seg = threadIdx.x >> 8;
+    uint32_t* h = tile_hist + (size_t)blockIdx.x * tiles_per_table * 256 + d;
+    const int per_seg = (tiles_per_table + RS_SCAN_SEGS - 1) / RS_SCAN_SEGS;
     const int i0 = seg * per_seg, i1 = min(tiles_per_table, i0 + per_seg);
     uint32_t sum = 0;
 #pragma unroll 8
-    for (int i = i0; i < i1; ++i) sum += h[(size_t)i * NBINS];
+    for (int i = i0; i < i1; ++i) sum += h[(size_t)i * 256];
     s_seg[seg][d] = sum;
     __syncthreads();
-    if (seg == 0) {  // exclusive scan of the digit totals over the digits
+    if (seg == 0) {  // exclusive scan of the digit totals over the 256 digits
         uint32_t tot = 0;
 #pragma unroll
-        for (int g = 0; g < SEGS; ++g) tot += s_seg[g][d];
+        for (int g = 0; g < RS_SCAN_SEGS; ++g) tot += s_seg[g][d];
         const int lane = d & 31, w = d >> 5;
         uint32_t inc = tot;
 #pragma unroll
@@ -179,8 +212,8 @@ radix_tile_scan_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table) {
     for (int g = 0; g < seg; ++g) run += s_seg[g][d];
 #pragma unroll 8
     for (int i = i0; i < i1; ++i) {
-        uint32_t x = h[(size_t)i * NBINS];
-        h[(size_t)i * NBINS] = run;
+        uint32_t x = h[(size_t)i * 256];
+        h[(size_t)i * 256] = run;
         run += x;
     }
 }
@@ -193,48 +226,45 @@ radix_tile_scan_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table) {
 constexpr int RS_CHUNK_TILES = 256;
 constexpr int RS_CHUNK_MIN_TILES = 512;  // tables with fewer tiles keep the single-launch scan
 
-template <int NBINS>
 __global__ void __launch_bounds__(RS_SCAN_THREADS)
 radix_tile_scan_chunk_kernel(uint32_t* __restrict__ tile_hist, int tiles_per_table, int n_chunks,
-                             uint32_t* __restrict__ chunk_tot /* [table][chunk][NBINS] */) {
-    constexpr int SEGS = RS_SCAN_THREADS / NBINS;
-    __shared__ uint32_t s_seg[SEGS][NBINS];
-    const int d = threadIdx.x & (NBINS - 1), seg = threadIdx.x / NBINS;
+                             uint32_t* __restrict__ chunk_tot /* [table][chunk][256] */) {
+    __shared__ uint32_t s_seg[RS_SCAN_SEGS][256];
+    const int d = threadIdx.x & 255, seg = threadIdx.x >> 8;
     const int table = blockIdx.x / n_chunks, chunk = blockIdx.x - table * n_chunks;
     const int t_begin = chunk * RS_CHUNK_TILES, t_end = min(tiles_per_table, t_begin + RS_CHUNK_TILES);
-    uint32_t* h = tile_hist + (size_t)table * tiles_per_table * NBINS + d;
-    const int per_seg = (t_end - t_begin + SEGS - 1) / SEGS;
+    uint32_t* h = tile_hist + (size_t)table * tiles_per_table * 256 + d;
+    const int per_seg = (t_end - t_begin + RS_SCAN_SEGS - 1) / RS_SCAN_SEGS;
     const int i0 = t_begin + seg * per_seg, i1 = min(t_end, i0 + per_seg);
     uint32_t sum = 0;
 #pragma unroll 8
-    for (int i = i0; i < i1; ++i) sum += h[(size_t)i * NBINS];
+    for (int i = i0; i < i1; ++i) sum += h[(size_t)i * 256];
     s_seg[seg][d] = sum;
     __syncthreads();
     uint32_t run = 0, tot = 0;
 #pragma unroll
-    for (int g = 0; g < SEGS; ++g) {
+    for (int g = 0; g < RS_SCAN_SEGS; ++g) {
         const uint32_t x = s_seg[g][d];
         if (g < seg) run += x;
         tot += x;
     }
-    if (seg == 0) chunk_tot[(size_t)blockIdx.x * NBINS + d] = tot;
+    if (seg == 0) chunk_tot[(size_t)blockIdx.x * 256 + d] = tot;
 #pragma unroll 8
     for (int i = i0; i < i1; ++i) {
-        const uint32_t x = h[(size_t)i * NBINS];
-        h[(size_t)i * NBINS] = run;
+        const uint32_t x = h[(size_t)i * 256];
+        h[(size_t)i * 256] = run;
         run += x;
     }
 }
 
-// one block of NBINS threads per table: chunk_tot -> chunk bases, in place
-template <int NBINS>
-__global__ void __launch_bounds__(NBINS)
+// one block of 256 threads per table: chunk_tot -> chunk bases, in place
+__global__ void __launch_bounds__(256)
 radix_chunk_base_kernel(uint32_t* __restrict__ chunk_tot, int n_chunks) {
-    __shared__ uint32_t s_warp[NBINS / 32];
+    __shared__ uint32_t s_warp[8];
     const int d = threadIdx.x, lane = d & 31, w = d >> 5;
-    uint32_t* ct = chunk_tot + (size_t)blockIdx.x * n_chunks * NBINS + d;
+    uint32_t* ct = chunk_tot + (size_t)blockIdx.x * n_chunks * 256 + d;
     uint32_t tot = 0;
-    for (int c = 0; c < n_chunks; ++c) tot += ct[(size_t)c * NBINS];
+    for (int c = 0; c < n_chunks; ++c) tot += ct[(size_t)c * 256];
     uint32_t inc = tot;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -246,33 +276,33 @@ radix_chunk_base_kernel(uint32_t* __restrict__ chunk_tot, int n_chunks) {
     uint32_t run = inc - tot;
     for (int i = 0; i < w; ++i) run += s_warp[i];
     for (int c = 0; c < n_chunks; ++c) {
-        const uint32_t x = ct[(size_t)c * NBINS];
-        ct[(size_t)c * NBINS] = run;
+        const uint32_t x = ct[(size_t)c * 256];
+        ct[(size_t)c * 256] = run;
         run += x;
     }
 }
 
 // ---------------------------------------------------------------------------------------
-// Pass step 3: stable scatter of one tile on digit `p`.
+// Pass step 3: stable scatter of one tile on byte `p`.
 // ---------------------------------------------------------------------------------------
-template <int NW, bool FIRST, int DB>
-__global__ void __launch_bounds__(RS_THREADS, (DB == 8 ? (NW == 1 ? 4 : RS_MIN_BLOCKS) : 2))
+// COMP: 0 plain keys; 1 first pass of a compressed sort (keys are compressed as they are
+// loaded); 2 its last pass (the original bytes are written back).
+template <int NW, bool FIRST, int COMP>
+__global__ void __launch_bounds__(RS_THREADS, (NW == 1 ? 4 : RS_MIN_BLOCKS))
 radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int n,
-                     int tiles_per_table, int p, uint32_t sub, const uint32_t* __restrict__ tile_off,
+                     int tiles_per_table, int p, KeyComp kc, const uint32_t* __restrict__ tile_off,
                      const uint32_t* __restrict__ chunk_base /* or null */, int n_chunks) {
-    using Cfg = SortCfg<NW, DB>;
+    using Cfg = SortCfg<NW>;
     constexpr int IPT = Cfg::IPT;
     constexpr int TILE = Cfg::TILE;
-    constexpr int NBINS = Cfg::NBINS;
-    constexpr int BPT = NBINS / RS_THREADS;  // bins per thread: 1 or 4, contiguous
     extern __shared__ __align__(16) uint32_t smem[];
     uint32_t* s_keys = smem;                       // [TILE][NW]
     uint32_t* s_vals = s_keys + (size_t)TILE * NW; // [TILE]
-    uint32_t* s_whist = s_vals + TILE;             // [RS_WARPS][NBINS]
-    uint32_t* s_gdst = s_whist + RS_WARPS * NBINS; // [NBINS] global dst of local position 0 of a bin
-    uint32_t* s_binstart = s_gdst + NBINS;         // [NBINS]
-    uint32_t* s_misc = s_binstart + NBINS;         // [32]
+    uint32_t* s_whist = s_vals + TILE;             // [RS_WARPS][256]
+    uint32_t* s_gdst = s_whist + RS_WARPS * 256;   // [256] global dst of local position 0 of a bin
+    uint32_t* s_binstart = s_gdst + 256;           // [256]
+    uint32_t* s_misc = s_binstart + 256;           // [32]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = blockIdx.x;
@@ -283,14 +313,9 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     const size_t base = (size_t)t * n + item0;
     // needed late: fetched early, and summed only where used (an add here would stall the warp on
     // both loads before the key loads are issued)
-    uint32_t my_off[BPT], my_base[BPT];
-#pragma unroll
-    for (int j = 0; j < BPT; ++j) {
-        const int bin = tid * BPT + j;
-        my_off[j] = tile_off[(size_t)tile * NBINS + bin];
-        my_base[j] = chunk_base ? chunk_base[((size_t)t * n_chunks + lt / RS_CHUNK_TILES) * NBINS + bin] : 0u;
-    }
-    for (int i = tid; i < RS_WARPS * NBINS; i += RS_THREADS) s_whist[i] = 0;
+    const uint32_t my_off = tile_off[(size_t)tile * 256 + tid];
+    const uint32_t my_base = chunk_base ? chunk_base[((size_t)t * n_chunks + lt / RS_CHUNK_TILES) * 256 + tid] : 0u;
+    for (int i = tid; i < RS_WARPS * 256; i += RS_THREADS) s_whist[i] = 0;
 
     // ---- load (all loads in flight together) ------------------------------------------
     uint32_t key[IPT][NW];
@@ -302,6 +327,7 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
         const int li = warp * (32 * IPT) + i * 32 + lane;
         if (li < count) {
             load_key<NW>(keys_in + (base + li) * NW, key[i]);
+            if (COMP == 1) comp_key<NW>(key[i], kc.sub);
             val[i] = FIRST ? (uint32_t)(item0 + li) : vals_in[base + li];
         } else {
 #pragma unroll
@@ -316,12 +342,12 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     for (int i = 0; i < IPT; ++i) {
         const int li = warp * (32 * IPT) + i * 32 + lane;
         const bool valid = li < count;
-        const uint32_t d = valid ? key_digit<NW, DB>(key[i], p, sub) : 0xFFFFu;
+        const uint32_t d = valid ? key_digit<NW>(key[i], p) : 0x100u;
         // lanes with the same digit.  For one-word keys the kernel is bound by the latency of the
         // shared-memory / match pipeline, and nine ballots (digit bits + validity) are cheaper
         // than match.any; wider keys are bandwidth-bound and take the shorter instruction.
         uint32_t peers;
-        if constexpr (NW == 1 && DB == 8) {
+        if constexpr (NW == 1) {
             peers = count == TILE ? 0xFFFFFFFFu : __ballot_sync(0xFFFFFFFFu, valid);
             if (!valid) peers = ~peers;
 #pragma unroll
@@ -336,7 +362,7 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
         const int leader = __ffs(peers) - 1;
         const uint32_t below = __popc(peers & ((1u << lane) - 1));
         uint32_t old = 0;
-        if (valid && lane == leader) old = atomicAdd(&s_whist[warp * NBINS + d], (uint32_t)__popc(peers));
+        if (valid && lane == leader) old = atomicAdd(&s_whist[warp * 256 + d], (uint32_t)__popc(peers));
         old = __shfl_sync(0xFFFFFFFFu, old, leader);
         rank[i] = (uint16_t)(old + below);
         dig[i] = (uint16_t)d;
@@ -344,21 +370,17 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     __syncthreads();
 
     // ---- per bin: exclusive offsets of the warps, tile count, start inside the tile ----
-    uint32_t cnt[BPT], tsum = 0;
-#pragma unroll
-    for (int j = 0; j < BPT; ++j) {
-        const int b = tid * BPT + j;
-        uint32_t c = 0;
+    uint32_t cnt = 0;
+    {
+        const int b = tid;
 #pragma unroll
         for (int w = 0; w < RS_WARPS; ++w) {
-            uint32_t x = s_whist[w * NBINS + b];
-            s_whist[w * NBINS + b] = c;
-            c += x;
+            uint32_t x = s_whist[w * 256 + b];
+            s_whist[w * 256 + b] = cnt;
+            cnt += x;
         }
-        cnt[j] = c;
-        tsum += c;
     }
-    uint32_t inc = tsum;
+    uint32_t inc = cnt;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         uint32_t x = __shfl_up_sync(0xFFFFFFFFu, inc, o);
@@ -368,22 +390,17 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     __syncthreads();
     uint32_t wbase = 0;
     for (int i = 0; i < warp; ++i) wbase += s_misc[1 + i];
-    uint32_t binstart = wbase + inc - tsum;
-#pragma unroll
-    for (int j = 0; j < BPT; ++j) {
-        const int b = tid * BPT + j;
-        s_binstart[b] = binstart;
-        s_gdst[b] = (uint32_t)((size_t)t * n) + my_off[j] + my_base[j] - binstart;
-        binstart += cnt[j];
-    }
+    const uint32_t binstart = wbase + inc - cnt;
+    s_binstart[tid] = binstart;
+    s_gdst[tid] = (uint32_t)((size_t)t * n) + my_off + my_base - binstart;
     __syncthreads();
 
     // ---- reorder inside shared memory ------------------------------------------------
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
         const uint32_t d = dig[i];
-        if (d < (uint32_t)NBINS) {
-            const uint32_t pos = s_binstart[d] + s_whist[warp * NBINS + d] + rank[i];
+        if (d < 256u) {
+            const uint32_t pos = s_binstart[d] + s_whist[warp * 256 + d] + rank[i];
 #pragma unroll
             for (int w = 0; w < NW; ++w) s_keys[(size_t)pos * NW + w] = key[i][w];
             s_vals[pos] = val[i];
@@ -396,8 +413,9 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
         uint32_t kk[NW];
 #pragma unroll
         for (int w = 0; w < NW; ++w) kk[w] = s_keys[(size_t)pos * NW + w];
-        const uint32_t d = key_digit<NW, DB>(kk, p, sub);
+        const uint32_t d = key_digit<NW>(kk, p);
         const uint32_t g = s_gdst[d] + (uint32_t)pos;
+        if (COMP == 2) decomp_key<NW>(kk, kc);
         store_key<NW>(keys_out + (size_t)g * NW, kk);
         vals_out[g] = s_vals[pos];
     }
@@ -432,51 +450,55 @@ key_byte_range_kernel(const uint32_t* __restrict__ keys, size_t n_words, uint32_
 
 // ---------------------------------------------------------------------------------------
 // Host driver.  keys[0]/vals[0] hold the input (vals[0] is never read: the first pass
-// takes the row id from the position); after `passes` passes the result is in buffer
-// passes & 1.  tile_hist must hold radix_sort_tile_words(n, L, NW, DB) words.
+// takes the row id from the position); after radix_sort_passes() passes the result is in
+// buffer passes & 1.  tile_hist must hold radix_sort_tile_words(n, L, NW) words.
+// `compressed` (NW <= 2 only): sort the 5-bit-per-byte form of the keys, see the top of the file.
 // ---------------------------------------------------------------------------------------
-inline int radix_sort_passes(int KB, int DB) { return DB == 8 ? KB : (KB + 1) / 2; }
+inline int radix_sort_passes(int KB, bool compressed) { return compressed ? (5 * KB + 7) / 8 : KB; }
 
-template <int NW, int DB>
+template <int NW>
 inline int radix_sort_tables_nw(const CtxPtr& c, uint32_t* keys[2], uint32_t* vals[2], int n, int L,
-                                int KB, uint32_t sub, uint32_t* tile_hist) {
-    using Cfg = SortCfg<NW, DB>;
-    constexpr int NBINS = Cfg::NBINS;
+                                int KB, uint32_t* tile_hist, bool compressed, KeyComp kc) {
+    using Cfg = SortCfg<NW>;
     cudaStream_t s = c->stream;
     const int tiles_per_table = (int)ceil_div(n, Cfg::TILE);
     const size_t total_tiles = (size_t)tiles_per_table * L;
-    auto k_first = radix_scatter_kernel<NW, true, DB>;
-    auto k_next = radix_scatter_kernel<NW, false, DB>;
-    CU_CHECK(cudaFuncSetAttribute(k_first, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
-    CU_CHECK(cudaFuncSetAttribute(k_next, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
+    constexpr bool CAN_COMP = NW <= 2;
+    auto k_first = radix_scatter_kernel<NW, true, 0>;
+    auto k_next = radix_scatter_kernel<NW, false, 0>;
+    auto k_first_c = radix_scatter_kernel<NW, true, CAN_COMP ? 1 : 0>;
+    auto k_last_c = radix_scatter_kernel<NW, false, CAN_COMP ? 2 : 0>;
+    for (auto k : {k_first, k_next, k_first_c, k_last_c})
+        CU_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
+    if (compressed && !CAN_COMP) fail(CULSH_ERR_INTERNAL, "compressed sort needs a key of at most two words");
     const bool chunked = tiles_per_table >= RS_CHUNK_MIN_TILES;
     const int n_chunks = chunked ? (int)ceil_div(tiles_per_table, RS_CHUNK_TILES) : 1;
-    uint32_t* chunk_tot = tile_hist + total_tiles * NBINS;  // [L][n_chunks][NBINS], behind the tile histograms
-    const int passes = radix_sort_passes(KB, DB);
+    uint32_t* chunk_tot = tile_hist + total_tiles * 256;  // [L][n_chunks][256], behind the tile histograms
+    const int passes = radix_sort_passes(KB, compressed);
     int cur = 0;
     for (int p = 0; p < passes; ++p) {
-        radix_tile_hist_kernel<NW, DB><<<(unsigned)total_tiles, RS_THREADS, 0, s>>>(keys[cur], n, tiles_per_table,
-                                                                                  p, sub, tile_hist);
+        if (compressed && p == 0)
+            radix_tile_hist_kernel<NW, CAN_COMP><<<(unsigned)total_tiles, RS_THREADS, 0, s>>>(
+                keys[cur], n, tiles_per_table, p, kc.sub, tile_hist);
+        else
+            radix_tile_hist_kernel<NW, false><<<(unsigned)total_tiles, RS_THREADS, 0, s>>>(
+                keys[cur], n, tiles_per_table, p, 0u, tile_hist);
         KERNEL_CHECK();
         if (chunked) {
-            radix_tile_scan_chunk_kernel<NBINS><<<(unsigned)(L * n_chunks), RS_SCAN_THREADS, 0, s>>>(
+            radix_tile_scan_chunk_kernel<<<(unsigned)(L * n_chunks), RS_SCAN_THREADS, 0, s>>>(
                 tile_hist, tiles_per_table, n_chunks, chunk_tot);
             KERNEL_CHECK();
-            radix_chunk_base_kernel<NBINS><<<(unsigned)L, NBINS, 0, s>>>(chunk_tot, n_chunks);
+            radix_chunk_base_kernel<<<(unsigned)L, 256, 0, s>>>(chunk_tot, n_chunks);
         } else {
-            radix_tile_scan_kernel<NBINS><<<(unsigned)L, RS_SCAN_THREADS, 0, s>>>(tile_hist, tiles_per_table);
+            radix_tile_scan_kernel<<<(unsigned)L, RS_SCAN_THREADS, 0, s>>>(tile_hist, tiles_per_table);
         }
         KERNEL_CHECK();
         const bool last = p == passes - 1;
         if (last && c->profiling) cudaEventRecord(c->ev_pass[0], s);
-        if (p == 0)
-            k_first<<<(unsigned)total_tiles, RS_THREADS, Cfg::SMEM, s>>>(
-                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, sub, tile_hist,
-                chunked ? chunk_tot : nullptr, n_chunks);
-        else
-            k_next<<<(unsigned)total_tiles, RS_THREADS, Cfg::SMEM, s>>>(
-                keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, sub, tile_hist,
-                chunked ? chunk_tot : nullptr, n_chunks);
+        auto kern = p == 0 ? (compressed ? k_first_c : k_first) : (compressed && last ? k_last_c : k_next);
+        kern<<<(unsigned)total_tiles, RS_THREADS, Cfg::SMEM, s>>>(
+            keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, kc, tile_hist,
+            chunked ? chunk_tot : nullptr, n_chunks);
         KERNEL_CHECK();
         if (last && c->profiling) cudaEventRecord(c->ev_pass[1], s);
         cur ^= 1;
@@ -484,28 +506,20 @@ inline int radix_sort_tables_nw(const CtxPtr& c, uint32_t* keys[2], uint32_t* va
     return cur;
 }
 
-inline size_t radix_sort_tile_words(int n, int L, int NW, int DB = 8) {
+inline size_t radix_sort_tile_words(int n, int L, int NW) {
     const size_t tiles = ceil_div(n, sort_tile_items(NW));
-    return (tiles + ceil_div(tiles, (size_t)RS_CHUNK_TILES)) * (size_t)L * ((size_t)1 << DB);  // tile histograms + chunk totals
+    return (tiles + ceil_div(tiles, (size_t)RS_CHUNK_TILES)) * (size_t)L * 256;  // tile histograms + chunk totals
 }
 
-// DB = 10 (two ranked bytes per pass) is available for keys of up to four words.
 inline int radix_sort_tables(const CtxPtr& c, int NW, uint32_t* keys[2], uint32_t* vals[2], int n,
-                             int L, int KB, uint32_t* tile_hist, int DB = 8, uint32_t sub = 0u) {
-    if (DB == 10) {
-        switch (NW) {
-            case 1: return radix_sort_tables_nw<1, 10>(c, keys, vals, n, L, KB, sub, tile_hist);
-            case 2: return radix_sort_tables_nw<2, 10>(c, keys, vals, n, L, KB, sub, tile_hist);
-            case 4: return radix_sort_tables_nw<4, 10>(c, keys, vals, n, L, KB, sub, tile_hist);
-        }
-        fail(CULSH_ERR_INTERNAL, "10-bit digits need a key of at most four words");
-    }
+                             int L, int KB, uint32_t* tile_hist, bool compressed = false,
+                             KeyComp kc = KeyComp{0u, 0u}) {
     switch (NW) {
-        case 1: return radix_sort_tables_nw<1, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
-        case 2: return radix_sort_tables_nw<2, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
-        case 4: return radix_sort_tables_nw<4, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
-        case 8: return radix_sort_tables_nw<8, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
-        case 16: return radix_sort_tables_nw<16, 8>(c, keys, vals, n, L, KB, 0u, tile_hist);
+        case 1: return radix_sort_tables_nw<1>(c, keys, vals, n, L, KB, tile_hist, compressed, kc);
+        case 2: return radix_sort_tables_nw<2>(c, keys, vals, n, L, KB, tile_hist, compressed, kc);
+        case 4: return radix_sort_tables_nw<4>(c, keys, vals, n, L, KB, tile_hist, compressed, kc);
+        case 8: return radix_sort_tables_nw<8>(c, keys, vals, n, L, KB, tile_hist, compressed, kc);
+        case 16: return radix_sort_tables_nw<16>(c, keys, vals, n, L, KB, tile_hist, compressed, kc);
     }
     fail(CULSH_ERR_UNSUPPORTED, "unsupported key width: %d words", NW);
 }

@@ -222,17 +222,18 @@ def test_pslsh_consistency_and_auto_window(eng):
     assert m.window_size == 100 or m.window_size == 99  # python/tests/test_pslsh.py:243-255
 
 
-def test_pslsh_paired_byte_digits_sort_like_single_bytes(eng, monkeypatch):
-    """One-byte p-stable keys whose values span at most 32 levels are sorted two ranked bytes per
-    pass; the index must be the one the byte-per-pass sort builds (negative and non-negative hash
-    values, odd and even numbers of hashes, one to four key words, more than one sort tile)."""
+def test_pslsh_compressed_sort_equals_plain_sort(eng, monkeypatch):
+    """One-byte p-stable keys (up to eight hashes) whose values span at most 32 levels are sorted in
+    compressed form (5 bits per hash); the index must be the one the sort of the plain keys builds
+    (negative and non-negative hash values, odd and even numbers of hashes, one and two key words,
+    more than one sort tile; sixteen hashes keep the plain sort)."""
     culsh, _ = eng
     rng = np.random.RandomState(41)
     for n, d, L, k, w in [(20000, 24, 5, 8, 4), (9000, 16, 3, 3, 2), (5000, 32, 4, 16, 8), (7000, 12, 6, 5, 3)]:
         X = rng.randn(n, d).astype(np.float32)
-        monkeypatch.delenv("CULSH_SORT_BYTE_DIGITS", raising=False)
+        monkeypatch.delenv("CULSH_SORT_PLAIN_KEYS", raising=False)
         a = culsh.PStableLSH(L, k, window_size=w, seed=3).fit(X)
-        monkeypatch.setenv("CULSH_SORT_BYTE_DIGITS", "1")
+        monkeypatch.setenv("CULSH_SORT_PLAIN_KEYS", "1")
         b = culsh.PStableLSH(L, k, window_size=w, seed=3).fit(X)
         assert a.index.elem_bytes == 1
         for g in ("get_candidate_indices", "get_bucket_signatures", "get_bucket_candidate_offsets",
