@@ -537,6 +537,7 @@ def run_workload(torch, args, wl, spec, world, rank, local, exchange, steps, war
             if world > 1:  # each rank pulls the lists of its slice of the queries from its peers
                 keep["local"] = cand
                 cand, keep["span"] = exchange.exchange(cand, [r * n for r in range(world)])
+                s_q = dict(s_q, **{"x_" + key: val for key, val in exchange.last_ms.items()})
         keep["cand"] = cand
         return s_fit, s_q, (read_back(cand) if host_out else 0)
 
@@ -719,6 +720,10 @@ def line_of(torch, args, wl, spec, world, m, peaks, tf32):
                 "h2d_bytes_per_step": int(m["h2d"]), "d2h_bytes_per_step": int(m["d2h"])},
         "gpu_launches": m["launches"], "clocks": m["clocks"],
     }
+    if world > 1 and "x_push" in sq:
+        line["exchange_ms"] = {key[2:]: mean(key, "query") for key in sq if key.startswith("x_")}
+        line["exchange_ms"]["note"] = ("rank 0's host wall time per step of the exchange: all-gather of the per-query "
+                                       "counts, positions, the push kernel (peer stores), closing barrier")
     if m["parity"] is not None:
         line["parity"] = m["parity"]
     if m["exchange_check"] is not None:

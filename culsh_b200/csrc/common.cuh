@@ -164,6 +164,13 @@ struct Ctx {
     culsh_stats stats{};
     int sm_count = 148;
     size_t smem_optin = 0;
+    // Large result / index blocks (>= BIG_BLOCK_MIN bytes) that were released: kept here and handed
+    // out again by size instead of going through the stream-ordered pool, where small short-lived
+    // allocations between two large ones fragment the reserve and send the next large request
+    // to the driver (milliseconds once peers have the device mapped).
+    struct BigBlock { void* p; size_t cap; };
+    std::vector<BigBlock> big_free;
+    size_t big_free_bytes = 0;
 
     ~Ctx() {
         cudaSetDevice(device);
@@ -176,6 +183,7 @@ struct Ctx {
         for (auto& e : chunk_free) if (e) cudaEventDestroy(e);
         if (copy_stream) cudaStreamSynchronize(copy_stream);
         for (auto& q : slot_ptr) if (q) cudaFree(q);
+        for (auto& b : big_free) cudaFree(b.p);
         if (pinned) cudaFreeHost(pinned);
         if (d_error) cudaFree(d_error);
         if (d_mma) cudaFree(d_mma);
@@ -185,23 +193,77 @@ struct Ctx {
 };
 using CtxPtr = std::shared_ptr<Ctx>;
 
-// Stream-ordered device buffer (cudaMallocAsync on the context's stream; the pool keeps
-// freed blocks, so steady-state calls do not reach the driver allocator).
+constexpr size_t BIG_BLOCK_MIN = (size_t)32 << 20;       // requests from this size on use the block list
+constexpr size_t BIG_BLOCK_KEEP = (size_t)16 << 30;      // at most this many released bytes are kept
+constexpr size_t BIG_BLOCK_KEEP_COUNT = 8;
+
+// Takes a released block that fits (no more than twice the request), else allocates one.
+inline void* big_block_alloc(Ctx& c, size_t bytes, size_t* cap_out) {
+    size_t best = c.big_free.size();
+    for (size_t i = 0; i < c.big_free.size(); ++i) {
+        const size_t cap = c.big_free[i].cap;
+        if (cap >= bytes && cap <= 2 * bytes && (best == c.big_free.size() || cap < c.big_free[best].cap)) best = i;
+    }
+    if (best < c.big_free.size()) {
+        Ctx::BigBlock b = c.big_free[best];
+        c.big_free.erase(c.big_free.begin() + (long)best);
+        c.big_free_bytes -= b.cap;
+        *cap_out = b.cap;
+        return b.p;
+    }
+    const size_t cap = (bytes + ((size_t)2 << 20) - 1) & ~(((size_t)2 << 20) - 1);
+    void* q = nullptr;
+    cudaError_t e = cudaMalloc(&q, cap);
+    if (e != cudaSuccess && !c.big_free.empty()) {  // give the kept blocks back and try once more
+        cudaGetLastError();
+        for (auto& b : c.big_free) cudaFree(b.p);
+        c.big_free.clear();
+        c.big_free_bytes = 0;
+        e = cudaMalloc(&q, cap);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        fail(CULSH_ERR_ALLOC, "device allocation of %zu bytes failed: %s", cap, cudaGetErrorString(e));
+    }
+    *cap_out = cap;
+    return q;
+}
+
+// The block may still be in use by work queued on the handle's stream; whoever takes it next
+// uses it on the same stream, so the order of the stream protects it.  Blocks beyond the keep
+// limits go back to the driver (oldest first; cudaFree waits for the device).
+inline void big_block_release(Ctx& c, void* p, size_t cap) {
+    c.big_free.push_back(Ctx::BigBlock{p, cap});
+    c.big_free_bytes += cap;
+    while (c.big_free.size() > BIG_BLOCK_KEEP_COUNT || c.big_free_bytes > BIG_BLOCK_KEEP) {
+        Ctx::BigBlock b = c.big_free.front();
+        c.big_free.erase(c.big_free.begin());
+        c.big_free_bytes -= b.cap;
+        cudaFree(b.p);
+    }
+}
+
+// Device buffer owned by a result or index object: small ones come from the stream-ordered
+// pool (cudaMallocAsync on the context's stream; the pool keeps freed blocks, so steady-state
+// calls do not reach the driver allocator), large ones from the handle's block list.
 template <typename T>
 struct DevBuf {
     T* p = nullptr;
     size_t n = 0;
     CtxPtr ctx;
+    size_t big_cap = 0;  // non-zero: a block of the handle's block list with this capacity
     DevBuf() = default;
     DevBuf(const CtxPtr& c, size_t count) { alloc(c, count); }
     DevBuf(const DevBuf&) = delete;
     DevBuf& operator=(const DevBuf&) = delete;
-    DevBuf(DevBuf&& o) noexcept : p(o.p), n(o.n), ctx(std::move(o.ctx)) { o.p = nullptr; o.n = 0; }
+    DevBuf(DevBuf&& o) noexcept : p(o.p), n(o.n), ctx(std::move(o.ctx)), big_cap(o.big_cap) {
+        o.p = nullptr; o.n = 0; o.big_cap = 0;
+    }
     DevBuf& operator=(DevBuf&& o) noexcept {
         if (this != &o) {
             release();
-            p = o.p; n = o.n; ctx = std::move(o.ctx);
-            o.p = nullptr; o.n = 0;
+            p = o.p; n = o.n; ctx = std::move(o.ctx); big_cap = o.big_cap;
+            o.p = nullptr; o.n = 0; o.big_cap = 0;
         }
         return *this;
     }
@@ -211,12 +273,16 @@ struct DevBuf {
         ctx = c;
         n = count;
         if (count == 0) return;
+        const size_t bytes = count * sizeof(T);
+        if (bytes >= BIG_BLOCK_MIN) {
+            p = static_cast<T*>(big_block_alloc(*c, bytes, &big_cap));
+            return;
+        }
         void* q = nullptr;
-        cudaError_t e = cudaMallocAsync(&q, count * sizeof(T), c->stream);
+        cudaError_t e = cudaMallocAsync(&q, bytes, c->stream);
         if (e != cudaSuccess) {
             cudaGetLastError();
-            fail(CULSH_ERR_ALLOC, "device allocation of %zu bytes failed: %s", count * sizeof(T),
-                 cudaGetErrorString(e));
+            fail(CULSH_ERR_ALLOC, "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
         }
         p = static_cast<T*>(q);
     }
@@ -225,11 +291,13 @@ struct DevBuf {
             int cur = -1;
             cudaGetDevice(&cur);
             if (cur != ctx->device) cudaSetDevice(ctx->device);
-            cudaFreeAsync(p, ctx->stream);
+            if (big_cap) big_block_release(*ctx, p, big_cap);
+            else cudaFreeAsync(p, ctx->stream);
             if (cur != ctx->device && cur >= 0) cudaSetDevice(cur);
         }
         p = nullptr;
         n = 0;
+        big_cap = 0;
     }
     size_t bytes() const { return n * sizeof(T); }
 };

@@ -208,9 +208,12 @@ void generate_params(culsh_index& ix) {
         }
     }
     const auto t0 = std::chrono::steady_clock::now();
+    HostTrace tr;
     generate_params_uncached(ix);
+    tr.lap("params: cuRAND calls issued");
     prepare_tc_split(ix);
     CU_CHECK(cudaStreamSynchronize(c->stream));
+    tr.lap("params: split + sync");
     c->last_params_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     if (c->param_cache_enabled) {
         if (c->param_cache.size() >= 16) c->param_cache.clear();
@@ -500,8 +503,10 @@ int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_buck
     ix.cand.p = reinterpret_cast<int32_t*>(v.p);
     ix.cand.n = v.n;
     ix.cand.ctx = v.ctx;
+    ix.cand.big_cap = v.big_cap;
     v.p = nullptr;
     v.n = 0;
+    v.big_cap = 0;
     tm.mark();
     c->stats.n_items = (uint64_t)n * L;
     c->stats.n_buckets = B;

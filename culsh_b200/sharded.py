@@ -186,6 +186,7 @@ class PeerExchange:
         self.local = None      # device address of my buffer (two halves)
         self.peers = []        # device addresses of every rank's buffer as mapped here
         self.retired = []      # [age, local, peers] of outgrown buffers that results may still use
+        self.last_ms = {}      # host wall time of the steps of the last exchange (every step ends in a sync)
 
     def _unmap_and_free(self, sets):
         """Collective, two phases: every rank unmaps its peers' buffers, the group meets at a
@@ -272,9 +273,11 @@ class PeerExchange:
         import ctypes as C
         import torch
         from . import _culsh_core, _lib
+        import time
         nq = cand.n_queries
         lib, hp = self.h.lib, self.h.ptr
         lo, hi = shard_bounds(nq, self.world, self.rank)
+        t0 = time.perf_counter()
         # outgrown buffers: results that pointed into them have expired two exchanges later
         for entry in self.retired:
             entry[0] += 1
@@ -288,18 +291,24 @@ class PeerExchange:
         totals = (C.c_uint64 * self.world)()
         out = C.c_void_p()
         torch.cuda.synchronize(counts_all.device)
+        t1 = time.perf_counter()
         _lib.check(lib.culsh_exchange_plan(hp, self.world, self.rank, nq, counts_all.data_ptr(),
                                            dstpos.data_ptr(), totals, C.byref(out)))
         merged = _culsh_core.Candidates(out, self.h)
         need = 4 * max(int(t) for t in totals)
         if need > self.capacity:      # the totals are the same on every rank: same decision everywhere
             self._grow(max(need, 256))
+        t2 = time.perf_counter()
         shift = self.phase * self.capacity
         recv = (C.c_void_p * self.world)(*[C.c_void_p(p + shift) for p in self.peers])
         ip, _, op = cand.device_pointers()
         _lib.check(lib.culsh_exchange_push(hp, self.world, nq, ip or None, op, dstpos.data_ptr(), recv,
                                            int(row_bases[self.rank]), int(cand.n_total_candidates)))
+        t3 = time.perf_counter()
         self._barrier()               # every rank's stores have landed
+        t4 = time.perf_counter()
+        self.last_ms = {"counts_all_gather": (t1 - t0) * 1e3, "plan": (t2 - t1) * 1e3, "push": (t3 - t2) * 1e3,
+                        "barrier": (t4 - t3) * 1e3, "pushed_bytes": 4 * int(cand.n_total_candidates)}
         merged._attach(self.local + shift, int(totals[self.rank]), keepalive=self)
         self.phase ^= 1
         return merged, (lo, hi)
