@@ -444,7 +444,7 @@ int build_index(culsh_index& ix, SortBuffers& sb, Scratch<int32_t>* item_to_buck
         Scratch<uint32_t> range(c, SL_MISC1, 2);
         CU_CHECK(cudaMemcpyAsync(range.p, init, sizeof(init), cudaMemcpyHostToDevice, c->stream));
         const size_t n_words = (size_t)n * L * NW;
-        key_byte_range_kernel<<<(unsigned)std::min<size_t>(ceil_div(n_words, 256), (size_t)c->sm_count * 16), 256, 0,
+        key_byte_range_kernel<<<(unsigned)std::min<size_t>(ceil_div(n_words, 1024), (size_t)c->sm_count * 16), 256, 0,
                                 c->stream>>>(sb.keys[0].p, n_words, range.p);
         KERNEL_CHECK();
         uint32_t r[2] = {0, 256};

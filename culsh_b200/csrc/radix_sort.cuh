@@ -288,7 +288,7 @@ radix_chunk_base_kernel(uint32_t* __restrict__ chunk_tot, int n_chunks) {
 // COMP: 0 plain keys; 1 first pass of a compressed sort (keys are compressed as they are
 // loaded); 2 its last pass (the original bytes are written back).
 template <int NW, bool FIRST, int COMP>
-__global__ void __launch_bounds__(RS_THREADS, (NW == 1 ? 4 : RS_MIN_BLOCKS))
+__global__ void __launch_bounds__(RS_THREADS, (NW <= 2 ? 4 : RS_MIN_BLOCKS))
 radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int n,
                      int tiles_per_table, int p, KeyComp kc, const uint32_t* __restrict__ tile_off,
@@ -429,14 +429,21 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
 __global__ void __launch_bounds__(256)
 key_byte_range_kernel(const uint32_t* __restrict__ keys, size_t n_words, uint32_t* __restrict__ out) {
     uint32_t hi_pos = 0, lo_neg = 256;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += (size_t)gridDim.x * blockDim.x) {
-        const uint32_t w = keys[i];
+    auto take = [&](uint32_t w) {
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             const uint32_t u = (w >> (8 * b)) & 0xFFu;
             if (u < 128u) hi_pos = max(hi_pos, u); else lo_neg = min(lo_neg, u);
         }
+    };
+    const size_t n4 = n_words / 4;  // the key array starts on a 16-byte boundary
+    const uint4* k4 = reinterpret_cast<const uint4*>(keys);
+    const size_t stride = (size_t)gridDim.x * blockDim.x, first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t i = first; i < n4; i += stride) {
+        const uint4 v = k4[i];
+        take(v.x); take(v.y); take(v.z); take(v.w);
     }
+    for (size_t i = 4 * n4 + first; i < n_words; i += stride) take(keys[i]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         hi_pos = max(hi_pos, __shfl_xor_sync(0xFFFFFFFFu, hi_pos, o));
