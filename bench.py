@@ -452,7 +452,13 @@ def config_of(wl, spec):
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels,
 # from ncu captures of launches of exactly this size (summaries and commands under profiles/);
 # a workload or size without a capture reports null.
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    ("c2", 1_000_000): {
+        "gather": 300_175_616 + 681_516_544,   # profiles/dedupe_chained_rank_kernel_c2_1M.md
+        "sort": 264_077_824 + 204_391_936,     # profiles/radix_scatter_kernel_c2_1M.md (second pass)
+        "hash": 512_649_728 + 113_138_944,     # profiles/project_tc_kernel_c2_1M.md
+    },
+}
 
 
 def check_exchange(torch, world, rank, n, local_cand, merged, span):
