@@ -4,6 +4,7 @@
 
 #include <cuda_runtime.h>
 #include <curand.h>
+#include <curand_kernel.h>
 
 #include <cstdarg>
 #include <cstdint>

@@ -171,6 +171,48 @@ __global__ void minhash_normalize_kernel(uint32_t* A, uint32_t* B, int n) {
     }
 }
 
+// Own generator kernel for the single-precision and integer parameter sets.  cuRAND's host
+// API with the XORWOW generator in its default ordering runs 4096 independent streams -
+// stream t is curand_init(seed, subsequence t, offset 0) of the device API - and deals the
+// output round-robin: 32-bit element e of a generator's life comes from stream e mod 4096
+// (its next draw), a normal pair p (outputs 2p, 2p + 1) is the next curand_normal2 of stream
+// p mod 4096, and a call that follows continues at the element after the last pair, every
+// stream going on from its own state.  One launch replaces the host API's seeding launch,
+// generation launches and the scaling / normalisation kernels (0.17 ms of host and device time
+// per fit); equality with the host API's output is what the parameter parity tests check.
+constexpr int XW_STREAMS = 4096;
+constexpr int XW_BLOCK = 32;
+
+__global__ void __launch_bounds__(XW_BLOCK)
+xorwow_dense_params_kernel(unsigned long long seed, float* __restrict__ normals, size_t n_pairs, int w,
+                           float* __restrict__ uniforms, int n_unif) {
+    const int t = blockIdx.x * XW_BLOCK + threadIdx.x;
+    curandStateXORWOW_t st;
+    curand_init(seed, (unsigned long long)t, 0ull, &st);
+    float2* out2 = reinterpret_cast<float2*>(normals);
+    for (size_t p = (size_t)t; p < n_pairs; p += XW_STREAMS) {
+        float2 v = curand_normal2(&st);
+        if (w) { v.x = v.x / w; v.y = v.y / w; }  // float / int, pslsh/hash.cuh:84-88
+        out2[p] = v;
+    }
+    // the uniform call continues at element n_pairs of the round-robin
+    const int first = (int)(n_pairs % XW_STREAMS);
+    for (int j = (t - first + XW_STREAMS) % XW_STREAMS; j < n_unif; j += XW_STREAMS)
+        uniforms[j] = curand_uniform(&st);
+}
+
+__global__ void __launch_bounds__(XW_BLOCK)
+xorwow_minhash_params_kernel(unsigned long long seed, uint32_t* __restrict__ A, uint32_t* __restrict__ B, int H) {
+    const int t = blockIdx.x * XW_BLOCK + threadIdx.x;
+    curandStateXORWOW_t st;
+    curand_init(seed, (unsigned long long)t, 0ull, &st);
+    for (int e = t; e < 2 * H; e += XW_STREAMS) {  // two consecutive calls of H elements
+        const uint32_t v = curand(&st);
+        if (e < H) A[e] = (v % (MINHASH_PRIME - 1u)) + 1u;  // minhash/hash.cuh:44-53
+        else B[e - H] = v % MINHASH_PRIME;
+    }
+}
+
 // The handle keeps one XORWOW generator for its lifetime (creating one allocates device
 // memory and synchronises the device); a call re-seeds it, which restarts the sequence at
 // offset 0 exactly as a freshly created generator would.
@@ -188,6 +230,13 @@ curandGenerator_t seeded_generator(const CtxPtr& c, uint64_t seed) {
     CURAND_CHECK(curandSetPseudoRandomGeneratorSeed(c->curand, seed));
     CURAND_CHECK(curandSetGeneratorOffset(c->curand, 0ull));
     return c->curand;
+}
+
+// CULSH_PARAMS_HOST_API=1 routes every parameter set through cuRAND's host API (the tests compare
+// the two); double-precision sets always take it.
+inline bool own_generator() {
+    const char* e = getenv("CULSH_PARAMS_HOST_API");
+    return !(e && *e && atoi(e) != 0);
 }
 
 void generate_params_uncached(culsh_index& ix);
@@ -225,10 +274,16 @@ void generate_params_uncached(culsh_index& ix) {
     const CtxPtr& c = ix.ctx;
     const int H = ix.L * ix.k;
     ix.params = std::make_shared<ParamSet>();
-    struct { curandGenerator_t g; } gen{seeded_generator(c, ix.seed)};
     if (ix.family == CULSH_MINHASH) {
         ix.params->p0.alloc(c, sizeof(uint32_t) * H);
         ix.params->p1.alloc(c, sizeof(uint32_t) * H);
+        if (own_generator()) {
+            xorwow_minhash_params_kernel<<<XW_STREAMS / XW_BLOCK, XW_BLOCK, 0, c->stream>>>(
+                ix.seed, reinterpret_cast<uint32_t*>(ix.params->p0.p), reinterpret_cast<uint32_t*>(ix.params->p1.p), H);
+            KERNEL_CHECK();
+            return;
+        }
+        struct { curandGenerator_t g; } gen{seeded_generator(c, ix.seed)};
         CURAND_CHECK(curandGenerate(gen.g, reinterpret_cast<uint32_t*>(ix.params->p0.p), H));
         CURAND_CHECK(curandGenerate(gen.g, reinterpret_cast<uint32_t*>(ix.params->p1.p), H));
         minhash_normalize_kernel<<<(unsigned)ceil_div(H, 256), 256, 0, c->stream>>>(
@@ -242,6 +297,16 @@ void generate_params_uncached(culsh_index& ix) {
              "n_hash_tables*n_hashes*n_features = %zu must be even (cuRAND normal generation)", pn);
     const size_t esz = ix.is_double ? 8 : 4;
     ix.params->p0.alloc(c, esz * pn);
+    if (!ix.is_double && own_generator()) {
+        const bool ps = ix.family == CULSH_PSLSH;
+        if (ps) ix.params->p1.alloc(c, esz * H);
+        xorwow_dense_params_kernel<<<XW_STREAMS / XW_BLOCK, XW_BLOCK, 0, c->stream>>>(
+            ix.seed, reinterpret_cast<float*>(ix.params->p0.p), pn / 2, ps ? ix.window : 0,
+            ps ? reinterpret_cast<float*>(ix.params->p1.p) : nullptr, ps ? H : 0);
+        KERNEL_CHECK();
+        return;
+    }
+    struct { curandGenerator_t g; } gen{seeded_generator(c, ix.seed)};
     if (ix.is_double)
         CURAND_CHECK(curandGenerateNormalDouble(gen.g, reinterpret_cast<double*>(ix.params->p0.p), pn, 0.0, 1.0));
     else

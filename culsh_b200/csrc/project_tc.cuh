@@ -87,6 +87,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a phase (try_wait may suspend the thread for a while, test_wait never does).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false when the CTA is aborting (the caller leaves its loop).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* d_error) {
@@ -338,13 +350,13 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&ready[s], TC_TRANSFORM_THREADS);
+            mbar_init(&ready[s], TC_TRANSFORM_THREADS / 32);  // one arrival per split warp
             mbar_init(&empty[s], 1);
             s_lo_flag[s] = 0;
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], TC_EPI_THREADS);
+            mbar_init(&acc_empty[b], TC_EPI_WARPS);  // one arrival per epilogue warp
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -388,6 +400,8 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             const uint32_t idesc = make_idesc_tf32(TC_BM, a.n_mma);
             uint32_t it = 0, u = 0;
             unsigned long long n_kb = 0, n_lo = 0;
+            bool pre_ok = false;
+            int pre_flag = 0;
             bool live = true;
             for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
                 for (int c = 0; c < n_units_per_tile && live; ++c, ++u) {
@@ -399,11 +413,23 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     for (int kb = 0; kb < a.n_kblocks; ++kb, ++it) {
                         const int s = it % STAGES;
                         const uint32_t phs = (it / STAGES) & 1;
-                        if (!mbar_wait(&full[s], phs, s_abort, a.d_error) ||
-                            !mbar_wait(&ready[s], phs, s_abort, a.d_error)) { live = false; break; }
+                        // The issuing thread is the serial resource of the kernel (a wait that succeeds
+                        // at once still costs ~100 cycles), so the barriers and the flag of the next
+                        // stage are probed before this stage's MMAs are issued and the answer is used
+                        // one iteration later.
+                        if (!pre_ok && (!mbar_wait(&full[s], phs, s_abort, a.d_error) ||
+                                        !mbar_wait(&ready[s], phs, s_abort, a.d_error))) { live = false; break; }
                         tc_fence_after();
-                        const int use_lo = s_lo_flag[s];
+                        const int use_lo = pre_ok ? pre_flag : s_lo_flag[s];
                         s_lo_flag[s] = 0;
+                        {
+                            const int s1 = (it + 1) % STAGES;
+                            const uint32_t ph1 = ((it + 1) / STAGES) & 1;
+                            const bool f = mbar_test_wait(&full[s1], ph1);
+                            const bool r = mbar_test_wait(&ready[s1], ph1);
+                            pre_flag = s_lo_flag[s1];  // meaningful only when both phases have completed
+                            pre_ok = f && r;
+                        }
                         ++n_kb;
                         n_lo += use_lo ? 1u : 0u;
                         const uint64_t dxh = make_smem_desc<KBLK>(smem_u32(xh(s)));
@@ -458,7 +484,8 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     }
                     if (any_lo) s_lo_flag[s] = 1;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_arrive(&ready[s]);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ready[s]);  // 128 arrivals on one barrier would serialise
                 }
             }
         }
@@ -497,7 +524,279 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     any_ovf |= o;
                 }
                 tc_fence_before();
-                mbar_arrive(&acc_empty[ab]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ab]);
+            }
+        }
+        if (any_ovf) atomicOr(a.d_error, DEV_ERR_NARROW_OVERFLOW);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// TS form: the X operand comes from tensor memory.  An MMA that takes both operands from shared
+// memory reads 4 KB (A) + 32 B x N (B) per K = 8 step, and with the TMA writes and the hi / lo
+// split on top the kernel above is bound by shared-memory bandwidth and by the depth of a
+// four-stage ring of 48 KB stages.  Here the split warps write xh / xl straight into tensor
+// memory (tcgen05.st, 16 + 16 columns per 16-wide K-block) and the MMAs read only P from shared
+// memory: a stage is X as loaded + P hi + P lo for 128 hash columns (48 KB with 32-wide K-blocks,
+// four stages; 24 KB with 16-wide ones, eight stages).  Tensor memory: two accumulators of 128
+// columns + an A ring of 256 columns (hi + lo of every stage) = 512 columns.  G groups of four
+// split warps can take the K-blocks in turn (one group is enough: the issuing thread is the limit).  Roles, barriers, epilogue and abort protocol are those of the
+// kernel above; a work unit is (128-row tile, chunk of whole tables with <= 128 hash columns).
+// ------------------------------------------------------------------------------------------
+constexpr int TS_BN = 128;
+constexpr int TS_A_COL0 = 2 * TS_BN;              // first tensor-memory column of the A ring
+template <int KB>
+struct TsCfg {
+    static constexpr int STAGES = 128 / KB;            // 256 tensor-memory columns / (2 * KB) per stage
+    static constexpr int X_BYTES = TC_BM * KB * 4;
+    static constexpr int P_BYTES = TS_BN * KB * 4;     // per part
+    static constexpr int STAGE_BYTES = X_BYTES + 2 * P_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 1024;
+};
+
+__device__ __forceinline__ void tc_mma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int FAMILY, int G, int KB>
+__global__ void __launch_bounds__(64 + G * TC_TRANSFORM_THREADS + TC_EPI_THREADS, 1)
+project_ts_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmP, TcArgs a) {
+    using Cfg = TsCfg<KB>;
+    constexpr int STAGES = Cfg::STAGES;
+    constexpr int TS_KBLK = KB, TS_X_BYTES = Cfg::X_BYTES, TS_STAGE_BYTES = Cfg::STAGE_BYTES;
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    auto xs = [&](int s) { return base + (size_t)s * TS_STAGE_BYTES; };
+    auto ph = [&](int s) { return base + (size_t)s * TS_STAGE_BYTES + TS_X_BYTES; };
+    auto pl = [&](int s) { return base + (size_t)s * TS_STAGE_BYTES + TS_X_BYTES + Cfg::P_BYTES; };
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + (size_t)STAGES * TS_STAGE_BYTES);
+    uint64_t* full = bars;                   // [STAGES] TMA bytes landed
+    uint64_t* ready = bars + STAGES;         // [STAGES] xh / xl of the stage are in tensor memory
+    uint64_t* empty = bars + 2 * STAGES;     // [STAGES] the stage's MMAs have completed
+    uint64_t* acc_full = bars + 3 * STAGES;  // [2]
+    uint64_t* acc_empty = acc_full + 2;      // [2]
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+    volatile int* s_lo_flag = s_abort + 1;   // [STAGES]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&ready[s], TC_TRANSFORM_THREADS / 32);  // one arrival per warp of a split group
+            mbar_init(&empty[s], 1);
+            s_lo_flag[s] = 0;
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], TC_EPI_WARPS);  // one arrival per epilogue warp
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // whole warp: allocate all 512 tensor-memory columns (one CTA per SM)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    const int n_units_per_tile = a.n_chunks;
+    const uint32_t stage_tx = (uint32_t)(TS_X_BYTES + 2 * a.n_mma * TS_KBLK * 4);
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool live = true;
+            for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
+                for (int c = 0; c < n_units_per_tile && live; ++c) {
+                    for (int kb = 0; kb < a.n_kblocks; ++kb, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t phs = (it / STAGES) & 1;
+                        if (!mbar_wait(&empty[s], phs ^ 1, s_abort, a.d_error)) { live = false; break; }
+                        mbar_expect_tx(&full[s], stage_tx);
+                        tma_load_2d(xs(s), &tmX, &full[s], kb * TS_KBLK, tile * TC_BM);
+                        tma_load_2d(ph(s), &tmP, &full[s], kb * TS_KBLK, (c * 2 + 0) * a.n_mma);
+                        tma_load_2d(pl(s), &tmP, &full[s], kb * TS_KBLK, (c * 2 + 1) * a.n_mma);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_tf32(TC_BM, a.n_mma);
+            uint32_t it = 0, u = 0;
+            unsigned long long n_kb = 0, n_lo = 0;
+            bool pre_ok = false;
+            int pre_flag = 0;
+            bool live = true;
+            for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
+                for (int c = 0; c < n_units_per_tile && live; ++c, ++u) {
+                    const int ab = u & 1;
+                    const uint32_t aph = (u >> 1) & 1;
+                    if (!mbar_wait(&acc_empty[ab], aph ^ 1, s_abort, a.d_error)) { live = false; break; }
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(ab * TS_BN);
+                    for (int kb = 0; kb < a.n_kblocks; ++kb, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t phs = (it / STAGES) & 1;
+                        // next stage's barriers and flag are probed early, as in project_tc_kernel
+                        if (!pre_ok && (!mbar_wait(&full[s], phs, s_abort, a.d_error) ||
+                                        !mbar_wait(&ready[s], phs, s_abort, a.d_error))) { live = false; break; }
+                        tc_fence_after();
+                        const int use_lo = pre_ok ? pre_flag : s_lo_flag[s];
+                        s_lo_flag[s] = 0;
+                        {
+                            const int s1 = (it + 1) % STAGES;
+                            const uint32_t ph1 = ((it + 1) / STAGES) & 1;
+                            const bool f = mbar_test_wait(&full[s1], ph1);
+                            const bool r = mbar_test_wait(&ready[s1], ph1);
+                            pre_flag = s_lo_flag[s1];  // meaningful only when both phases have completed
+                            pre_ok = f && r;
+                        }
+                        ++n_kb;
+                        n_lo += use_lo ? 1u : 0u;
+                        const uint32_t axh = tmem_base + (uint32_t)(TS_A_COL0 + s * 2 * TS_KBLK);
+                        const uint32_t axl = axh + (uint32_t)TS_KBLK;
+                        const uint64_t dph = make_smem_desc<TS_KBLK>(smem_u32(ph(s)));
+                        const uint64_t dpl = make_smem_desc<TS_KBLK>(smem_u32(pl(s)));
+#pragma unroll
+                        for (int ks = 0; ks < TS_KBLK / 8; ++ks) {
+                            const uint64_t adv = (uint64_t)(ks * 2);  // 32 bytes per K step, in 16-byte units
+                            const uint32_t acol = (uint32_t)(ks * 8);  // 8 tf32 values = 8 columns per K step
+                            tc_mma_tf32_ts(d_tmem, axh + acol, dpl + adv, idesc, (kb | ks) != 0);
+                            if (use_lo) tc_mma_tf32_ts(d_tmem, axl + acol, dph + adv, idesc, 1u);
+                            tc_mma_tf32_ts(d_tmem, axh + acol, dph + adv, idesc, 1u);
+                        }
+                        tc_commit(&empty[s]);  // shared-memory stage and A stage reusable once these MMAs are done
+                    }
+                    if (live) tc_commit(&acc_full[ab]);
+                }
+            }
+            if (a.d_mma) {
+                atomicAdd(a.d_mma, n_kb);
+                atomicAdd(a.d_mma + 1, n_lo);
+            }
+        }
+    } else if (warp < 2 + 4 * G) {
+        // ---------------- split X into hi / lo, straight into tensor memory ----------------
+        // G groups of four warps take the K-blocks in turn, so that G of them are in flight.
+        const int grp = (warp - 2) >> 2;
+        // Warp w may touch tensor-memory lanes 32 * (w % 4) ...: a lane owns one row of the tile.
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        // TMA swizzle: 16-byte chunk c of row r sits at chunk c ^ sw (64-byte rows: (r >> 1) & 3, 128-byte rows: r & 7)
+        const int sw = KB == 32 ? (r & 7) : ((r >> 1) & 3);
+        uint32_t it = 0;
+        bool live = true;
+        for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
+            for (int c = 0; c < n_units_per_tile && live; ++c) {
+                for (int kb = 0; kb < a.n_kblocks; ++kb, ++it) {
+                    if ((int)(it % G) != grp) continue;
+                    const int s = it % STAGES;
+                    const uint32_t phs = (it / STAGES) & 1;
+                    if (!mbar_wait(&full[s], phs, s_abort, a.d_error)) { live = false; break; }
+                    const uint4* row = reinterpret_cast<const uint4*>(xs(s) + (size_t)r * (TS_KBLK * 4));
+                    uint32_t hi[KB], lo[KB];
+                    bool any_lo = false;
+#pragma unroll
+                    for (int j = 0; j < KB / 4; ++j) {
+                        const uint4 v = row[j ^ sw];
+                        const uint32_t x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t h = x[e] & 0xFFFFE000u;
+                            const float l = __uint_as_float(x[e]) - __uint_as_float(h);
+                            hi[4 * j + e] = h;
+                            lo[4 * j + e] = __float_as_uint(l);
+                            any_lo |= l != 0.f;
+                        }
+                    }
+                    // the A stage is free: the producer refilled the stage only after `empty`
+                    tc_fence_after();
+                    const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                                        (uint32_t)(TS_A_COL0 + s * 2 * TS_KBLK);
+#pragma unroll
+                    for (int j = 0; j < KB / 16; ++j) {
+                        tc_st16(ta + (uint32_t)(16 * j), hi + 16 * j);
+                        tc_st16(ta + (uint32_t)(TS_KBLK + 16 * j), lo + 16 * j);
+                    }
+                    tc_st_wait();
+                    if (any_lo) s_lo_flag[s] = 1;
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ready[s]);  // 128 arrivals on one barrier would serialise
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;        // TMEM lanes this warp may read: 32*quarter ...
+        const int half = (warp - (2 + 4 * G)) >> 2;  // which half of the unit's tables this warp packs
+        const int NW = a.key_words;
+        const int k = a.k;
+        uint32_t u = 0;
+        bool live = true;
+        bool any_ovf = false;
+        for (int tile = blockIdx.x; tile < a.n_tiles && live; tile += gridDim.x) {
+            const int row = tile * TC_BM + quarter * 32 + lane;
+            const bool row_ok = row < a.n;
+            for (int c = 0; c < n_units_per_tile && live; ++c, ++u) {
+                const int ab = u & 1;
+                const uint32_t aph = (u >> 1) & 1;
+                if (!mbar_wait(&acc_full[ab], aph, s_abort, a.d_error)) { live = false; break; }
+                tc_fence_after();
+                const int t0 = c * a.tables_per_chunk;
+                const int tables_here = min(a.tables_per_chunk, a.L - t0);
+                const int split = (tables_here + 1) >> 1;
+                const int tb = half == 0 ? 0 : split, te = half == 0 ? split : tables_here;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * TS_BN);
+                if (te > tb) {
+                    bool o;
+                    const bool byte_form = FAMILY == CULSH_PSLSH && a.elem_bytes == 1 && ((tb * k) & 15) == 0;
+                    if (byte_form && k == 8) o = epilogue_pslsh_bytes<8>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (byte_form && k == 4) o = epilogue_pslsh_bytes<4>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (byte_form && k == 16) o = epilogue_pslsh_bytes<16>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (byte_form && k == 2) o = epilogue_pslsh_bytes<2>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (NW == 1) o = epilogue_columns<FAMILY, 1>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else if (NW == 2) o = epilogue_columns<FAMILY, 2>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    else o = epilogue_columns<FAMILY, 0>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    any_ovf |= o;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ab]);
             }
         }
         if (any_ovf) atomicOr(a.d_error, DEV_ERR_NARROW_OVERFLOW);
@@ -516,6 +815,7 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 // ------------------------------------------------------------------------------------------
 struct TcPlan {
     int kblk, d_pad, n_chunks, tables_per_chunk, n_mma;
+    bool ts;
 };
 
 inline int tc_kblk_choice() {
@@ -527,11 +827,30 @@ inline int tc_kblk_choice() {
     return v;
 }
 
+// Which kernel projects a shape.  Measured on B200: project_ts_kernel issues MMAs of N <= 128
+// (64 cycles of tensor work each) and is bound by the rate at which one thread can issue them,
+// project_tc_kernel issues N <= 256 and is bound by shared-memory traffic; the first wins when
+// all hash columns fit one 128-column chunk (12.5M x 96 rows, 16 x 8 hashes: 1.83 vs 2.31 ms),
+// the second otherwise (1M x 128, 32 x 16: 0.61 vs 0.66 ms; 10M x 256, 48 x 24: 25 vs 29 ms).
+// CULSH_TC_VARIANT (read once per process) overrides: 0 = always project_tc_kernel,
+// 1 = project_ts_kernel whenever it applies (the tests run every shape through both).
+inline int tc_variant() {
+    static int v = [] {
+        const char* e = getenv("CULSH_TC_VARIANT");
+        return e && *e ? atoi(e) : 2;
+    }();
+    return v;
+}
+
 inline bool tc_plan(int d, int L, int k, TcPlan& p) {
-    if (k > TC_BN || d % 4 != 0) return false;
-    p.kblk = tc_kblk_choice();
+    const int variant = tc_variant();
+    const bool ts = variant == 1 ? k <= TS_BN : (variant == 2 && L * k <= TS_BN);
+    const int bn = ts ? TS_BN : TC_BN;
+    if (k > bn || d % 4 != 0) return false;
+    p.ts = ts;
+    p.kblk = ts ? 32 : tc_kblk_choice();
     p.d_pad = (d + p.kblk - 1) / p.kblk * p.kblk;
-    p.tables_per_chunk = std::min(L, TC_BN / k);
+    p.tables_per_chunk = std::min(L, bn / k);
     p.n_chunks = (L + p.tables_per_chunk - 1) / p.tables_per_chunk;
     p.n_mma = (p.tables_per_chunk * k + 15) / 16 * 16;
     return true;
@@ -630,6 +949,15 @@ inline bool launch_project_tc(const CtxPtr& c, cudaStream_t stream, int family, 
     a.key_words = ks.key_words; a.elem_bytes = ks.elem_bytes; a.family = family;
     a.row_offset = row_offset; a.n_total = n_total;
     int grid = std::min(a.n_tiles, c->sm_count);
+    if (p.ts) {
+        constexpr int smem_ts = TsCfg<32>::SMEM;
+        if ((size_t)smem_ts > c->smem_optin) return false;
+        auto kern = family == CULSH_RPLSH ? project_ts_kernel<CULSH_RPLSH, 1, 32> : project_ts_kernel<CULSH_PSLSH, 1, 32>;
+        CU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_ts));
+        kern<<<grid, 64 + TC_TRANSFORM_THREADS + TC_EPI_THREADS, smem_ts, stream>>>(tmX, tmP, a);
+        KERNEL_CHECK();
+        return true;
+    }
     auto kern = p.kblk == 32
                     ? (family == CULSH_RPLSH ? project_tc_kernel<32, CULSH_RPLSH> : project_tc_kernel<32, CULSH_PSLSH>)
                     : (family == CULSH_RPLSH ? project_tc_kernel<16, CULSH_RPLSH> : project_tc_kernel<16, CULSH_PSLSH>);

@@ -243,6 +243,51 @@ def test_pslsh_compressed_sort_equals_plain_sort(eng, monkeypatch):
         assert sig.min() < 0 < sig.max()
 
 
+def test_own_parameter_generator_equals_curand_host_api(eng, monkeypatch):
+    """The single-launch XORWOW kernel must reproduce cuRAND's host API bit for bit: parameter
+    counts below, at and above one round of the 4096 generator streams, a uniform call that starts
+    in the middle of a round, MinHash's two consecutive integer calls (rplsh/hash.cuh:59-78,
+    pslsh/hash.cuh:60-89, minhash/hash.cuh:26-54)."""
+    culsh, core_mod = eng
+    ones = {d: np.ones((4, d), np.float32) for d in (2, 6, 24, 128, 250)}
+    tiny = sp.csr_matrix(np.array([[1, 1, 0, 0]], dtype=np.float32))
+    handle_core = core_mod.RPLSHCore(1, 1, 0)  # every core of this thread shares one engine handle
+
+    def params(host_api, fam, L, k, d, seed):
+        if host_api:
+            monkeypatch.setenv("CULSH_PARAMS_HOST_API", "1")
+        else:
+            monkeypatch.delenv("CULSH_PARAMS_HOST_API", raising=False)
+        if fam == "rplsh":
+            est = culsh.RPLSH(L, k, seed=seed)
+        elif fam == "pslsh":
+            est = culsh.PStableLSH(L, k, window_size=3, seed=seed)
+        else:
+            est = culsh.MinHashLSH(L, k, seed=seed)
+        handle_core.set_param_cache(False)
+        try:
+            ix = est.fit(tiny if fam == "minhash" else ones[d]).index
+        finally:
+            handle_core.set_param_cache(True)
+        if fam == "rplsh":
+            return [ix.get_projection_matrix()]
+        if fam == "pslsh":
+            return [ix.get_projection_matrix(), ix.get_bias()]
+        return [ix.get_hash_a(), ix.get_hash_b()]
+
+    cases = [("rplsh", 1, 1, 2), ("rplsh", 3, 5, 6), ("rplsh", 16, 16, 24), ("rplsh", 32, 16, 128),
+             ("rplsh", 48, 24, 250), ("pslsh", 1, 1, 2), ("pslsh", 7, 3, 6), ("pslsh", 16, 8, 128),
+             ("pslsh", 80, 64, 24), ("pslsh", 100, 41, 6), ("minhash", 1, 1, 0), ("minhash", 32, 4, 0),
+             ("minhash", 256, 16, 0), ("minhash", 625, 16, 0)]
+    for fam, L, k, d in cases:
+        for seed in (0, 42, 2**40 + 7):
+            own = params(False, fam, L, k, d, seed)
+            ref = params(True, fam, L, k, d, seed)
+            for a, b in zip(own, ref):
+                assert a.dtype == b.dtype and a.shape == b.shape
+                assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), (fam, L, k, d, seed)
+
+
 # ------------------------------------------------------------------------------------------
 # MinHash
 # ------------------------------------------------------------------------------------------
@@ -605,17 +650,21 @@ def test_shard_merge_equals_unsharded(eng):
 # ------------------------------------------------------------------------------------------
 # tensor-core projection (tcgen05 3xTF32) against the CUDA-core projection and the oracle
 # ------------------------------------------------------------------------------------------
-def test_tensor_core_projection_wide_k_block_variant():
-    """The 32-wide K-block variant of the tensor-core kernel is chosen once per process
-    (CULSH_TC_KBLK), so its cases run in a child process with the variable set."""
+@pytest.mark.parametrize("variant", [{"CULSH_TC_VARIANT": "0"}, {"CULSH_TC_VARIANT": "1"},
+                                     {"CULSH_TC_VARIANT": "0", "CULSH_TC_KBLK": "32"}],
+                         ids=["operands_from_shared_memory", "x_from_tensor_memory", "wide_k_blocks"])
+def test_tensor_core_projection_kernel_variants(variant):
+    """Which tensor-core kernel projects a shape is decided once per process (by shape, or by
+    CULSH_TC_VARIANT / CULSH_TC_KBLK), so every case below also runs in child processes that
+    force each kernel onto all shapes."""
     import subprocess
     import sys
-    if os.environ.get("CULSH_TC_KBLK") == "32":
+    if os.environ.get("CULSH_TC_CHILD") == "1":
         pytest.skip("already inside the child process")
-    env = dict(os.environ, CULSH_TC_KBLK="32")
+    env = dict(os.environ, CULSH_TC_CHILD="1", **variant)
     res = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-x", "-m", "gpu",
                           "-p", "no:cacheprovider", "-k",
-                          "test_tensor_core_projection and not wide_k_block"],
+                          "test_tensor_core_projection and not kernel_variants"],
                          env=env, capture_output=True, text=True, timeout=900)
     tail = (res.stdout + res.stderr)[-2000:]
     assert res.returncode == 0, tail
