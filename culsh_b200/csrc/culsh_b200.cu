@@ -719,7 +719,8 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
     // large candidate sets and the row range is a few chain windows; otherwise scratch + compaction.
     int n_win = 1;
     const int cbits = chain_window_bits(ix.n, &n_win);
-    const int stage_ids = (int)std::min<long>(40960, std::max<long>(256, env_long("CULSH_CHAIN_STAGE", 5120)));
+    const long stage_env = env_long("CULSH_CHAIN_STAGE", 5120);
+    const int stage_ids = stage_env == 0 ? 0 : (int)std::min<long>(40960, std::max<long>(256, stage_env));
     const bool chained = n_win <= CHAIN_MAX_WINDOWS && L <= CW_MAX_L && (size_t)nb * 2 >= (size_t)n_q &&
                          (uint64_t)n_q * (uint64_t)n_win < (1ull << 31) &&
                          chain_window_smem_bytes(cbits, stage_ids) + 1024 <= c->smem_optin;

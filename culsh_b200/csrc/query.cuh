@@ -949,6 +949,46 @@ dedupe_chained_rank_kernel(const int32_t* __restrict__ matched, const int32_t* _
     __syncthreads();
     // ---- 4 + 5. rank, stage, copy out ----
     unsigned long long excl = 0;
+    if (stage_ids == 0) {
+        // Direct form (no stage): ranks are computed while warp 0 walks the chain, then every id
+        // is stored at out[excl + rank]; the ~20 KB target span of a window merges in L2.
+        auto rank_of = [&](int32_t x) -> uint32_t {
+            const uint32_t id = (uint32_t)(x - win_lo);
+            const uint32_t word = id >> 5;
+            const uint32_t below = bm32[word] & ((1u << (id & 31)) - 1u);
+            return base32[id >> 9] + (uint32_t)pre16[word] + (uint32_t)__popc(below);
+        };
+        uint32_t rk[MK];
+        if (single && warp != 0) {
+#pragma unroll
+            for (int j = 0; j < MK; ++j) rk[j] = v[j] >= 0 ? rank_of(v[j]) : 0u;
+        }
+        if (warp == 0) {
+            unsigned long long e;
+            chain_exclusive_prefix(status, tk, (unsigned long long)wtotal, lane, d_error, false, true, e);
+            if (lane == 0) s_excl = e;
+            if (single) {
+#pragma unroll
+                for (int j = 0; j < MK; ++j) rk[j] = v[j] >= 0 ? rank_of(v[j]) : 0u;
+            }
+        }
+        __syncthreads();
+        excl = s_excl;
+        int32_t* dst = out_indices + excl;
+        if (single) {
+#pragma unroll
+            for (int j = 0; j < MK; ++j)
+                if (v[j] >= 0) dst[rk[j]] = v[j];
+        } else {
+            wk.init(s_lo, s_pre, L);
+            for (int e0 = wk.w_begin + lane; e0 - lane < wk.w_end; e0 += 32 * MK) {
+                wk.load(cand, s_lo, s_pre, e0, v);
+#pragma unroll
+                for (int j = 0; j < MK; ++j)
+                    if (v[j] >= 0) dst[rank_of(v[j])] = v[j];
+            }
+        }
+    } else
     for (uint32_t chunk_lo = 0; chunk_lo == 0 || chunk_lo < wtotal; chunk_lo += (uint32_t)stage_ids) {
         auto rank = [&](int32_t x) {
             const uint32_t id = (uint32_t)(x - win_lo);
