@@ -90,7 +90,7 @@ SIGNATURES = {
     "culsh_host_free": [VP],
     "culsh_merge_shard_candidates": [VP, I, I, PP, PP, C.POINTER(C.c_int64), PP],
     "culsh_exchange_plan": [VP, I, I, I, VP, VP, C.POINTER(C.c_uint64), PP],
-    "culsh_exchange_push": [VP, I, I, VP, VP, VP, PP, C.c_int64, U64],
+    "culsh_exchange_push": [VP, I, I, I, VP, VP, VP, PP, C.c_int64, U64],
     "culsh_candidates_attach_indices": [VP, VP, U64],
     "culsh_merge_shard_candidates_noalloc": [VP, I, I, PP, PP, C.POINTER(C.c_int64), VP, U64, VP, VP,
                                              C.POINTER(C.c_uint64)],

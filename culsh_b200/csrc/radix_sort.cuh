@@ -14,7 +14,10 @@
 // key of 5 bits per hash - 5 passes instead of 8 for eight hashes -, and the last pass writes the
 // original bytes back.  The rank keeps the unsigned order of the byte (non-negative values
 // first, then the negative ones, two's complement bytes 128..255), so the sorted order is the
-// one a byte-per-pass sort of the original keys gives.
+// one a byte-per-pass sort of the original keys gives.  When such a key takes two words (five to
+// eight hashes: at most 40 bits compressed) and the table has at most 2^24 rows, the compressed
+// key and the row id travel PACKED in one 64-bit item (key << 24 | id) between the first and the
+// last pass: 8 bytes per item instead of 12 and no separate id array in the passes in between.
 #pragma once
 
 #include "common.cuh"
@@ -287,7 +290,11 @@ radix_chunk_base_kernel(uint32_t* __restrict__ chunk_tot, int n_chunks) {
 // ---------------------------------------------------------------------------------------
 // COMP: 0 plain keys; 1 first pass of a compressed sort (keys are compressed as they are
 // loaded); 2 its last pass (the original bytes are written back).
-template <int NW, bool FIRST, int COMP>
+// PACK (NW = 2, compressed): items are (compressed key << 24 | row id); the digit of pass p is
+// byte p + 3 of the item, ids are neither loaded nor stored except by the last pass.
+constexpr int RS_PACK_ID_BITS = 24;
+
+template <int NW, bool FIRST, int COMP, bool PACK = false>
 __global__ void __launch_bounds__(RS_THREADS, (NW <= 2 ? 4 : RS_MIN_BLOCKS))
 radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int n,
@@ -311,6 +318,7 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     const int item0 = lt * TILE;
     const int count = min(TILE, n - item0);
     const size_t base = (size_t)t * n + item0;
+    const int pd = PACK ? p + 3 : p;  // byte of the item that holds this pass's digit
     // needed late: fetched early, and summed only where used (an add here would stall the warp on
     // both loads before the key loads are issued)
     const uint32_t my_off = tile_off[(size_t)tile * 256 + tid];
@@ -328,7 +336,15 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
         if (li < count) {
             load_key<NW>(keys_in + (base + li) * NW, key[i]);
             if (COMP == 1) comp_key<NW>(key[i], kc.sub);
-            val[i] = FIRST ? (uint32_t)(item0 + li) : vals_in[base + li];
+            if constexpr (PACK) {
+                if (COMP == 1) {  // (40-bit compressed key) << 24 | row id
+                    key[i][0] = (key[i][0] << RS_PACK_ID_BITS) | (key[i][NW - 1] >> (32 - RS_PACK_ID_BITS));
+                    key[i][NW - 1] = (key[i][NW - 1] << RS_PACK_ID_BITS) | (uint32_t)(item0 + li);
+                }
+                val[i] = 0;
+            } else {
+                val[i] = FIRST ? (uint32_t)(item0 + li) : vals_in[base + li];
+            }
         } else {
 #pragma unroll
             for (int w = 0; w < NW; ++w) key[i][w] = 0;
@@ -342,7 +358,7 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     for (int i = 0; i < IPT; ++i) {
         const int li = warp * (32 * IPT) + i * 32 + lane;
         const bool valid = li < count;
-        const uint32_t d = valid ? key_digit<NW>(key[i], p) : 0x100u;
+        const uint32_t d = valid ? key_digit<NW>(key[i], pd) : 0x100u;
         // lanes with the same digit.  For one-word keys the kernel is bound by the latency of the
         // shared-memory / match pipeline, and nine ballots (digit bits + validity) are cheaper
         // than match.any; wider keys are bandwidth-bound and take the shorter instruction.
@@ -403,7 +419,7 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
             const uint32_t pos = s_binstart[d] + s_whist[warp * 256 + d] + rank[i];
 #pragma unroll
             for (int w = 0; w < NW; ++w) s_keys[(size_t)pos * NW + w] = key[i][w];
-            s_vals[pos] = val[i];
+            if constexpr (!PACK) s_vals[pos] = val[i];
         }
     }
     __syncthreads();
@@ -413,11 +429,21 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
         uint32_t kk[NW];
 #pragma unroll
         for (int w = 0; w < NW; ++w) kk[w] = s_keys[(size_t)pos * NW + w];
-        const uint32_t d = key_digit<NW>(kk, p);
+        const uint32_t d = key_digit<NW>(kk, pd);
         const uint32_t g = s_gdst[d] + (uint32_t)pos;
-        if (COMP == 2) decomp_key<NW>(kk, kc);
-        store_key<NW>(keys_out + (size_t)g * NW, kk);
-        vals_out[g] = s_vals[pos];
+        if constexpr (PACK) {
+            if (COMP == 2) {  // unpack: id from the low bits, the key back to its two-word compressed form
+                vals_out[g] = kk[NW - 1] & ((1u << RS_PACK_ID_BITS) - 1u);
+                kk[NW - 1] = (kk[0] << (32 - RS_PACK_ID_BITS)) | (kk[NW - 1] >> RS_PACK_ID_BITS);
+                kk[0] >>= RS_PACK_ID_BITS;
+                decomp_key<NW>(kk, kc);
+            }
+            store_key<NW>(keys_out + (size_t)g * NW, kk);
+        } else {
+            if (COMP == 2) decomp_key<NW>(kk, kc);
+            store_key<NW>(keys_out + (size_t)g * NW, kk);
+            vals_out[g] = s_vals[pos];
+        }
     }
 }
 
@@ -475,7 +501,14 @@ inline int radix_sort_tables_nw(const CtxPtr& c, uint32_t* keys[2], uint32_t* va
     auto k_next = radix_scatter_kernel<NW, false, 0>;
     auto k_first_c = radix_scatter_kernel<NW, true, CAN_COMP ? 1 : 0>;
     auto k_last_c = radix_scatter_kernel<NW, false, CAN_COMP ? 2 : 0>;
-    for (auto k : {k_first, k_next, k_first_c, k_last_c})
+    constexpr bool CAN_PACK = NW == 2;
+    auto k_first_p = radix_scatter_kernel<NW, true, CAN_PACK ? 1 : 0, CAN_PACK>;
+    auto k_next_p = radix_scatter_kernel<NW, false, 0, CAN_PACK>;
+    auto k_last_p = radix_scatter_kernel<NW, false, CAN_PACK ? 2 : 0, CAN_PACK>;
+    // CULSH_SORT_NO_PACK=1 keeps key and id apart in a compressed sort (the tests compare the two)
+    const char* no_pack = getenv("CULSH_SORT_NO_PACK");
+    const bool pack = compressed && CAN_PACK && n <= (1 << RS_PACK_ID_BITS) && !(no_pack && atoi(no_pack) != 0);
+    for (auto k : {k_first, k_next, k_first_c, k_last_c, k_first_p, k_next_p, k_last_p})
         CU_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     if (compressed && !CAN_COMP) fail(CULSH_ERR_INTERNAL, "compressed sort needs a key of at most two words");
     const bool chunked = tiles_per_table >= RS_CHUNK_MIN_TILES;
@@ -489,7 +522,7 @@ inline int radix_sort_tables_nw(const CtxPtr& c, uint32_t* keys[2], uint32_t* va
                 keys[cur], n, tiles_per_table, p, kc.sub, tile_hist);
         else
             radix_tile_hist_kernel<NW, false><<<(unsigned)total_tiles, RS_THREADS, 0, s>>>(
-                keys[cur], n, tiles_per_table, p, 0u, tile_hist);
+                keys[cur], n, tiles_per_table, pack ? p + 3 : p, 0u, tile_hist);
         KERNEL_CHECK();
         if (chunked) {
             radix_tile_scan_chunk_kernel<<<(unsigned)(L * n_chunks), RS_SCAN_THREADS, 0, s>>>(
@@ -503,6 +536,7 @@ inline int radix_sort_tables_nw(const CtxPtr& c, uint32_t* keys[2], uint32_t* va
         const bool last = p == passes - 1;
         if (last && c->profiling) cudaEventRecord(c->ev_pass[0], s);
         auto kern = p == 0 ? (compressed ? k_first_c : k_first) : (compressed && last ? k_last_c : k_next);
+        if (pack) kern = p == 0 ? k_first_p : (last ? k_last_p : k_next_p);
         kern<<<(unsigned)total_tiles, RS_THREADS, Cfg::SMEM, s>>>(
             keys[cur], vals[cur], keys[cur ^ 1], vals[cur ^ 1], n, tiles_per_table, p, kc, tile_hist,
             chunked ? chunk_tot : nullptr, n_chunks);

@@ -302,7 +302,7 @@ class PeerExchange:
         shift = self.phase * self.capacity
         recv = (C.c_void_p * self.world)(*[C.c_void_p(p + shift) for p in self.peers])
         ip, _, op = cand.device_pointers()
-        _lib.check(lib.culsh_exchange_push(hp, self.world, nq, ip or None, op, dstpos.data_ptr(), recv,
+        _lib.check(lib.culsh_exchange_push(hp, self.world, self.rank, nq, ip or None, op, dstpos.data_ptr(), recv,
                                            int(row_bases[self.rank]), int(cand.n_total_candidates)))
         t3 = time.perf_counter()
         self._barrier()               # every rank's stores have landed

@@ -219,13 +219,15 @@ int culsh_merge_shard_candidates(culsh_handle* h, int n_shards, int n_queries,
  *     merged counts and offsets but no ids yet.
  *   culsh_exchange_push: store this rank's lists (indices / offsets, device, local row ids),
  *     shifted by row_base, at dstpos inside recv[owner] - device pointers, peer memory for the
- *     other ranks (culsh_peer_open), each with room for its slice total.  Returns when the
- *     stores have been issued and the stream is idle; the owners may read after a barrier.
+ *     other ranks (culsh_peer_open), each with room for its slice total.  The queries are
+ *     visited so that every rank deals its stores evenly over all owners at any moment (the
+ *     order depends on rank), which keeps every NVLink ingress equally loaded.  Returns when
+ *     the stores have been issued and the stream is idle; the owners may read after a barrier.
  *   culsh_candidates_attach_indices: point a result object at an id array it does not own
  *     (the owner's receive buffer, which must outlive it). */
 int culsh_exchange_plan(culsh_handle* h, int n_ranks, int rank, int n_queries, const uint64_t* counts_all,
                         uint64_t* dstpos, uint64_t* slice_totals, culsh_candidates** out);
-int culsh_exchange_push(culsh_handle* h, int n_ranks, int n_queries, const int32_t* indices,
+int culsh_exchange_push(culsh_handle* h, int n_ranks, int rank, int n_queries, const int32_t* indices,
                         const uint64_t* offsets, const uint64_t* dstpos, void* const* recv, int64_t row_base,
                         uint64_t total);
 int culsh_candidates_attach_indices(culsh_candidates* c, const int32_t* indices, uint64_t total);

@@ -226,7 +226,8 @@ def test_pslsh_compressed_sort_equals_plain_sort(eng, monkeypatch):
     """One-byte p-stable keys (up to eight hashes) whose values span at most 32 levels are sorted in
     compressed form (5 bits per hash); the index must be the one the sort of the plain keys builds
     (negative and non-negative hash values, odd and even numbers of hashes, one and two key words,
-    more than one sort tile; sixteen hashes keep the plain sort)."""
+    more than one sort tile; sixteen hashes keep the plain sort); with five to eight hashes the
+    compressed key and the row id travel packed in one 64-bit item."""
     culsh, _ = eng
     rng = np.random.RandomState(41)
     for n, d, L, k, w in [(20000, 24, 5, 8, 4), (9000, 16, 3, 3, 2), (5000, 32, 4, 16, 8), (7000, 12, 6, 5, 3)]:
@@ -235,10 +236,15 @@ def test_pslsh_compressed_sort_equals_plain_sort(eng, monkeypatch):
         a = culsh.PStableLSH(L, k, window_size=w, seed=3).fit(X)
         monkeypatch.setenv("CULSH_SORT_PLAIN_KEYS", "1")
         b = culsh.PStableLSH(L, k, window_size=w, seed=3).fit(X)
+        monkeypatch.delenv("CULSH_SORT_PLAIN_KEYS", raising=False)
+        monkeypatch.setenv("CULSH_SORT_NO_PACK", "1")  # compressed, key and row id in separate arrays
+        c = culsh.PStableLSH(L, k, window_size=w, seed=3).fit(X)
+        monkeypatch.delenv("CULSH_SORT_NO_PACK", raising=False)
         assert a.index.elem_bytes == 1
         for g in ("get_candidate_indices", "get_bucket_signatures", "get_bucket_candidate_offsets",
                   "get_table_bucket_offsets"):
             assert np.array_equal(getattr(a.index, g)(), getattr(b.index, g)()), (g, n, k)
+            assert np.array_equal(getattr(a.index, g)(), getattr(c.index, g)()), (g, n, k)
         sig = a.index.get_bucket_signatures().view(np.int32)
         assert sig.min() < 0 < sig.max()
 
@@ -411,7 +417,9 @@ def test_sort_path_for_mid_sized_sets_on_a_large_index(eng):
 
 
 @pytest.mark.parametrize("bits,stage,threads,slices,loads", [
-    (None, None, None, None, None),  # defaults: two windows at this size
+    (None, None, None, None, None),  # defaults: one window at this size, ids stored straight into the CSR
+    (131072, 0, 256, 1, 16),         # 3 windows, no stage, a warp's ids do not fit one batch of loads at 16
+    (65536, 0, 512, 0, 4),           # 5 windows, no stage, second walk over the lists
     (8192, 256, 256, 1, 16),         # many windows (falls back to the windowed bitmap kernel)
     (65536, 256, 256, 1, 8),         # 5 windows, many copy-out chunks, precomputed slices
     (65536, 300, 512, 0, 4),         # the CTAs search their slices themselves
