@@ -746,12 +746,16 @@ def run_ours(args, wl, spec):
     m = run_workload(torch, args, wl, spec, world, rank, local, exchange, args.steps, args.warmup,
                      e2e=not args.skip_e2e, checks=not args.skip_checks)
     m["steps"], m["warmup"] = args.steps, args.warmup
-    extra = {}
+    extra, extra_errors = {}, {}
     if wl == "c2" and args.rows is None and not args.no_extra:
         torch.cuda.empty_cache()
         for ew in ("c4", "c5"):
-            em = run_workload(torch, args, ew, dict(WORKLOADS[ew]), world, rank, local, exchange, 5, 3,
-                              e2e=False, checks=False)
+            try:
+                em = run_workload(torch, args, ew, dict(WORKLOADS[ew]), world, rank, local, exchange, 5, 3,
+                                  e2e=False, checks=False)
+            except Exception as ex:  # the headline line must still be printed
+                extra_errors[ew] = f"{type(ex).__name__}: {ex}"[:300]
+                break
             em["steps"], em["warmup"] = 5, 3
             extra[ew] = em
             torch.cuda.empty_cache()
@@ -768,6 +772,8 @@ def run_ours(args, wl, spec):
             el = line_of(torch, args, ew, dict(WORKLOADS[ew]), world, em, peaks, tf32)
             line["extra"][ew] = {key: el[key] for key in ("metric", "value", "unit", "ms_per_step", "steps", "scaling",
                                                        "config", "stage_ms", "shape", "first_call_ms")}
+    for ew, msg in extra_errors.items():
+        line.setdefault("extra", {})[ew] = {"error": msg}
     if world == 1 and not args.skip_cpu:
         line["cpu_baseline"] = cpu_baseline(wl)
     print(json.dumps(line))

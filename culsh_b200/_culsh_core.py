@@ -280,6 +280,11 @@ class _IndexBase:
     key_words = property(lambda self: int(self._m.key_words))
     elem_bytes = property(lambda self: int(self._m.elem_bytes))
 
+    def row_keys(self, out_ptr: int):
+        """Write the packed key of every indexed row, [L][n_samples][key_words] uint32 in row
+        order, to device memory at `out_ptr`."""
+        _lib.check(self._h.lib.culsh_index_row_keys(self._h.ptr, self._ptr, out_ptr))
+
     def _copy(self, fn, n, dtype):
         arr = np.empty(int(n), dtype=dtype)
         if n:
@@ -417,6 +422,15 @@ class _CoreBase:
         """False: every fit generates its hash parameters again (upstream's behaviour) instead
         of reusing the set this handle made for the same (family, shape, seed)."""
         _lib.check(self._h.lib.culsh_set_param_cache(self._h.ptr, int(bool(enabled))))
+
+    def query_keys(self, keys_ptr: int, n_queries: int, index) -> Candidates:
+        """Candidates for queries given as packed keys on the device ([L][n_queries][key_words]
+        uint32 in the index's own key layout, e.g. another shard's `index.row_keys`): lookup,
+        gather and dedupe without hashing."""
+        out = C.c_void_p()
+        _lib.check(self._h.lib.culsh_index_query_keys(self._h.ptr, index._ptr, keys_ptr, int(n_queries),
+                                                      C.byref(out)))
+        return Candidates(out, self._h)
 
     def set_projection_path(self, path: int):
         _lib.check(self._h.lib.culsh_set_projection_path(self._h.ptr, int(path)))

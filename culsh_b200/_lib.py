@@ -90,6 +90,8 @@ SIGNATURES = {
     "culsh_host_free": [VP],
     "culsh_merge_shard_candidates": [VP, I, I, PP, PP, C.POINTER(C.c_int64), PP],
     "culsh_exchange_plan": [VP, I, I, I, VP, VP, C.POINTER(C.c_uint64), PP],
+    "culsh_index_row_keys": [VP, VP, VP],
+    "culsh_index_query_keys": [VP, VP, VP, I, PP],
     "culsh_exchange_push": [VP, I, I, I, VP, VP, VP, PP, C.c_int64, U64],
     "culsh_candidates_attach_indices": [VP, VP, U64],
     "culsh_merge_shard_candidates_noalloc": [VP, I, I, PP, PP, C.POINTER(C.c_int64), VP, U64, VP, VP,

@@ -1274,6 +1274,62 @@ int culsh_index_hash_csr(culsh_handle* h, const culsh_index* ix, const int32_t* 
     });
 }
 
+// ---- packed keys in and out: the sharded self-join ships signatures, not rows -------------
+int culsh_index_row_keys(culsh_handle* h, const culsh_index* ix, uint32_t* keys_out) {
+    return guarded([&] {
+        if (!h || !ix || !keys_out) fail(CULSH_ERR_INVALID, "null argument");
+        if (!is_device_pointer(keys_out)) fail(CULSH_ERR_INVALID, "keys_out must be device memory");
+        DeviceGuard g(h->ctx->device);
+        const CtxPtr& c = ix->ctx;
+        if (ix->n_buckets > 0) {
+            CULSH_DISPATCH_NW(ix->ks.key_words,
+                              (row_keys_kernel<NW><<<(unsigned)ceil_div(ix->n_buckets, 256), 256, 0, c->stream>>>(
+                                  ix->bucket_keys.p, ix->bucket_offsets.p, ix->cand.p, ix->n_buckets, ix->n, keys_out)));
+            KERNEL_CHECK();
+        }
+        CU_CHECK(cudaStreamSynchronize(c->stream));
+    });
+}
+
+int culsh_index_query_keys(culsh_handle* h, const culsh_index* ix, const uint32_t* keys, int n_q,
+                           culsh_candidates** out) {
+    return guarded([&] {
+        if (!h || !ix || !out) fail(CULSH_ERR_INVALID, "null handle, index or output pointer");
+        if (ix->ctx->device != h->ctx->device) fail(CULSH_ERR_INVALID, "index lives on another device");
+        if (n_q < 0) fail(CULSH_ERR_INVALID, "n_queries must not be negative");
+        DeviceGuard g(h->ctx->device);
+        const CtxPtr& c = ix->ctx;
+        c->stats = culsh_stats{};
+        launch_counter() = 0;
+        auto res = std::make_unique<culsh_candidates>();
+        if (n_q == 0) {
+            empty_result(c, *res);
+            *out = res.release();
+            return;
+        }
+        if (!keys || !is_device_pointer(keys)) fail(CULSH_ERR_INVALID, "keys must be device memory");
+        if ((uint64_t)n_q * ix->L >= (1ull << 31))
+            fail(CULSH_ERR_UNSUPPORTED, "n_queries * n_hash_tables must be below 2^31 per call");
+        reset_error_word(c);
+        const int NW = ix->ks.key_words;
+        const size_t pairs = (size_t)n_q * ix->L;
+        StageTimer tm(c);
+        Scratch<int32_t> matched(c, SL_MATCHED, pairs);
+        tm.mark();
+        CULSH_DISPATCH_NW(NW, (lookup_kernel<NW><<<(unsigned)ceil_div(pairs, 256), 256, 0, c->stream>>>(
+                                  keys, nullptr, n_q, ix->L, ix->bucket_keys.p, ix->table_offsets.p, matched.p)));
+        KERNEL_CHECK();
+        tm.mark();
+        query_from_matched(*ix, matched.p, n_q, *res, tm);
+        c->stats.lookup_ms = tm.between(0, 1);
+        c->stats.gather_ms = tm.between(1, 2);
+        c->stats.total_ms = tm.between(0, 2);
+        check_error_word(read_error_word(c));
+        c->stats.launches = launch_counter();
+        *out = res.release();
+    });
+}
+
 // ---- Index getters / loaders ------------------------------------------------------------
 int culsh_index_get_meta(const culsh_index* ix, culsh_index_meta* m) {
     return guarded([&] {

@@ -252,4 +252,26 @@ __global__ void pack_keys_kernel(const uint8_t* __restrict__ raw, size_t count, 
     }
 }
 
+// Packed key of every indexed row, in row order: out[(t * n + row) * NW + w] = key of the bucket
+// that holds `row` in table t.  One thread per bucket walks the bucket's rows (buckets of an LSH
+// index are short); the stores of a table stay inside its n * NW words.
+template <int NW>
+__global__ void __launch_bounds__(256)
+row_keys_kernel(const uint32_t* __restrict__ bucket_keys, const int32_t* __restrict__ bucket_offsets,
+                const int32_t* __restrict__ cand, int n_buckets, int n, uint32_t* __restrict__ out) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_buckets) return;
+    uint32_t key[NW];
+#pragma unroll
+    for (int w = 0; w < NW; ++w) key[w] = bucket_keys[(size_t)b * NW + w];
+    const int lo = bucket_offsets[b], hi = bucket_offsets[b + 1];
+    if (lo >= hi) return;
+    const size_t table_base = (size_t)(lo / n) * (size_t)n;  // a bucket lies inside one table
+    for (int p = lo; p < hi; ++p) {
+        uint32_t* dst = out + (table_base + (size_t)cand[p]) * NW;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) dst[w] = key[w];
+    }
+}
+
 }  // namespace culsh_b200

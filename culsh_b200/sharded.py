@@ -341,23 +341,71 @@ def all_gather_rows(X, group=None):
     return torch.cat([out[j * longest:j * longest + r] for j, r in enumerate(rows)]), rows
 
 
+def all_gather_row_keys(index, group=None, device=None):
+    """Packed keys of every shard's rows, [L][n_all][key_words] int32 on this rank's device, rows in
+    rank order; returns (keys_all, rows_per_rank).  Every shard writes the keys of its own rows
+    (`index.row_keys`), one padded all_gather_into_tensor (NCCL) moves them."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    L, nw, n_local = index.n_hash_tables, index.key_words, index.n_samples
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    rows = [None] * world
+    dist.all_gather_object(rows, int(n_local), group=group)
+    longest = max(rows)
+    block = torch.zeros((L, longest, nw), dtype=torch.int32, device=dev) if n_local < longest else \
+        torch.empty((L, longest, nw), dtype=torch.int32, device=dev)
+    if n_local == longest:
+        index.row_keys(block.data_ptr())
+    else:
+        mine = torch.empty((L, n_local, nw), dtype=torch.int32, device=dev)
+        index.row_keys(mine.data_ptr())
+        block[:, :n_local] = mine
+    gathered = torch.empty((world, L, longest, nw), dtype=torch.int32, device=dev)
+    dist.all_gather_into_tensor(gathered, block, group=group)
+    keys_all = torch.empty((L, sum(rows), nw), dtype=torch.int32, device=dev)
+    base = 0
+    for j, r in enumerate(rows):
+        keys_all[:, base:base + r] = gathered[j, :, :r]
+        base += r
+    return keys_all, rows
+
+
 def fit_query_sharded(estimator, X_local, exchange: "PeerExchange", batch_size: Optional[int] = None,
-                      group=None):
+                      group=None, ship: Optional[str] = None):
     """Self-join over a row-sharded data set (upstream: single-GPU fit_query, core/fit_query.cuh:30-55).
 
     `estimator` is an unfitted RPLSH / PStableLSH object built with the same arguments (seed
     included) on every rank; `X_local` is this rank's row block (blocks in rank order form the
     data set, every block as long as the first except possibly the last ones, as shard_bounds
-    cuts them).  Every rank fits its block, all blocks are gathered so that every rank can ask
-    its shard for the neighbours of EVERY row, and the peer exchange hands each rank the merged
-    candidate lists of its own rows with global row ids.  Returns (Candidates, (row_lo, row_hi)).
+    cuts them).  Every rank fits its block, then every rank asks its shard for the neighbours of
+    EVERY row, and the peer exchange hands each rank the merged candidate lists of its own rows
+    with global row ids.  Returns (Candidates, (row_lo, row_hi)).
+
+    What travels between the shards (`ship`): "keys" - the packed signatures of the rows, taken
+    from the fitted index, so that every row is hashed once, by its own shard (RPLSH on CUDA
+    tensors: a signature bit means the same on every shard) - or "rows" - the rows themselves,
+    hashed again by every shard (PStableLSH, whose shards may narrow their key elements
+    differently; NumPy inputs).  Default: "keys" where it applies.
     """
+    import numpy as np
     model = estimator.fit(X_local)
-    X_all, rows = all_gather_rows(X_local, group)
+    keys_ok = (type(estimator).__name__ == "RPLSH" and not isinstance(X_local, np.ndarray)
+               and getattr(X_local, "is_cuda", False))
+    if ship is None:
+        ship = "keys" if keys_ok else "rows"
+    if ship == "keys":
+        if not keys_ok:
+            raise ValueError("signatures can be shipped for RPLSH on CUDA tensors only")
+        keys_all, rows = all_gather_row_keys(model.index, group, X_local.device)
+        cand = model._core.query_keys(keys_all.data_ptr(), int(keys_all.shape[1]), model.index)
+        del keys_all
+    else:
+        X_all, rows = all_gather_rows(X_local, group)
+        cand = model.query(X_all, batch_size=batch_size)
     bases = [0]
     for r in rows[:-1]:
         bases.append(bases[-1] + r)
-    cand = model.query(X_all, batch_size=batch_size)
     merged, (lo, hi) = exchange.exchange(cand, bases)
     me = exchange.rank
     if (lo, hi) != (bases[me], bases[me] + rows[me]):

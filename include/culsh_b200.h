@@ -146,6 +146,18 @@ int culsh_minhash_fit_query(culsh_handle* h, const int32_t* indices, const int32
                             int n_samples, int n_features, int n_hash_tables, int n_hashes,
                             uint64_t seed, culsh_candidates** out);
 
+/* ---- packed keys in and out (extension; no upstream counterpart: upstream's self-join,
+ *      core/fit_query.cuh:30-55, is single-GPU).  A row-sharded self-join ships the rows' packed
+ *      signatures between the shards instead of the rows, so every row is hashed once.
+ *   culsh_index_row_keys: packed key of every indexed row in row order, device memory,
+ *     [n_hash_tables][n_samples][key_words] uint32 (key_words from culsh_index_get_meta).
+ *   culsh_index_query_keys: candidates for n_queries queries given as such keys (device,
+ *     [n_hash_tables][n_queries][key_words], same family, shape, seed and key layout as the
+ *     index): lookup + gather + dedupe, no hashing. -------------------------------------- */
+int culsh_index_row_keys(culsh_handle* h, const culsh_index* index, uint32_t* keys_out);
+int culsh_index_query_keys(culsh_handle* h, const culsh_index* index, const uint32_t* keys, int n_queries,
+                           culsh_candidates** out);
+
 /* ---- signatures only (diagnostic; upstream keeps X_sig internal: rplsh/hash.cuh:93-129,
  *      pslsh/hash.cuh:105-142, minhash/hash.cuh:142-155).  `sig_out` receives upstream's
  *      table-major raw layout [L][n][k] of uint8 / int32 / uint32, host or device. -------- */

@@ -452,6 +452,33 @@ def test_chained_dedupe_windows_chunks_and_slices(eng, monkeypatch, bits, stage,
     _assert_candidates_equal(model.query(Q), want)
 
 
+def test_query_by_row_keys_equals_fit_query(eng):
+    """The packed keys an index reports for its own rows, fed back as queries, give the self-join
+    of fit_query (the path a row-sharded self-join takes between shards); one- and two-word keys,
+    sign bits and p-stable bytes."""
+    import torch
+    culsh, core_mod = eng
+    rng = np.random.RandomState(17)
+    n, d = 5000, 24
+    X = rng.randn(n, d).astype(np.float32)
+    X[100:140] = X[7]  # a larger bucket
+    cases = [(culsh.RPLSH(6, 10, seed=3), core_mod.RPLSHCore(6, 10, 3)),
+             (culsh.RPLSH(3, 40, seed=3), core_mod.RPLSHCore(3, 40, 3)),
+             (culsh.PStableLSH(5, 6, window_size=2, seed=3), core_mod.PSLSHCore(5, 6, 2, 3))]
+    for lsh, core in cases:
+        model = lsh.fit(X)
+        ix = model.index
+        keys = torch.full((ix.n_hash_tables, n, ix.key_words), -1, dtype=torch.int32, device="cuda")
+        ix.row_keys(keys.data_ptr())
+        got = core.query_keys(keys.data_ptr(), n, ix)
+        want = lsh.fit_query(X)
+        assert np.array_equal(got.get_offsets(), want.get_offsets())
+        assert np.array_equal(got.get_indices(), want.get_indices())
+        assert np.array_equal(got.get_counts(), want.get_counts())
+        sub = core.query_keys(keys[:, :0].contiguous().data_ptr(), 0, ix)
+        assert sub.n_queries == 0
+
+
 def test_no_match_and_zero_queries(eng):
     culsh, _ = eng
     rng = np.random.RandomState(3)

@@ -106,9 +106,15 @@ def _nccl_worker(rank, world, port, out_dir):
         lo, hi = sharded.shard_bounds(n, world, rank)
         Xd = torch.from_numpy(X[lo:hi]).cuda(rank)
         ex = sharded.PeerExchange(device=rank)
-        fq, (r_lo, r_hi) = sharded.fit_query_sharded(culsh_b200.RPLSH(L, k, seed=9), Xd, ex, batch_size=2000)
+        # default for RPLSH on CUDA tensors: the shards ship packed signatures, not rows
+        fq, (r_lo, r_hi) = sharded.fit_query_sharded(culsh_b200.RPLSH(L, k, seed=9), Xd, ex)
         np.savez(os.path.join(out_dir, f"n{rank}.npz"), idx=fq.get_indices(), off=fq.get_offsets(),
                  r_lo=r_lo, r_hi=r_hi)
+        fr, (q_lo, q_hi) = sharded.fit_query_sharded(culsh_b200.RPLSH(L, k, seed=9), Xd, ex, batch_size=2000,
+                                                      ship="rows")
+        assert (q_lo, q_hi) == (r_lo, r_hi)
+        assert np.array_equal(fr.get_indices(), fq.get_indices())
+        assert np.array_equal(fr.get_offsets(), fq.get_offsets())
         if rank == 0:
             w = culsh_b200.RPLSH(L, k, seed=9).fit_query(X)
             np.savez(os.path.join(out_dir, "n_whole.npz"), idx=w.get_indices(), off=w.get_offsets())
