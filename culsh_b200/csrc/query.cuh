@@ -701,26 +701,16 @@ __device__ __forceinline__ int warp_lower_bound(const int32_t* __restrict__ a, i
 template <int NT, int MK>
 struct ListWalk {
     int t, next, base, w_begin, w_end, per_warp;
-    // Up to 32 lists: lane i keeps the end of list i in the flat sequence and the shift from flat
-    // position to position in cand, and a row of 32 elements finds its lists with two ballots and
-    // a shuffle - no shared-memory reads and no loop that one row's load would have to wait for,
-    // so all MK loads of a batch are issued back to back.
-    bool in_regs;
-    int pre_hi, shift;
 
     __device__ __forceinline__ void init(const int* __restrict__ s_lo, const int* __restrict__ s_pre, int Lg) {
         constexpr int NWARP = NT / 32;
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int warp = threadIdx.x >> 5;
         const int total = s_pre[Lg];
         per_warp = (((total + NWARP - 1) / NWARP) + 31) & ~31;
         w_begin = warp * per_warp;
         w_end = min(total, w_begin + per_warp);
         t = 0; next = 0; base = 0;
-        in_regs = Lg <= 32;
-        pre_hi = 0x7FFFFFFF; shift = 0;
-        if (in_regs) {
-            if (lane < Lg) { pre_hi = s_pre[lane + 1]; shift = s_lo[lane] - s_pre[lane]; }
-        } else if (w_begin < w_end) {
+        if (w_begin < w_end) {
             int a = 0, b = Lg - 1;
             while (a < b) {  // largest t with s_pre[t] <= w_begin
                 const int mid = (a + b + 1) >> 1;
@@ -731,29 +721,9 @@ struct ListWalk {
             base = s_lo[t] - s_pre[t];  // flat position -> position in cand
         }
     }
-    // batch whose first element (of lane 0) is the flat position e0 - lane; called by whole warps
+    // batch whose first element (of lane 0) is the flat position e0 - lane
     __device__ __forceinline__ void load(const int32_t* __restrict__ cand, const int* __restrict__ s_lo,
                                          const int* __restrict__ s_pre, int e0, int32_t (&v)[MK]) {
-        if (in_regs) {
-            const int lane = threadIdx.x & 31;
-#pragma unroll
-            for (int j = 0; j < MK; ++j) {
-                const int e = e0 + 32 * j, row = e - lane;
-                v[j] = -1;
-                if (row < w_end) {  // warp-uniform
-                    int tt = __popc(__ballot_sync(0xFFFFFFFFu, pre_hi <= row));  // lists that end before the row
-                    uint32_t inside = __ballot_sync(0xFFFFFFFFu, pre_hi > row && pre_hi <= row + 31);
-                    while (inside) {  // list ends inside the row: seldom more than one
-                        const int i = __ffs(inside) - 1;
-                        inside &= inside - 1;
-                        tt += e >= __shfl_sync(0xFFFFFFFFu, pre_hi, i) ? 1 : 0;
-                    }
-                    const int sh = __shfl_sync(0xFFFFFFFFu, shift, tt & 31);
-                    if (e < w_end) v[j] = cand[sh + e];
-                }
-            }
-            return;
-        }
 #pragma unroll
         for (int j = 0; j < MK; ++j) {
             const int e = e0 + 32 * j;
