@@ -454,9 +454,9 @@ def config_of(wl, spec):
 # a workload or size without a capture reports null.
 NCU_TRAFFIC = {
     ("c2", 1_000_000): {
-        "gather": 300_175_616 + 681_516_544,   # profiles/dedupe_chained_rank_kernel_c2_1M.md
-        "sort": 264_077_824 + 204_391_936,     # profiles/radix_scatter_kernel_c2_1M.md (second pass)
-        "hash": 512_649_728 + 113_138_944,     # profiles/project_tc_kernel_c2_1M.md
+        "gather": 273_526_528 + 677_084_416,   # profiles/dedupe_chained_rank_kernel_c2_1M.md
+        "sort": 264_078_336 + 203_595_776,     # profiles/radix_scatter_kernel_c2_1M.md (second pass)
+        "hash": 512_629_760 + 113_291_008,     # profiles/project_tc_kernel_c2_1M.md
     },
 }
 

@@ -432,6 +432,11 @@ class _CoreBase:
                                                       C.byref(out)))
         return Candidates(out, self._h)
 
+    def trim_scratch(self, keep_bytes: int = 0):
+        """Free the engine's grow-only temporaries and kept result blocks larger than
+        `keep_bytes` (they are allocated again when next needed)."""
+        _lib.check(self._h.lib.culsh_trim_scratch(self._h.ptr, int(keep_bytes)))
+
     def set_projection_path(self, path: int):
         _lib.check(self._h.lib.culsh_set_projection_path(self._h.ptr, int(path)))
 

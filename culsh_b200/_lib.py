@@ -48,6 +48,7 @@ SIGNATURES = {
     "culsh_get_stats": [VP, C.POINTER(Stats)],
     "culsh_set_profiling": [VP, I],
     "culsh_set_param_cache": [VP, I],
+    "culsh_trim_scratch": [VP, U64],
     "culsh_set_projection_path": [VP, I],
     "culsh_rplsh_fit_f32": [VP, VP, I, I, I, I, U64, PP],
     "culsh_rplsh_fit_f64": [VP, VP, I, I, I, I, U64, PP],

@@ -728,8 +728,11 @@ void query_from_matched(const culsh_index& ix, const int32_t* matched, int n_q, 
                          (uint64_t)n_q * (uint64_t)n_win < (1ull << 31) &&
                          chain_window_smem_bytes(cbits, stage_ids) + 1024 <= c->smem_optin;
     const uint32_t n_other = (uint32_t)n_q - nb - nm;  // queries on the warp path (incl. empty ones)
+    // Scratch copy of the ids of the queries that do not take the chained kernel (warp / sort
+    // paths write it, indexed by raw offsets); the chained kernel reads it only for those, so a
+    // query set that is all large sets (the 1M-row benchmark: 743 MB) needs none.
     Scratch<int32_t> tmp;
-    tmp.reserve(c, SL_TMP, raw_total);
+    if (!(chained && n_other == 0 && nm == 0)) tmp.reserve(c, SL_TMP, raw_total);
     tr.lap("alloc tmp");
     if (n_other) {
         size_t blocks = std::min<size_t>(ceil_div(n_q, SM_WARPS), (size_t)c->sm_count * 16);
@@ -1101,6 +1104,32 @@ int culsh_set_param_cache(culsh_handle* h, int enabled) {
         if (!h) fail(CULSH_ERR_INVALID, "null handle");
         h->ctx->param_cache_enabled = enabled != 0;
         if (!enabled) h->ctx->param_cache.clear();
+    });
+}
+
+int culsh_trim_scratch(culsh_handle* h, uint64_t keep_bytes) {
+    return guarded([&] {
+        if (!h) fail(CULSH_ERR_INVALID, "null handle");
+        const CtxPtr& c = h->ctx;
+        DeviceGuard g(c->device);
+        CU_CHECK(cudaStreamSynchronize(c->stream));
+        CU_CHECK(cudaStreamSynchronize(c->copy_stream));
+        for (int i = 0; i < SL_COUNT; ++i) {
+            if (c->slot_ptr[i] && c->slot_cap[i] > keep_bytes) {
+                CU_CHECK(cudaFree(c->slot_ptr[i]));
+                c->slot_ptr[i] = nullptr;
+                c->slot_cap[i] = 0;
+            }
+        }
+        for (auto it = c->big_free.begin(); it != c->big_free.end();) {
+            if (it->cap > keep_bytes) {
+                c->big_free_bytes -= it->cap;
+                CU_CHECK(cudaFree(it->p));
+                it = c->big_free.erase(it);
+            } else {
+                ++it;
+            }
+        }
     });
 }
 

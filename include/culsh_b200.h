@@ -95,6 +95,12 @@ int culsh_set_profiling(culsh_handle* h, int enabled);
  * with the same (family, shape, window, dtype, seed); 0 = every fit generates them again,
  * as upstream does (rplsh/hash.cuh:59-78, pslsh/hash.cuh:60-89, minhash/hash.cuh:42-54). */
 int culsh_set_param_cache(culsh_handle* h, int enabled);
+/* Temporaries live in per-handle device buffers that only grow (after a 10M-row self-join:
+ * 5.7 GB) and released result blocks are kept for reuse; this frees every such buffer larger
+ * than keep_bytes (0 = all of them).  Waits for the handle's streams; the next call that needs
+ * a buffer allocates it again.  No upstream counterpart (upstream allocates and frees its
+ * temporaries inside every call, core/fit.cuh:160-252, core/query.cuh:290-478). */
+int culsh_trim_scratch(culsh_handle* h, uint64_t keep_bytes);
 /* Force the projection path: 0 auto, 1 SIMT fp32/fp64 kernel, 2 tcgen05 3xTF32 kernel. */
 int culsh_set_projection_path(culsh_handle* h, int path);
 

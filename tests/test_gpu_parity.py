@@ -479,6 +479,30 @@ def test_query_by_row_keys_equals_fit_query(eng):
         assert sub.n_queries == 0
 
 
+def test_trim_scratch_frees_and_recovers(eng):
+    """The handle's grow-only temporaries and kept result blocks can be handed back to the device;
+    the next call allocates what it needs again and returns the same result."""
+    import torch
+    culsh, core_mod = eng
+    rng = np.random.RandomState(3)
+    X = rng.randn(200_000, 16).astype(np.float32)
+    lsh = culsh.RPLSH(8, 6, seed=2)
+    core = core_mod.RPLSHCore(8, 6, 2)
+    model = lsh.fit(X)
+    first = model.query(X[:2000])
+    idx, off = first.get_indices(), first.get_offsets()
+    del first
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    core.trim_scratch(0)
+    free_after = torch.cuda.mem_get_info()[0]
+    assert free_after > free_before + (8 << 20)  # sort buffers of 1.6 M items alone are 12.8 MB
+    again = model.query(X[:2000])
+    assert np.array_equal(again.get_indices(), idx) and np.array_equal(again.get_offsets(), off)
+    core.trim_scratch(1 << 40)  # nothing is that large: a no-op
+    assert np.array_equal(lsh.fit(X).query(X[:2000]).get_offsets(), off)
+
+
 def test_no_match_and_zero_queries(eng):
     culsh, _ = eng
     rng = np.random.RandomState(3)
