@@ -545,21 +545,25 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 // split on top the kernel above is bound by shared-memory bandwidth and by the depth of a
 // four-stage ring of 48 KB stages.  Here the split warps write xh / xl straight into tensor
 // memory (tcgen05.st, 16 + 16 columns per 16-wide K-block) and the MMAs read only P from shared
-// memory: a stage is X as loaded + P hi + P lo for 128 hash columns (48 KB with 32-wide K-blocks,
-// four stages; 24 KB with 16-wide ones, eight stages).  Tensor memory: two accumulators of 128
-// columns + an A ring of 256 columns (hi + lo of every stage) = 512 columns.  G groups of four
+// memory: a stage is X as loaded + P hi + P lo for BN hash columns (32-wide K-blocks: 48 KB and
+// four stages at BN = 128, 64 KB and three stages at BN = 192).  Tensor memory: two accumulators
+// of BN columns + an A ring in the remaining columns (hi + lo of a K-block = 64 columns: four
+// stages at BN = 128, two at BN = 192, where a split warp therefore waits for the MMAs of the
+// K-block two back before it overwrites their operand).  G groups of four
 // split warps can take the K-blocks in turn (one group is enough: the issuing thread is the limit).  Roles, barriers, epilogue and abort protocol are those of the
 // kernel above; a work unit is (128-row tile, chunk of whole tables with <= 128 hash columns).
 // ------------------------------------------------------------------------------------------
-constexpr int TS_BN = 128;
-constexpr int TS_A_COL0 = 2 * TS_BN;              // first tensor-memory column of the A ring
-template <int KB>
+constexpr int TS_BN = 128;      // accumulator columns of the narrow form
+constexpr int TS_BN_WIDE = 192; // and of the wide form (shapes of several chunks)
+template <int KB, int BN>
 struct TsCfg {
-    static constexpr int STAGES = 128 / KB;            // 256 tensor-memory columns / (2 * KB) per stage
+    static constexpr int A_STAGES = (512 - 2 * BN) / (2 * KB);  // tensor-memory columns left for xh / xl
     static constexpr int X_BYTES = TC_BM * KB * 4;
-    static constexpr int P_BYTES = TS_BN * KB * 4;     // per part
+    static constexpr int P_BYTES = BN * KB * 4;                 // per part
     static constexpr int STAGE_BYTES = X_BYTES + 2 * P_BYTES;
+    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;   // shared-memory ring
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 1024;
+    static_assert(A_STAGES >= 2 && STAGES >= A_STAGES, "ring sizes");
 };
 
 __device__ __forceinline__ void tc_mma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
@@ -581,11 +585,12 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
 }
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-template <int FAMILY, int G, int KB>
+template <int FAMILY, int G, int KB, int BN>
 __global__ void __launch_bounds__(64 + G * TC_TRANSFORM_THREADS + TC_EPI_THREADS, 1)
 project_ts_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmP, TcArgs a) {
-    using Cfg = TsCfg<KB>;
-    constexpr int STAGES = Cfg::STAGES;
+    using Cfg = TsCfg<KB, BN>;
+    constexpr int STAGES = Cfg::STAGES, A_STAGES = Cfg::A_STAGES;
+    constexpr int TS_A_COL0 = 2 * BN;  // first tensor-memory column of the A ring
     constexpr int TS_KBLK = KB, TS_X_BYTES = Cfg::X_BYTES, TS_STAGE_BYTES = Cfg::STAGE_BYTES;
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
@@ -667,7 +672,7 @@ project_ts_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     const uint32_t aph = (u >> 1) & 1;
                     if (!mbar_wait(&acc_empty[ab], aph ^ 1, s_abort, a.d_error)) { live = false; break; }
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + (uint32_t)(ab * TS_BN);
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(ab * BN);
                     for (int kb = 0; kb < a.n_kblocks; ++kb, ++it) {
                         const int s = it % STAGES;
                         const uint32_t phs = (it / STAGES) & 1;
@@ -687,7 +692,7 @@ project_ts_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                         }
                         ++n_kb;
                         n_lo += use_lo ? 1u : 0u;
-                        const uint32_t axh = tmem_base + (uint32_t)(TS_A_COL0 + s * 2 * TS_KBLK);
+                        const uint32_t axh = tmem_base + (uint32_t)(TS_A_COL0 + (int)(it % A_STAGES) * 2 * TS_KBLK);
                         const uint32_t axl = axh + (uint32_t)TS_KBLK;
                         const uint64_t dph = make_smem_desc<TS_KBLK>(smem_u32(ph(s)));
                         const uint64_t dpl = make_smem_desc<TS_KBLK>(smem_u32(pl(s)));
@@ -743,10 +748,16 @@ project_ts_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                             any_lo |= l != 0.f;
                         }
                     }
-                    // the A stage is free: the producer refilled the stage only after `empty`
+                    // The A stage must be free: the MMAs of K-block it - A_STAGES have completed.  With as
+                    // many A stages as shared-memory stages the producer's wait on `empty` before it
+                    // refilled this stage says so already.
+                    if (A_STAGES < STAGES && it >= (uint32_t)A_STAGES) {
+                        const uint32_t prev = it - (uint32_t)A_STAGES;
+                        if (!mbar_wait(&empty[prev % STAGES], (prev / STAGES) & 1, s_abort, a.d_error)) { live = false; break; }
+                    }
                     tc_fence_after();
                     const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) +
-                                        (uint32_t)(TS_A_COL0 + s * 2 * TS_KBLK);
+                                        (uint32_t)(TS_A_COL0 + (int)(it % A_STAGES) * 2 * TS_KBLK);
 #pragma unroll
                     for (int j = 0; j < KB / 16; ++j) {
                         tc_st16(ta + (uint32_t)(16 * j), hi + 16 * j);
@@ -781,7 +792,7 @@ project_ts_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 const int tables_here = min(a.tables_per_chunk, a.L - t0);
                 const int split = (tables_here + 1) >> 1;
                 const int tb = half == 0 ? 0 : split, te = half == 0 ? split : tables_here;
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * TS_BN);
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * BN);
                 if (te > tb) {
                     bool o;
                     const bool byte_form = FAMILY == CULSH_PSLSH && a.elem_bytes == 1 && ((tb * k) & 15) == 0;
@@ -814,7 +825,7 @@ project_ts_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 // Host side
 // ------------------------------------------------------------------------------------------
 struct TcPlan {
-    int kblk, d_pad, n_chunks, tables_per_chunk, n_mma;
+    int kblk, d_pad, n_chunks, tables_per_chunk, n_mma, bn;
     bool ts;
 };
 
@@ -827,13 +838,19 @@ inline int tc_kblk_choice() {
     return v;
 }
 
-// Which kernel projects a shape.  Measured on B200: project_ts_kernel issues MMAs of N <= 128
-// (64 cycles of tensor work each) and is bound by the rate at which one thread can issue them,
-// project_tc_kernel issues N <= 256 and is bound by shared-memory traffic; the first wins when
-// all hash columns fit one 128-column chunk (12.5M x 96 rows, 16 x 8 hashes: 1.83 vs 2.31 ms),
-// the second otherwise (1M x 128, 32 x 16: 0.61 vs 0.66 ms; 10M x 256, 48 x 24: 25 vs 29 ms).
-// CULSH_TC_VARIANT (read once per process) overrides: 0 = always project_tc_kernel,
-// 1 = project_ts_kernel whenever it applies (the tests run every shape through both).
+// Which kernel projects a shape.  Three forms: both operands in shared memory with chunks of
+// <= 256 hash columns (project_tc_kernel), X in tensor memory with chunks of <= 128 columns, or of
+// <= 192 columns (project_ts_kernel).  Measured on B200 (fit, ms):
+//                                        shared, 256   tensor, 128   tensor, 192
+//   12.5M x 96,  16 x 8  (one chunk)         2.31          1.85           -
+//   1M x 128,    32 x 16                     0.62          0.66          0.62
+//   10M x 256,   48 x 24                     24.8          29            22.7
+// One chunk: the 128-column form.  Several chunks: a unit of n_mma columns costs about
+// 40 + 1.3 * n_mma cycles per K step in every form (the tensor-memory form 9 % less), so the form
+// with the smaller chunks * (40 + 1.3 * n_mma) is taken, the shared-memory one on a tie.
+// CULSH_TC_VARIANT (read once per process) overrides: 0 = shared memory always, 1 = tensor memory /
+// 128 columns wherever it applies, 3 = tensor memory / 192 columns for shapes of several chunks
+// (the tests run every shape through each).
 inline int tc_variant() {
     static int v = [] {
         const char* e = getenv("CULSH_TC_VARIANT");
@@ -842,17 +859,37 @@ inline int tc_variant() {
     return v;
 }
 
+inline void tc_chunking(int L, int k, int bn, int& tables_per_chunk, int& n_chunks, int& n_mma) {
+    tables_per_chunk = std::min(L, bn / k);
+    n_chunks = (L + tables_per_chunk - 1) / tables_per_chunk;
+    n_mma = (tables_per_chunk * k + 15) / 16 * 16;
+}
+
 inline bool tc_plan(int d, int L, int k, TcPlan& p) {
     const int variant = tc_variant();
-    const bool ts = variant == 1 ? k <= TS_BN : (variant == 2 && L * k <= TS_BN);
-    const int bn = ts ? TS_BN : TC_BN;
+    bool ts;
+    int bn;
+    if (variant == 0) { ts = false; bn = TC_BN; }
+    else if (variant == 1) { ts = k <= TS_BN; bn = ts ? TS_BN : TC_BN; }
+    else if (variant == 3) { ts = k <= TS_BN_WIDE; bn = ts ? (L * k > TS_BN ? TS_BN_WIDE : TS_BN) : TC_BN; }
+    else if (L * k <= TS_BN) { ts = true; bn = TS_BN; }
+    else {
+        ts = false; bn = TC_BN;
+        if (k <= TS_BN_WIDE && k <= TC_BN) {
+            int t, c, m;
+            tc_chunking(L, k, TC_BN, t, c, m);
+            const double cost_shared = c * (40.0 + 1.3 * m);
+            tc_chunking(L, k, TS_BN_WIDE, t, c, m);
+            const double cost_tensor = 0.91 * c * (40.0 + 1.3 * m);
+            if (cost_tensor < 0.97 * cost_shared) { ts = true; bn = TS_BN_WIDE; }
+        }
+    }
+    p.bn = bn;
     if (k > bn || d % 4 != 0) return false;
     p.ts = ts;
     p.kblk = ts ? 32 : tc_kblk_choice();
     p.d_pad = (d + p.kblk - 1) / p.kblk * p.kblk;
-    p.tables_per_chunk = std::min(L, bn / k);
-    p.n_chunks = (L + p.tables_per_chunk - 1) / p.tables_per_chunk;
-    p.n_mma = (p.tables_per_chunk * k + 15) / 16 * 16;
+    tc_chunking(L, k, bn, p.tables_per_chunk, p.n_chunks, p.n_mma);
     return true;
 }
 
@@ -950,13 +987,19 @@ inline bool launch_project_tc(const CtxPtr& c, cudaStream_t stream, int family, 
     a.row_offset = row_offset; a.n_total = n_total;
     int grid = std::min(a.n_tiles, c->sm_count);
     if (p.ts) {
-        constexpr int smem_ts = TsCfg<32>::SMEM;
-        if ((size_t)smem_ts > c->smem_optin) return false;
-        auto kern = family == CULSH_RPLSH ? project_ts_kernel<CULSH_RPLSH, 1, 32> : project_ts_kernel<CULSH_PSLSH, 1, 32>;
-        CU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_ts));
-        kern<<<grid, 64 + TC_TRANSFORM_THREADS + TC_EPI_THREADS, smem_ts, stream>>>(tmX, tmP, a);
-        KERNEL_CHECK();
-        return true;
+        auto go = [&](auto kern, int smem_bytes) -> bool {
+            if ((size_t)smem_bytes > c->smem_optin) return false;
+            CU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+            kern<<<grid, 64 + TC_TRANSFORM_THREADS + TC_EPI_THREADS, smem_bytes, stream>>>(tmX, tmP, a);
+            KERNEL_CHECK();
+            return true;
+        };
+        const bool rp = family == CULSH_RPLSH;
+        if (p.bn == TS_BN_WIDE)
+            return rp ? go(project_ts_kernel<CULSH_RPLSH, 1, 32, TS_BN_WIDE>, TsCfg<32, TS_BN_WIDE>::SMEM)
+                      : go(project_ts_kernel<CULSH_PSLSH, 1, 32, TS_BN_WIDE>, TsCfg<32, TS_BN_WIDE>::SMEM);
+        return rp ? go(project_ts_kernel<CULSH_RPLSH, 1, 32, TS_BN>, TsCfg<32, TS_BN>::SMEM)
+                  : go(project_ts_kernel<CULSH_PSLSH, 1, 32, TS_BN>, TsCfg<32, TS_BN>::SMEM);
     }
     auto kern = p.kblk == 32
                     ? (family == CULSH_RPLSH ? project_tc_kernel<32, CULSH_RPLSH> : project_tc_kernel<32, CULSH_PSLSH>)

@@ -709,9 +709,10 @@ def test_shard_merge_equals_unsharded(eng):
 # ------------------------------------------------------------------------------------------
 # tensor-core projection (tcgen05 3xTF32) against the CUDA-core projection and the oracle
 # ------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("variant", [{"CULSH_TC_VARIANT": "0"}, {"CULSH_TC_VARIANT": "1"},
+@pytest.mark.parametrize("variant", [{"CULSH_TC_VARIANT": "0"}, {"CULSH_TC_VARIANT": "1"}, {"CULSH_TC_VARIANT": "3"},
                                      {"CULSH_TC_VARIANT": "0", "CULSH_TC_KBLK": "32"}],
-                         ids=["operands_from_shared_memory", "x_from_tensor_memory", "wide_k_blocks"])
+                         ids=["operands_from_shared_memory", "x_from_tensor_memory", "x_from_tensor_memory_192_columns",
+                              "wide_k_blocks"])
 def test_tensor_core_projection_kernel_variants(variant):
     """Which tensor-core kernel projects a shape is decided once per process (by shape, or by
     CULSH_TC_VARIANT / CULSH_TC_KBLK), so every case below also runs in child processes that
