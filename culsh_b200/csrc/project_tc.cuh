@@ -321,6 +321,55 @@ __device__ __forceinline__ bool epilogue_pslsh_bytes(const TcArgs& a, uint32_t t
     return any_ovf;
 }
 
+// Fast form of the sign-bit epilogue for keys of one word (k <= 32): sixteen accumulator columns
+// become sixteen key bits with straight-line code (no per-element counters or branches as in the
+// general form), the bits run through a 64-bit buffer from which every finished table takes its k
+// bits, and the tensor-memory load of the next sixteen columns is in flight while the current ones
+// are packed.  The general form made the epilogue warps the limit of shapes with few K-blocks per
+// unit (1M x 128, 32 x 16: 1,200 of every 1,400 cycles busy).
+__device__ __forceinline__ void epilogue_rplsh_bits(const TcArgs& a, uint32_t taddr, int c_begin, int c_end,
+                                                    int first_table, int row, bool row_ok) {
+    const int k = a.k;
+    const uint64_t kmask = k == 32 ? 0xFFFFFFFFull : ((1ull << k) - 1ull);
+    int tables_left = (c_end - c_begin) / k;
+    int tbl = first_table;
+    uint64_t buf = 0;
+    int nbits = -(c_begin & 15);  // columns of the first group that lie before c_begin are dropped
+    auto consume = [&](const uint32_t (&r)[16]) {
+        uint32_t m = 0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) m |= ((~r[j]) >> 31) << (15 - j);  // 1 where the sign bit is clear (rplsh/hash.cuh:47)
+        if (nbits < 0) { m &= 0xFFFFu >> (-nbits); }
+        buf = (buf << 16) | (uint64_t)m;
+        nbits += 16;
+        while (nbits >= k && tables_left > 0) {  // warp-uniform
+            const uint32_t key = (uint32_t)((buf >> (nbits - k)) & kmask);
+            if (row_ok) a.keys[(size_t)tbl * a.n_total + a.row_offset + row] = key;
+            nbits -= k; ++tbl; --tables_left;
+        }
+    };
+    // groups of sixteen columns on sixteen-column boundaries (the last group may reach past c_end,
+    // never past the accumulator: its width is a multiple of sixteen); the load of the next group
+    // is in flight while the current one is packed
+    uint32_t ra[16], rb[16];
+    int g = c_begin & ~15;
+    tc_ld16(taddr + (uint32_t)g, ra);
+    tc_ld_wait();
+    while (tables_left > 0) {
+        const bool n1 = g + 16 < c_end;
+        if (n1) tc_ld16(taddr + (uint32_t)(g + 16), rb);
+        consume(ra);
+        if (!n1) break;
+        tc_ld_wait();
+        const bool n2 = g + 32 < c_end;
+        if (n2) tc_ld16(taddr + (uint32_t)(g + 32), ra);
+        consume(rb);
+        if (!n2) break;
+        tc_ld_wait();
+        g += 32;
+    }
+}
+
 template <int KBLK, int FAMILY>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmP, TcArgs a) {
@@ -514,7 +563,8 @@ project_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 if (te > tb) {
                     bool o;
                     const bool byte_form = FAMILY == CULSH_PSLSH && a.elem_bytes == 1 && ((tb * k) & 15) == 0;
-                    if (byte_form && k == 8) o = epilogue_pslsh_bytes<8>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    if (FAMILY == CULSH_RPLSH && NW == 1) { epilogue_rplsh_bits(a, taddr, tb * k, te * k, t0 + tb, row, row_ok); o = false; }
+                    else if (byte_form && k == 8) o = epilogue_pslsh_bytes<8>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
                     else if (byte_form && k == 4) o = epilogue_pslsh_bytes<4>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
                     else if (byte_form && k == 16) o = epilogue_pslsh_bytes<16>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
                     else if (byte_form && k == 2) o = epilogue_pslsh_bytes<2>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
@@ -796,7 +846,8 @@ project_ts_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 if (te > tb) {
                     bool o;
                     const bool byte_form = FAMILY == CULSH_PSLSH && a.elem_bytes == 1 && ((tb * k) & 15) == 0;
-                    if (byte_form && k == 8) o = epilogue_pslsh_bytes<8>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
+                    if (FAMILY == CULSH_RPLSH && NW == 1) { epilogue_rplsh_bits(a, taddr, tb * k, te * k, t0 + tb, row, row_ok); o = false; }
+                    else if (byte_form && k == 8) o = epilogue_pslsh_bytes<8>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
                     else if (byte_form && k == 4) o = epilogue_pslsh_bytes<4>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
                     else if (byte_form && k == 16) o = epilogue_pslsh_bytes<16>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
                     else if (byte_form && k == 2) o = epilogue_pslsh_bytes<2>(a, taddr, tb * k, te * k, t0 + tb, t0 * k, row, row_ok);
