@@ -728,11 +728,15 @@ def test_tensor_core_projection_kernel_variants(variant):
                          env=env, capture_output=True, text=True, timeout=900)
     tail = (res.stdout + res.stderr)[-2000:]
     assert res.returncode == 0, tail
-    assert "7 passed" in res.stdout, tail
+    assert "11 passed" in res.stdout, tail
 
 
 @pytest.mark.parametrize("fam,n,d,L,k", [("rplsh", 5000, 128, 32, 16), ("rplsh", 1000, 100, 8, 12),
                                          ("rplsh", 3333, 256, 48, 24), ("rplsh", 130, 64, 3, 40),
+                                         # sign-bit packer: second half of a unit starting off a 16-column
+                                         # boundary (36, 4, 10), one bit and 32 bits per key
+                                         ("rplsh", 777, 48, 5, 12), ("rplsh", 500, 32, 7, 1),
+                                         ("rplsh", 640, 40, 3, 5), ("rplsh", 900, 64, 3, 32),
                                          ("pslsh", 4097, 96, 16, 8), ("pslsh", 999, 32, 5, 3),
                                          ("pslsh", 2000, 128, 4, 16)])
 @pytest.mark.parametrize("kblk", [int(os.environ.get("CULSH_TC_KBLK", "16"))])  # chosen per process
