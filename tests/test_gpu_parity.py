@@ -364,6 +364,32 @@ def test_minhash_values_next_to_the_prime(eng):
     assert np.array_equal(got, want)
 
 
+def test_warp_path_sorts_up_to_1024_ids(eng):
+    """One or two tables of ~700-row buckets: raw candidate counts on both sides of 512 (sixteen ids
+    per lane of the warp's sort network) and of 1024 (thirty-two, the warp path's limit)."""
+    culsh, core_mod = eng
+    rng = np.random.RandomState(77)
+    n, d = 45000, 10
+    X = rng.randn(n, d).astype(np.float32)
+    seen = np.zeros(3, bool)
+    for L, k in ((1, 6), (2, 7)):
+        model = culsh.RPLSH(L, k, seed=5).fit(X)
+        core = core_mod.RPLSHCore(L, k, 5)
+        sig = _sig_matrix(core.hash(X, model.index))
+        sel = rng.randint(0, n, 96)
+        want = oracle.query_index(oracle.fit_index(sig, L, k), sig[sel])
+        raw = np.zeros(len(sel), np.int64)  # raw = sum of the matched buckets' sizes
+        for t in range(L):
+            keys = [bytes(r) for r in sig[:, t * k:(t + 1) * k]]
+            sizes = {}
+            for kk in keys:
+                sizes[kk] = sizes.get(kk, 0) + 1
+            raw += np.array([sizes[keys[i]] for i in sel])
+        seen |= np.array([(raw <= 512).any(), ((raw > 512) & (raw <= 1024)).any(), (raw > 1024).any()])
+        _assert_candidates_equal(model.query(X[sel]), want)
+    assert seen.all(), seen
+
+
 def test_large_buckets_use_the_bitmap_path(eng):
     """k = 2 sign bits -> four buckets per table of ~n/4 rows: raw candidate counts far above
     the warp path's limit; heavy cross-table duplication."""
@@ -408,7 +434,7 @@ def test_sort_path_for_mid_sized_sets_on_a_large_index(eng):
     cand = model.query(X[sel])
     want = oracle.query_index(oidx, sig[sel])
     counts = want[2].astype(np.int64)
-    assert ((counts > 512) & (counts <= 8192)).mean() >= 0.3  # a good share takes the sort path
+    assert ((counts > 1024) & (counts <= 8192)).mean() >= 0.15  # a good share takes the sort path
     _assert_candidates_equal(cand, want)
     # one-table, few-bit index on the same rows: sets far above the sort path's limit
     m2 = culsh.RPLSH(2, 3, seed=8).fit(X)
