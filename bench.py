@@ -456,7 +456,7 @@ NCU_TRAFFIC = {
     ("c2", 1_000_000): {
         "gather": 273_526_528 + 677_084_416,   # profiles/dedupe_chained_rank_kernel_c2_1M.md
         "sort": 264_078_336 + 203_595_776,     # profiles/radix_scatter_kernel_c2_1M.md (second pass)
-        "hash": 512_629_760 + 113_291_008,     # profiles/project_tc_kernel_c2_1M.md
+        "hash": 512_630_784 + 113_564_928,     # profiles/project_tc_kernel_c2_1M.md
     },
 }
 
